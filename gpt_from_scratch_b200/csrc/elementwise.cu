@@ -1,0 +1,412 @@
+// Memory-bound kernels of the training step: RMSNorm fwd/bwd, rotary embedding,
+// SwiGLU fwd/bwd, embedding lookup fwd/bwd. Each replaces a chain of ATen kernels of
+// the reference with one pass over the data (16-byte vector accesses, fp32 math).
+//
+// Reference counterparts: core/normalization.py:13-25 (RMSNorm), core/rope_triton.py:74-141
+// (RoPE), core/mlp.py:25-28 (SwiGLU), core/tensor_parallel/layers.py:117-134 (embedding).
+#include <algorithm>
+
+#include "common.cuh"
+
+using namespace gfs;
+
+namespace {
+
+constexpr int NORM_WARPS = 4;
+constexpr int NORM_MAXV = 16;  // vectors of 8 bf16 cached per lane: covers H <= 4096
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---------------------------------------------------------------------------
+// RMSNorm forward: y = bf16(x * rstd) * w, rstd = rsqrt(mean(x^2) + eps). One warp per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = H >> 3;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * H;
+  uint4 cache[NORM_MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      cache[i] = *reinterpret_cast<const uint4*>(xr + 8 * v);
+      const float2 a = unpack_bf16x2(cache[i].x), b = unpack_bf16x2(cache[i].y), c = unpack_bf16x2(cache[i].z),
+                   d = unpack_bf16x2(cache[i].w);
+      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    }
+  }
+  for (int v = lane + 32 * NORM_MAXV; v < nvec; v += 32) {
+    float f[8];
+    load8(xr + 8 * v, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float f[8], g[8];
+      const float2 a = unpack_bf16x2(cache[i].x), b = unpack_bf16x2(cache[i].y), c = unpack_bf16x2(cache[i].z),
+                   d = unpack_bf16x2(cache[i].w);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+      load8(w + 8 * v, g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = round_bf16(f[e] * rstd) * g[e];
+      store8(yr + 8 * v, f);
+    }
+  }
+  for (int v = lane + 32 * NORM_MAXV; v < nvec; v += 32) {
+    float f[8], g[8];
+    load8(xr + 8 * v, f);
+    load8(w + 8 * v, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = round_bf16(f[e] * rstd) * g[e];
+    store8(yr + 8 * v, f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward. Each CTA owns a contiguous block of rows; every lane keeps the
+// weight-gradient partial of its own columns in registers across the rows of its
+// warp, so dw needs no atomics: partials [gridDim.x, H] are summed by a second kernel.
+//   g = dy * w;  dx = rstd * g - x * rstd^3 * mean(g * x)  (+ dres);  dw += dy * bf16(x * rstd)
+// ---------------------------------------------------------------------------
+constexpr int NB_WARPS = 8;
+constexpr int NB_MAXV = 4;  // register-cached column vectors per lane (H <= 1024); more are handled in column slabs
+
+__global__ void __launch_bounds__(NB_WARPS * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int H, int rows_per_cta) {
+  extern __shared__ float red[];  // [NB_WARPS][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H >> 3;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  float* my_red = red + static_cast<size_t>(warp) * H;
+  for (int i = lane; i < H; i += 32) my_red[i] = 0.f;
+  __syncwarp();
+
+  for (int row = r0 + warp; row < r1; row += NB_WARPS) {
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float a[8], b[8], c[8];
+      load8(dyr + 8 * v, a);
+      load8(xr + 8 * v, b);
+      load8(w + 8 * v, c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += a[e] * c[e] * b[e];
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rs * rs * rs / static_cast<float>(H);
+    for (int v = lane; v < nvec; v += 32) {
+      float a[8], b[8], c[8], o[8];
+      load8(dyr + 8 * v, a);
+      load8(xr + 8 * v, b);
+      load8(w + 8 * v, c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rs * a[e] * c[e] - b[e] * coef;
+      if (dres != nullptr) {
+        float d[8];
+        load8(dres + static_cast<size_t>(row) * H + 8 * v, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += d[e];
+      }
+      store8(dxr + 8 * v, o);
+      float* acc = my_red + 8 * v;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += a[e] * round_bf16(b[e] * rs);
+    }
+  }
+  __syncthreads();
+  float* outp = dw_partial + static_cast<size_t>(blockIdx.x) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < NB_WARPS; ++wv) s += red[static_cast<size_t>(wv) * H + i];
+    outp[i] = s;
+  }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int parts,
+                                         int H, int accumulate) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[static_cast<size_t>(p) * H + i];
+  if (accumulate) s += __bfloat162float(dw[i]);
+  dw[i] = __float2bfloat16_rn(s);
+}
+
+// ---------------------------------------------------------------------------
+// Rotary embedding, interleaved pairs, in place on `parts` consecutive [nh*D] blocks
+// of every token (parts = 2: the q and k thirds of a [S,B,3,nh,D] buffer).
+//   x'[2i] = x[2i] cos - x[2i+1] sin ; x'[2i+1] = x[2i] sin + x[2i+1] cos ; backward: sin -> -sin
+// ---------------------------------------------------------------------------
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cosb,
+                            const float* __restrict__ sinb, int S, int B, int nhD, int D, int parts,
+                            long token_stride, int backward, int s_offset) {
+  const int vec_per_token = (parts * nhD) >> 3;
+  const size_t total = static_cast<size_t>(S) * B * vec_per_token;
+  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
+       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t token = v / vec_per_token;
+    const int e0 = static_cast<int>(v % vec_per_token) << 3;
+    const int s = static_cast<int>(token / B) + s_offset;
+    const int d = e0 % D;
+    __nv_bfloat16* p = x + token * token_stride + e0;
+    float f[8];
+    load8(p, f);
+    const float4 c = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(s) * (D >> 1) + (d >> 1));
+    float4 sn = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(s) * (D >> 1) + (d >> 1));
+    if (backward) {
+      sn.x = -sn.x; sn.y = -sn.y; sn.z = -sn.z; sn.w = -sn.w;
+    }
+    float o[8];
+    o[0] = f[0] * c.x - f[1] * sn.x; o[1] = f[0] * sn.x + f[1] * c.x;
+    o[2] = f[2] * c.y - f[3] * sn.y; o[3] = f[2] * sn.y + f[3] * c.y;
+    o[4] = f[4] * c.z - f[5] * sn.z; o[5] = f[4] * sn.z + f[5] * c.z;
+    o[6] = f[6] * c.w - f[7] * sn.w; o[7] = f[6] * sn.w + f[7] * c.w;
+    store8(p, o);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU on a [M, 2I] buffer whose first I columns are the gate and last I the up half.
+// ---------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int M, int I) {
+  const int vec_per_row = I >> 3;
+  const size_t total = static_cast<size_t>(M) * vec_per_row;
+  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
+       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = v / vec_per_row;
+    const int c = static_cast<int>(v % vec_per_row) << 3;
+    float g[8], u[8], o[8];
+    load8(gu + row * 2 * I + c, g);
+    load8(gu + row * 2 * I + I + c, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sg = 1.f / (1.f + __expf(-g[e]));
+      // silu rounded to bf16 before the product, as two separate bf16 ops would do
+      o[e] = round_bf16(g[e] * sg) * u[e];
+    }
+    store8(act + row * I + c, o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, int M, int I) {
+  const int vec_per_row = I >> 3;
+  const size_t total = static_cast<size_t>(M) * vec_per_row;
+  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
+       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = v / vec_per_row;
+    const int c = static_cast<int>(v % vec_per_row) << 3;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + row * 2 * I + c, g);
+    load8(gu + row * 2 * I + I + c, u);
+    load8(dact + row * I + c, d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sg = 1.f / (1.f + __expf(-g[e]));
+      const float silu = g[e] * sg;
+      dg[e] = d[e] * u[e] * sg * (1.f + g[e] * (1.f - sg));
+      du[e] = d[e] * silu;
+    }
+    store8(dgu + row * 2 * I + c, dg);
+    store8(dgu + row * 2 * I + I + c, du);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Embedding forward: out[s - s0, b, :] = W[id - v0] if v0 <= id < v1 else 0, ids are [B, S].
+// One warp per output row.
+// ---------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ W,
+                                     __nv_bfloat16* __restrict__ out, int B, int S, int H, int v0, int v1, int s0,
+                                     int s_count) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= s_count * B) return;
+  const int s = s0 + r / B;
+  const int b = r % B;
+  const long long id = ids[static_cast<size_t>(b) * S + s];
+  __nv_bfloat16* o = out + static_cast<size_t>(r) * H;
+  const int nvec = H >> 3;
+  if (id >= v0 && id < v1) {
+    const __nv_bfloat16* src = W + static_cast<size_t>(id - v0) * H;
+    for (int v = lane; v < nvec; v += 32)
+      *reinterpret_cast<uint4*>(o + 8 * v) = *reinterpret_cast<const uint4*>(src + 8 * v);
+  } else {
+    for (int v = lane; v < nvec; v += 32) *reinterpret_cast<uint4*>(o + 8 * v) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// Embedding backward over token ids sorted ascending (perm gives each sorted position's
+// row in dout). A warp owns one run of equal ids and sums its rows in sorted order,
+// so the result is deterministic; dW rows are accumulated (bf16, fp32 sum).
+__global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ perm,
+                                     const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dW, int n,
+                                     int H, int v0, int v1) {
+  const int lane = threadIdx.x & 31;
+  const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= n) return;
+  const long long id = sorted_ids[p];
+  if (id < v0 || id >= v1) return;
+  if (p > 0 && sorted_ids[p - 1] == id) return;  // not the start of a run
+  int q_end = p + 1;
+  while (q_end < n && sorted_ids[q_end] == id) ++q_end;
+  __nv_bfloat16* dst = dW + static_cast<size_t>(id - v0) * H;
+  const int nvec = H >> 3;
+  for (int v = lane; v < nvec; v += 32) {
+    float acc[8];
+    load8(dst + 8 * v, acc);
+    for (int q = p; q < q_end; ++q) {
+      float f[8];
+      load8(dout + static_cast<size_t>(perm[q]) * H + 8 * v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    store8(dst + 8 * v, acc);
+  }
+}
+
+inline int grid_for(size_t work_items, int threads, int max_blocks_per_sm = 16) {
+  const size_t blocks = (work_items + threads - 1) / threads;
+  const size_t cap = static_cast<size_t>(gfs_host::sm_count()) * max_blocks_per_sm;
+  return static_cast<int>(std::max<size_t>(1, std::min(blocks, cap)));
+}
+
+}  // namespace
+
+extern "C" {
+
+int gfs_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows, int H, float eps, void* stream) {
+  if (H & 7) return -1;
+  if (rows == 0) return 0;
+  const int blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
+  rmsnorm_fwd_kernel<<<blocks, NORM_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<float*>(rstd), rows, H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Number of fp32 elements the backward needs in `partial`: parts * H with parts from this call.
+int gfs_rmsnorm_bwd_parts(int rows) {
+  const int sms = gfs_host::sm_count();
+  const int want = sms * 2;
+  const int rows_per_cta = std::max(NB_WARPS, (rows + want - 1) / want);
+  return (rows + rows_per_cta - 1) / rows_per_cta;
+}
+
+// dx = rmsnorm backward (+ dres); dw (bf16 [H]) written or accumulated. partial: fp32 scratch [parts*H].
+int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* dres, void* dx,
+                    void* dw, void* partial, int rows, int H, int accumulate_dw, void* stream_) {
+  if (H & 7) return -1;
+  if (rows == 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int parts = gfs_rmsnorm_bwd_parts(rows);
+  const int rows_per_cta = (rows + parts - 1) / parts;
+  const size_t smem = static_cast<size_t>(NB_WARPS) * H * sizeof(float);
+  if (smem > 200 * 1024) return -1;
+  static int smem_set = 0;
+  if (smem > 48 * 1024 && smem_set < static_cast<int>(smem)) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return -10;
+    smem_set = 200 * 1024;
+  }
+  rmsnorm_bwd_kernel<<<parts, NB_WARPS * 32, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
+      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), static_cast<float*>(partial), rows, H,
+      rows_per_cta);
+  if (cudaGetLastError() != cudaSuccess) return -11;
+  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, stream>>>(static_cast<const float*>(partial),
+                                                              static_cast<__nv_bfloat16*>(dw), parts, H,
+                                                              accumulate_dw);
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+int gfs_rope(void* x, const void* cosb, const void* sinb, int S, int B, int nh, int D, int parts, long token_stride,
+             int backward, int s_offset, void* stream) {
+  if ((D & 7) || (token_stride & 7)) return -1;
+  const size_t total = static_cast<size_t>(S) * B * ((static_cast<size_t>(parts) * nh * D) >> 3);
+  if (total == 0) return 0;
+  rope_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), static_cast<const float*>(cosb), static_cast<const float*>(sinb), S, B, nh * D,
+      D, parts, token_stride, backward, s_offset);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_swiglu_fwd(const void* gu, void* act, int M, int I, void* stream) {
+  if (I & 7) return -1;
+  const size_t total = static_cast<size_t>(M) * (I >> 3);
+  if (total == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(act), M, I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_swiglu_bwd(const void* dact, const void* gu, void* dgu, int M, int I, void* stream) {
+  if (I & 7) return -1;
+  const size_t total = static_cast<size_t>(M) * (I >> 3);
+  if (total == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(gu),
+      static_cast<__nv_bfloat16*>(dgu), M, I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_embedding_fwd(const void* ids, const void* W, void* out, int B, int S, int H, int v0, int v1, int s0,
+                      int s_count, void* stream) {
+  if (H & 7) return -1;
+  const int rows = s_count * B;
+  if (rows == 0) return 0;
+  const int warps = 8;
+  embedding_fwd_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(ids), static_cast<const __nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(out), B, S,
+      H, v0, v1, s0, s_count);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_embedding_bwd(const void* sorted_ids, const void* perm, const void* dout, void* dW, int n, int H, int v0,
+                      int v1, void* stream) {
+  if (H & 7) return -1;
+  if (n == 0) return 0;
+  const int warps = 8;
+  embedding_bwd_kernel<<<(n + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(sorted_ids), static_cast<const long long*>(perm),
+      static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dW), n, H, v0, v1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // extern "C"

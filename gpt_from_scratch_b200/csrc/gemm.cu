@@ -1,0 +1,416 @@
+// bf16 GEMM for sm_100a: C[M,N] = op(A)[M,K] * op(B)[K,N] (+ R), fp32 accumulation in TMEM.
+//
+// One persistent CTA per SM, six warps with fixed roles:
+//   warp 0    TMA producer  (cp.async.bulk.tensor 2-D loads, 128-byte swizzle, STAGES-deep ring)
+//   warp 1    MMA issuer    (one thread issues tcgen05.mma 128xBNx16; owns the TMEM allocation)
+//   warps 2-5 epilogue      (tcgen05.ld -> registers -> bf16/fp32 global stores), double-buffered
+//                           accumulators so tile i's epilogue overlaps tile i+1's main loop
+//
+// Operand layouts (all row-major in global memory, leading dimension in elements):
+//   A K-major : A is [M, K]          A MN-major: A is stored as [K, M]
+//   B K-major : B is [N, K]          B MN-major: B is stored as [K, N]
+// which covers the three GEMMs of a linear layer without any transposed copies:
+//   forward  Y = X W^T        : A = X  (K-major),  B = W  (K-major)
+//   dgrad    dX = dY W        : A = dY (K-major),  B = W  (MN-major, contraction over W's rows)
+//   wgrad    dW = dY^T X      : A = dY (MN-major), B = X  (MN-major), contraction over tokens
+//
+// Small outputs (wgrad of the per-layer linears) use deterministic split-K: each split
+// writes an fp32 partial tile to a workspace and a second kernel sums the splits in a
+// fixed order, adds the optional addend and rounds once to bf16.
+//
+// Counterpart in the reference: the cuBLAS calls behind F.linear and its autograd
+// (core/tensor_parallel/layers.py:47,82).
+#include <algorithm>
+#include <cstdio>
+
+#include "common.cuh"
+
+using namespace gfs;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum EpiMode : int { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL_F32 = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int ldc, ldr;
+  __nv_bfloat16* C;
+  const __nv_bfloat16* R;
+  float* ws;
+  int split_k;
+  int kblocks_total;
+  int kblocks_per_split;
+  int tiles_m, tiles_n;
+  int epi_mode;
+  uint32_t* status;
+};
+
+template <int BN, int STAGES>
+struct SmemCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-B alignment
+};
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  using Cfg = SmemCfg<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128B swizzle wants tile bases aligned to 1024 B.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                  // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;        // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;    // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
+
+  const int tiles_mn = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_mn * p.split_k;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const int z = t / tiles_mn;
+        const int mn = t - z * tiles_mn;
+        const int m0 = (mn / p.tiles_n) * BM;
+        const int n0 = (mn % p.tiles_n) * BN;
+        const int kb0 = z * p.kblocks_per_split;
+        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+          uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmap_a, &full_bar[stage], m0 + 64 * i, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmap_b, &full_bar[stage], n0 + 64 * i, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (*abort_flag) {
+        // let copies that are still in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const int z = t / tiles_mn;
+        const int kb0 = z * p.kblocks_per_split;
+        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_split);
+        mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, wctx, STATUS_TIMEOUT_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&full_bar[stage], phase, wctx, STATUS_TIMEOUT_PIPE_FULL);
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = A_MN ? umma_desc_sw128(sa + k * 2048, 8192, 1024)
+                                        : umma_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_desc_sw128(sb + k * 2048, 8192, 1024)
+                                        : umma_desc_sw128(sb + k * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit(&tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int z = t / tiles_mn;
+      const int mn = t - z * tiles_mn;
+      const int m0 = (mn / p.tiles_n) * BM;
+      const int n0 = (mn % p.tiles_n) * BN;
+      mbar_wait(&tmem_full[acc], acc_phase, wctx, STATUS_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c, v);
+        tmem_ld_wait();
+        if (row < p.M) {
+          if (p.epi_mode == EPI_PARTIAL_F32) {
+            float* dst = p.ws + (static_cast<size_t>(z) * p.M + row) * p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (col0 + 4 * j + 4 <= p.N) {
+                float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                *reinterpret_cast<float4*>(dst + 4 * j) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
+            const __nv_bfloat16* res = p.R + static_cast<size_t>(row) * p.ldr + col0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col0 + 8 * j + 8 <= p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * j + e]);
+                if (p.epi_mode == EPI_ADD) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(res + 8 * j);
+                  const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
+                               r3 = unpack_bf16x2(rr.w);
+                  f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
+                  f[4] += r2.x; f[5] += r2.y; f[6] += r3.x; f[7] += r3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// Sum split-K partials in split order, add the optional addend, round once to bf16.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ C,
+                                     const __nv_bfloat16* __restrict__ R, int M, int N, int ldc, int ldr, int splits,
+                                     int add) {
+  const int groups_per_row = N >> 3;
+  const size_t total = static_cast<size_t>(M) * groups_per_row;
+  for (size_t g = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; g < total;
+       g += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(g / groups_per_row);
+    const int col = static_cast<int>(g % groups_per_row) << 3;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int z = 0; z < splits; ++z) {
+      const float4* src = reinterpret_cast<const float4*>(ws + (static_cast<size_t>(z) * M + row) * N + col);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    if (add) {
+      const uint4 rr = *reinterpret_cast<const uint4*>(R + static_cast<size_t>(row) * ldr + col);
+      const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
+                   r3 = unpack_bf16x2(rr.w);
+      acc[0] += r0.x; acc[1] += r0.y; acc[2] += r1.x; acc[3] += r1.y;
+      acc[4] += r2.x; acc[5] += r2.y; acc[6] += r3.x; acc[7] += r3.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(C + static_cast<size_t>(row) * ldc + col) = o;
+  }
+}
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+int launch_variant(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = SmemCfg<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, STAGES>;
+  static bool attr_set = false;
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set || attr_dev != dev) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::TOTAL) != cudaSuccess) return -10;
+    attr_set = true;
+    attr_dev = dev;
+  }
+  kern<<<grid, GEMM_THREADS, Cfg::TOTAL, stream>>>(*ta, *tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int choose_split(int tiles, int kblocks, int sms, size_t mn_elems, size_t ws_bytes) {
+  if (tiles * 10 >= sms * 9 || kblocks < 8) return 1;
+  int best = 1;
+  long best_cost = 1L << 60;
+  for (int s = 1; s <= 16; ++s) {
+    const int per = (kblocks + s - 1) / s;
+    if (per < 4) break;
+    if ((per * (s - 1)) >= kblocks) continue;  // would leave an empty split
+    if (s > 1 && static_cast<size_t>(s) * mn_elems * 4 > ws_bytes) break;
+    const long waves = (static_cast<long>(tiles) * s + sms - 1) / sms;
+    const long cost = waves * (per + 6) + (s > 1 ? 6 * s : 0);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+extern "C" {
+
+// C[M,N] = op(A) op(B) (+R when add != 0). See the file header for operand layouts.
+// ws/ws_bytes: fp32 workspace for split-K (may be null: split-K is then disabled).
+// force_split: 0 = automatic, >0 = use exactly that many splits (tests).
+// Returns 0 on success, a negative value if the arguments cannot be served.
+int gfs_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc,
+                  int ldr, int a_mn_major, int b_mn_major, int add, void* ws, size_t ws_bytes, int force_split,
+                  void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || (add && (ldr & 7))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       (add ? reinterpret_cast<uintptr_t>(R) : 0)) & 15)
+    return -2;
+  const int BN = (N > 128) ? 256 : 128;
+  const CUtensorMap* ta = a_mn_major ? gfs_host::tmap_2d_cached(A, K, M, lda, 64, 64)
+                                     : gfs_host::tmap_2d_cached(A, M, K, lda, BM, 64);
+  const CUtensorMap* tb = b_mn_major ? gfs_host::tmap_2d_cached(B, K, N, ldb, 64, 64)
+                                     : gfs_host::tmap_2d_cached(B, N, K, ldb, BN, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ldr = ldr;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.ws = static_cast<float*>(ws);
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.kblocks_total = (K + BK - 1) / BK;
+  p.status = gfs_host::status_words();
+  const int sms = gfs_host::sm_count();
+  const int tiles = p.tiles_m * p.tiles_n;
+  int split = 1;
+  if (ws != nullptr) {
+    split = force_split > 0 ? force_split
+                            : choose_split(tiles, p.kblocks_total, sms, static_cast<size_t>(M) * N, ws_bytes);
+    if (split > p.kblocks_total) split = p.kblocks_total;
+    if (split > 1 && static_cast<size_t>(split) * M * N * 4 > ws_bytes) split = 1;
+  }
+  p.kblocks_per_split = (p.kblocks_total + split - 1) / split;
+  split = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;  // no empty splits
+  p.split_k = split;
+  p.epi_mode = split > 1 ? EPI_PARTIAL_F32 : (add ? EPI_ADD : EPI_STORE);
+  const int grid = std::min(tiles * split, sms);
+
+  int rc;
+  if (BN == 256) {
+    if (!a_mn_major && !b_mn_major) rc = launch_variant<false, false, 256, 4>(ta, tb, p, grid, stream);
+    else if (!a_mn_major && b_mn_major) rc = launch_variant<false, true, 256, 4>(ta, tb, p, grid, stream);
+    else if (a_mn_major && b_mn_major) rc = launch_variant<true, true, 256, 4>(ta, tb, p, grid, stream);
+    else rc = launch_variant<true, false, 256, 4>(ta, tb, p, grid, stream);
+  } else {
+    if (!a_mn_major && !b_mn_major) rc = launch_variant<false, false, 128, 6>(ta, tb, p, grid, stream);
+    else if (!a_mn_major && b_mn_major) rc = launch_variant<false, true, 128, 6>(ta, tb, p, grid, stream);
+    else if (a_mn_major && b_mn_major) rc = launch_variant<true, true, 128, 6>(ta, tb, p, grid, stream);
+    else rc = launch_variant<true, false, 128, 6>(ta, tb, p, grid, stream);
+  }
+  if (rc != 0) return rc;
+  if (split > 1) {
+    const size_t groups = static_cast<size_t>(M) * (N >> 3);
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<size_t>((groups + threads - 1) / threads, static_cast<size_t>(sms) * 8));
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p.ws, p.C, p.R, M, N, ldc, ldr, split, add);
+    if (cudaGetLastError() != cudaSuccess) return -12;
+  }
+  return 0;
+}
+
+// Number of kernels gfs_gemm_bf16 launches for this problem (1, or 2 with split-K).
+int gfs_gemm_bf16_launches(int M, int N, int K, size_t ws_bytes) {
+  const int BN = (N > 128) ? 256 : 128;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int kb = (K + BK - 1) / BK;
+  int s = ws_bytes ? choose_split(tiles, kb, gfs_host::sm_count(), static_cast<size_t>(M) * N, ws_bytes) : 1;
+  return s > 1 ? 2 : 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+"""bf16 GEMMs of a linear layer (forward, dgrad, wgrad) on the tcgen05 kernel.
+
+On CUDA bf16 tensors the three products run on ``gfs_gemm_bf16`` (csrc/gemm.cu);
+on any other device/dtype they are plain ``torch.matmul`` calls so the same model
+code runs in fp32 on CPU.
+
+Counterpart in the reference: ``F.linear`` and its autograd in
+core/tensor_parallel/layers.py:47,82.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_WS_BYTES = 96 << 20
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        ws = torch.empty(_WS_BYTES // 4, dtype=torch.float32, device=device)
+        _workspaces[idx] = ws
+    return ws
+
+
+def use_native(*tensors: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+
+
+def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
+    """Return a 2-D tensor whose last dim is contiguous and whose pitch/base fit TMA."""
+    assert t.dim() == 2
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+              out: torch.Tensor | None = None, addend: torch.Tensor | None = None,
+              force_split: int = 0) -> torch.Tensor:
+    """``out[M,N] = op(a) @ op(b) (+ addend)`` with fp32 accumulation.
+
+    ``a`` is ``[M,K]`` (K-major) or ``[K,M]`` (``a_mn_major``); ``b`` is ``[N,K]``
+    (K-major) or ``[K,N]`` (``b_mn_major``). ``addend`` may alias ``out``.
+    """
+    a = _rowmajor_2d(a)
+    b = _rowmajor_2d(b)
+    if a_mn_major:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn_major:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, (a.shape, b.shape, a_mn_major, b_mn_major)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    ws = _workspace(a.device)
+    rc = _lib.lib().gfs_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(addend),
+        M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        addend.stride(0) if addend is not None else 0,
+        1 if a_mn_major else 0, 1 if b_mn_major else 0, 1 if addend is not None else 0,
+        ws.data_ptr(), ws.numel() * 4, force_split, _lib.stream_ptr())
+    _lib.check(rc, "gfs_gemm_bf16")
+    return out
+
+
+def linear_fwd(x2d: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x2d[M,K] @ w[N,K]^T (+ residual[M,N])``."""
+    if use_native(x2d, w):
+        return gemm_bf16(x2d, w, out=out, addend=residual)
+    y = x2d @ w.t()
+    if residual is not None:
+        y = y + residual
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def linear_dgrad(dy2d: torch.Tensor, w: torch.Tensor, addend: torch.Tensor | None = None,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """``dy2d[M,N] @ w[N,K] (+ addend[M,K])``."""
+    if use_native(dy2d, w):
+        return gemm_bf16(dy2d, w, b_mn_major=True, out=out, addend=addend)
+    dx = dy2d @ w
+    if addend is not None:
+        dx = dx + addend
+    if out is not None:
+        out.copy_(dx)
+        return out
+    return dx
+
+
+def linear_wgrad(dy2d: torch.Tensor, x2d: torch.Tensor, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """``dy2d[M,N]^T @ x2d[M,K]`` -> ``[N,K]``; written or accumulated into ``out``."""
+    if use_native(dy2d, x2d) and (out is None or use_native(out)):
+        return gemm_bf16(dy2d, x2d, a_mn_major=True, b_mn_major=True, out=out,
+                         addend=out if (accumulate and out is not None) else None)
+    dw = dy2d.t() @ x2d
+    if out is not None:
+        if accumulate:
+            out.add_(dw)
+        else:
+            out.copy_(dw)
+        return out
+    return dw

@@ -1,0 +1,71 @@
+"""Numerics of the tcgen05 GEMM against an fp32 PyTorch reference (all operand layouts)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn, addend):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    y = A @ B
+    if addend is not None:
+        y = y + addend.float()
+    return y
+
+
+def _check(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    # bf16 output rounding (2^-8 relative) plus accumulation-order noise
+    assert err <= 1.5e-2 * scale + 1e-3, f"max err {err} vs scale {scale} (K={K})"
+
+
+SHAPES = [
+    (128, 256, 64), (128, 128, 128), (256, 512, 256), (384, 768, 768), (1000, 1384, 328),
+    (130, 8, 72), (2048, 2304, 768), (96, 4096, 1024),
+]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(cuda_device, M, N, K, a_mn, b_mn):
+    from gpt_from_scratch_b200.ops.gemm import gemm_bf16
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        pytest.skip("pitch must be a multiple of 8 elements")
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device=cuda_device, generator=g).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=cuda_device, generator=g).bfloat16()
+    out = gemm_bf16(a, b, a_mn_major=a_mn, b_mn_major=b_mn)
+    _check(out, _ref(a, b, a_mn, b_mn, None), K)
+
+
+@pytest.mark.parametrize("split", [0, 1, 2, 5])
+def test_gemm_splitk_and_addend(cuda_device, split):
+    from gpt_from_scratch_b200.ops.gemm import gemm_bf16
+    M, N, K = 768, 768, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn((K, M), device=cuda_device, generator=g).bfloat16()
+    b = torch.randn((K, N), device=cuda_device, generator=g).bfloat16()
+    r = torch.randn((M, N), device=cuda_device, generator=g).bfloat16()
+    out = r.clone()
+    gemm_bf16(a, b, a_mn_major=True, b_mn_major=True, out=out, addend=out, force_split=split)
+    _check(out, _ref(a, b, True, True, r), K)
+    out2 = r.clone()
+    gemm_bf16(a, b, a_mn_major=True, b_mn_major=True, out=out2, addend=out2, force_split=split)
+    assert torch.equal(out, out2), "split-K must be deterministic"
+
+
+def test_gemm_strided_views(cuda_device):
+    """Operands and output that are column slices of wider buffers (pitch != width)."""
+    from gpt_from_scratch_b200.ops.gemm import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(11)
+    big_a = torch.randn((512, 1024), device=cuda_device, generator=g).bfloat16()
+    big_b = torch.randn((640, 1024), device=cuda_device, generator=g).bfloat16()
+    a = big_a[:, 256:768]
+    b = big_b[:, 128:640]
+    big_c = torch.zeros((512, 1280), device=cuda_device, dtype=torch.bfloat16)
+    out = big_c[:, 640:]
+    gemm_bf16(a, b, out=out)
+    _check(out, a.float() @ b.float().t(), 512)
+    assert big_c[:, :640].abs().max().item() == 0
