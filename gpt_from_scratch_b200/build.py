@@ -27,7 +27,6 @@ BUILD_DIR = PKG_DIR.parent / "build" / "gfs_b200"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
-    "--use_fast_math",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]

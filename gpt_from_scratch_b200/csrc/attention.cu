@@ -1,0 +1,773 @@
+// Causal flash attention forward and backward for sm_100a (head_dim 64 or 128, bf16).
+//
+// All matrix products run on tcgen05.mma with fp32 accumulators in TMEM; operands are
+// staged by TMA straight out of strided tensors (for the model: the packed
+// [S,B,3,nh,D] qkv buffer, so no permute/contiguous copies exist), and the output is
+// written directly in [S,B,nh*D] layout.
+//
+// Forward (one CTA per 128 query rows of one (batch, head); 6 warps):
+//   warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax (one thread per query row).
+//   Per 128-key block: S = Q K^T -> TMEM; softmax threads read their row with tcgen05.ld,
+//   keep the running max / sum, write P (bf16) into 128B-swizzled shared memory; the MMA
+//   warp then computes P V into a second TMEM tile that the softmax threads fold into
+//   their register-resident output row (rescaled by exp(m_old - m_new)). S, P and PV are
+//   double buffered so block j+1's QK^T overlaps block j's softmax.
+//
+// Backward (two kernels from one template, deterministic, no atomics):
+//   mode 0: one CTA per 128 keys   -> dK, dV, streaming 64-query tiles
+//   mode 1: one CTA per 128 queries -> dQ,     streaming 64-key tiles
+//   Both recompute P = exp(S*scale - LSE), dS = P * (dP - D) from two score MMAs
+//   (X = R1 T1^T, Y = R2 T2^T), write P / dS (bf16) to shared memory and accumulate
+//   dV += P^T dO, dK += dS^T Q (mode 0) or dQ += dS K (mode 1) in TMEM. The streamed tile
+//   is consumed twice from the same shared-memory bytes: K-major for the score MMA and
+//   MN-major for the gradient MMA.
+//
+// Reference counterparts: core/myFlashAttn.py:460-728 (_attn_fwd), :740-790 (pre-pass),
+// :805-1066 (_attn_bwd_LoopQ), :1079-1317 (_attn_bwd_LoopKV).
+#include <algorithm>
+
+#include "common.cuh"
+
+using namespace gfs;
+
+namespace {
+
+constexpr int ATT_THREADS = 192;
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+
+// A K-major [rows x K] (64-column blocks a_blk bytes apart), B K-major [N x K] (blocks b_blk apart).
+template <int KSTEPS>
+__device__ __forceinline__ void mma_kk(uint32_t d, uint32_t a, uint32_t a_blk, uint32_t b, uint32_t b_blk,
+                                       uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint64_t ad = umma_desc_sw128(a + (ks >> 2) * a_blk + (ks & 3) * 32, 16, 1024);
+    const uint64_t bd = umma_desc_sw128(b + (ks >> 2) * b_blk + (ks & 3) * 32, 16, 1024);
+    umma_ss(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+// A K-major; B MN-major: stored as [K rows x N] in 64-column blocks b_blk bytes apart
+// (each block: K rows of 128 B).
+template <int KSTEPS>
+__device__ __forceinline__ void mma_kmn(uint32_t d, uint32_t a, uint32_t a_blk, uint32_t b, uint32_t b_blk,
+                                        uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint64_t ad = umma_desc_sw128(a + (ks >> 2) * a_blk + (ks & 3) * 32, 16, 1024);
+    const uint64_t bd = umma_desc_sw128(b + ks * 2048, b_blk, 1024);
+    umma_ss(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Forward
+// ---------------------------------------------------------------------------
+struct FwdParams {
+  __nv_bfloat16* O;
+  long long o_ss, o_bs, o_hs;  // element strides: sequence, batch, head
+  float* lse;                  // [B, nh, S_pad]
+  int S, S_pad, B, nh;
+  float scale;
+  int causal;
+  uint32_t* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, const FwdParams p) {
+  constexpr int DB = D / 64;
+  constexpr int TILE_BYTES = DB * 16384;  // [128 x D] bf16 as DB swizzled blocks
+  constexpr int P_BYTES = 32768;          // [128 x 128] bf16 as 2 swizzled blocks
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Qs = smem;
+  uint8_t* Ks = Qs + TILE_BYTES;
+  uint8_t* Vs = Ks + 2 * TILE_BYTES;
+  uint8_t* Ps = Vs + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 7;
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_empty = bars + 11;
+  uint64_t* p_full = bars + 13;
+  uint64_t* p_empty = bars + 15;
+  uint64_t* o_full = bars + 17;
+  uint64_t* o_empty = bars + 19;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest (most key blocks) first
+  const int bh = blockIdx.y;
+  const int b = bh / p.nh;
+  const int h = bh % p.nh;
+  const int n_blocks_all = (p.S + 127) >> 7;
+  const int n_kv = p.causal ? min(qt + 1, n_blocks_all) : n_blocks_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&p_empty[i], 1);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) tma_load_4d(Qs + db * 16384, &tq, q_full, db * 64, qt * 128, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1u;
+        mbar_wait(&k_empty[st], par, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+        mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+          tma_load_4d(Ks + st * TILE_BYTES + db * 16384, &tk, &k_full[st], db * 64, j * 128, h, b);
+        mbar_wait(&v_empty[st], par, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+        mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+          tma_load_4d(Vs + st * TILE_BYTES + db * 16384, &tv, &v_full[st], db * 64, j * 128, h, b);
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
+      const uint32_t q_addr = smem_u32(Qs);
+      mbar_wait(q_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
+      auto issue_s = [&](int j) {
+        const int st = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        mbar_wait(&k_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
+        mbar_wait(&s_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        mma_kk<D / 16>(tmem_base + st * 128, q_addr, 16384, smem_u32(Ks + st * TILE_BYTES), 16384, idesc_s, false);
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+      };
+      issue_s(0);
+      for (int j = 0; j < n_kv; ++j) {
+        if (j + 1 < n_kv) issue_s(j + 1);
+        const int st = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        mbar_wait(&p_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
+        mbar_wait(&v_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
+        mbar_wait(&o_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        mma_kmn<8>(tmem_base + 256 + st * D, smem_u32(Ps + st * P_BYTES), 16384, smem_u32(Vs + st * TILE_BYTES),
+                   16384, idesc_o, false);
+        umma_commit(&o_full[st]);
+        umma_commit(&v_empty[st]);
+        umma_commit(&p_empty[st]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;       // row inside the query tile
+    const int row_g = qt * 128 + r;          // query position
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * LOG2E_F;
+    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+
+    auto fold_pv = [&](int j, float alpha) {
+      const int st = j & 1;
+      mbar_wait(&o_full[st], (j >> 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + lane_base + 256 + st * D + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c + e] = o[c + e] * alpha + __uint_as_float(v[e]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty[st]);
+    };
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      const uint32_t par = (j >> 1) & 1;
+      const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
+      mbar_wait(&s_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
+      tc_fence_after();
+      const uint32_t s_addr = tmem_base + lane_base + st * 128;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col_g = j * 128 + c + e;
+            const bool dead = (p.causal && col_g > row_g) || col_g >= p.S;
+            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(v[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // row with no live key so far
+      const float alpha = fast_exp2((m - m_use) * sl2);
+      const float moff = m_use * sl2;
+      mbar_wait(&p_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+      float rs = 0.f;
+      uint8_t* prow = Ps + st * P_BYTES + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c, v);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = fast_exp2(__uint_as_float(v[e]) * sl2 - moff);
+          if (need_mask) {
+            const int col_g = j * 128 + c + e;
+            if ((p.causal && col_g > row_g) || col_g >= p.S) x = 0.f;
+          }
+          pv[e] = x;
+          rs += x;
+        }
+        uint8_t* blk = prow + (c >> 6) * 16384;
+        const int chunk0 = (c & 63) >> 3;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(pv[8 * q4 + 0], pv[8 * q4 + 1]);
+          w.y = pack_bf16x2(pv[8 * q4 + 2], pv[8 * q4 + 3]);
+          w.z = pack_bf16x2(pv[8 * q4 + 4], pv[8 * q4 + 5]);
+          w.w = pack_bf16x2(pv[8 * q4 + 6], pv[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>(blk + ((((chunk0 + q4) ^ (r & 7)) & 7) << 4)) = w;
+        }
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[st]);
+        mbar_arrive(&p_full[st]);
+      }
+      if (j > 0) fold_pv(j - 1, alpha_prev);
+      alpha_prev = alpha;
+    }
+    fold_pv(n_kv - 1, alpha_prev);
+
+    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+    if (row_g < p.S) {
+      __nv_bfloat16* dst = p.O + row_g * p.o_ss + b * p.o_bs + h * p.o_hs;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint4 w;
+        w.x = pack_bf16x2(o[c + 0] * inv_l, o[c + 1] * inv_l);
+        w.y = pack_bf16x2(o[c + 2] * inv_l, o[c + 3] * inv_l);
+        w.z = pack_bf16x2(o[c + 4] * inv_l, o[c + 5] * inv_l);
+        w.w = pack_bf16x2(o[c + 6] * inv_l, o[c + 7] * inv_l);
+        *reinterpret_cast<uint4*>(dst + c) = w;
+      }
+    }
+    if (row_g < p.S_pad) {
+      const float mm = (m == -INFINITY) ? 0.f : m;
+      p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] = mm * p.scale + logf(fmaxf(l, 1e-37f));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Backward pre-pass: dvec[b,h,s] = sum_d dO[s,b,h,d] * O[s,b,h,d]; one warp per row.
+// ---------------------------------------------------------------------------
+__global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                 float* __restrict__ dvec, int S, int S_pad, int B, int nh, int D, long long do_ss,
+                                 long long do_bs, long long do_hs, long long o_ss, long long o_bs, long long o_hs) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = static_cast<long long>(S) * B * nh;
+  if (row >= total) return;
+  const int h = static_cast<int>(row % nh);
+  const int b = static_cast<int>((row / nh) % B);
+  const int s = static_cast<int>(row / (static_cast<long long>(nh) * B));
+  const __nv_bfloat16* a = dO + s * do_ss + b * do_bs + h * do_hs;
+  const __nv_bfloat16* c = O + s * o_ss + b * o_bs + h * o_hs;
+  float acc = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + d));
+    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(c + d));
+    acc += x.x * y.x + x.y * y.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dvec[(static_cast<size_t>(b) * nh + h) * S_pad + s] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// Backward main kernel
+// ---------------------------------------------------------------------------
+struct BwdParams {
+  __nv_bfloat16* out1;  // mode 0: dK, mode 1: dQ
+  __nv_bfloat16* out2;  // mode 0: dV
+  long long o1_ss, o1_bs, o1_hs;
+  long long o2_ss, o2_bs, o2_hs;
+  const float* lse;   // [B, nh, S_pad]
+  const float* dvec;  // [B, nh, S_pad]
+  int S, S_pad, B, nh;
+  float scale;
+  int causal;
+  uint32_t* status;
+};
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
+                 const __grid_constant__ CUtensorMap tt1, const __grid_constant__ CUtensorMap tt2,
+                 const BwdParams p) {
+  constexpr int DB = D / 64;
+  constexpr int R_BYTES = DB * 16384;  // resident [128 x D]
+  constexpr int T_BYTES = DB * 8192;   // streamed [64 x D]
+  constexpr int M_BYTES = 16384;       // [128 x 64] bf16
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t ACC1 = 256, ACC2 = 256 + D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* R1 = smem;
+  uint8_t* R2 = R1 + R_BYTES;
+  uint8_t* T1 = R2 + R_BYTES;        // 2 stages
+  uint8_t* T2 = T1 + 2 * T_BYTES;    // 2 stages
+  uint8_t* M1 = T2 + 2 * T_BYTES;    // 2 buffers
+  uint8_t* M2 = M1 + 2 * M_BYTES;    // 2 buffers
+  float* stats = reinterpret_cast<float*>(M2 + 2 * M_BYTES);  // mode 0: [2 stages][lse 64 | dvec 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + 1024);
+  uint64_t* r_full = bars;
+  uint64_t* t_full = bars + 1;
+  uint64_t* t_empty = bars + 3;
+  uint64_t* xy_full = bars + 5;
+  uint64_t* xy_empty = bars + 7;
+  uint64_t* m_full = bars + 9;
+  uint64_t* m_empty = bars + 11;
+  uint64_t* acc_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.nh;
+  const int h = bh % p.nh;
+  const int n_small = (p.S + 63) >> 6;  // number of 64-row streamed tiles in the sequence
+  // resident tile index and range of streamed tiles
+  int rt, t_begin, t_end;
+  if (MODE == 0) {
+    rt = blockIdx.x;  // key tile; the first ones have the most query tiles
+    t_begin = p.causal ? 2 * rt : 0;
+    t_end = n_small;
+  } else {
+    rt = gridDim.x - 1 - blockIdx.x;  // query tile; the last ones have the most key tiles
+    t_begin = 0;
+    t_end = p.causal ? min(n_small, 2 * rt + 2) : n_small;
+  }
+  const int n_t = t_end - t_begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&t_empty[i], 1);
+      mbar_init(&xy_full[i], 1);
+      mbar_init(&xy_empty[i], 4);
+      mbar_init(&m_full[i], 4);
+      mbar_init(&m_empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tr1);
+    tma_prefetch_desc(&tr2);
+    tma_prefetch_desc(&tt1);
+    tma_prefetch_desc(&tt2);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(r_full, 2 * R_BYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        tma_load_4d(R1 + db * 16384, &tr1, r_full, db * 64, rt * 128, h, b);
+        tma_load_4d(R2 + db * 16384, &tr2, r_full, db * 64, rt * 128, h, b);
+      }
+      for (int t = 0; t < n_t; ++t) {
+        const int st = t & 1;
+        const int ti = t_begin + t;
+        mbar_wait(&t_empty[st], ((t >> 1) & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+        mbar_arrive_expect_tx(&t_full[st], 2 * T_BYTES + (MODE == 0 ? 512 : 0));
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_4d(T1 + st * T_BYTES + db * 8192, &tt1, &t_full[st], db * 64, ti * 64, h, b);
+          tma_load_4d(T2 + st * T_BYTES + db * 8192, &tt2, &t_full[st], db * 64, ti * 64, h, b);
+        }
+        if (MODE == 0) {
+          const size_t off = static_cast<size_t>(bh) * p.S_pad + ti * 64;
+          bulk_load_1d(stats + st * 128, p.lse + off, 256, &t_full[st]);
+          bulk_load_1d(stats + st * 128 + 64, p.dvec + off, 256, &t_full[st]);
+        }
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_xy = umma_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, 0, 1);
+      const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
+      mbar_wait(r_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
+      auto issue_xy = [&](int t) {
+        const int st = t & 1;
+        const uint32_t par = (t >> 1) & 1;
+        mbar_wait(&t_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
+        mbar_wait(&xy_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        mma_kk<D / 16>(tmem_base + st * 64, r1, 16384, smem_u32(T1 + st * T_BYTES), 8192, idesc_xy, false);
+        mma_kk<D / 16>(tmem_base + 128 + st * 64, r2, 16384, smem_u32(T2 + st * T_BYTES), 8192, idesc_xy, false);
+        umma_commit(&xy_full[st]);
+      };
+      if (n_t > 0) issue_xy(0);
+      for (int t = 0; t < n_t; ++t) {
+        if (t + 1 < n_t) issue_xy(t + 1);
+        const int st = t & 1;
+        mbar_wait(&m_full[st], (t >> 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        if (MODE == 0) {
+          // dV += P^T dO ; dK += dS^T Q
+          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + st * M_BYTES), 0, smem_u32(T2 + st * T_BYTES), 8192, idesc_acc,
+                     t > 0);
+          mma_kmn<4>(tmem_base + ACC2, smem_u32(M2 + st * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
+                     t > 0);
+        } else {
+          // dQ += dS K
+          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + st * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
+                     t > 0);
+        }
+        umma_commit(&t_empty[st]);
+        umma_commit(&m_empty[st]);
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int row_g = rt * 128 + r;  // mode 0: key position, mode 1: query position
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * LOG2E_F;
+    float row_lse = 0.f, row_dvec = 0.f;
+    if (MODE == 1 && row_g < p.S_pad) {
+      row_lse = p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] * LOG2E_F;
+      row_dvec = p.dvec[static_cast<size_t>(bh) * p.S_pad + row_g];
+    }
+    for (int t = 0; t < n_t; ++t) {
+      const int st = t & 1;
+      const uint32_t par = (t >> 1) & 1;
+      const int ti = t_begin + t;
+      bool need_mask;
+      if (MODE == 0) need_mask = (p.causal && ti < 2 * rt + 2) || ((ti + 1) * 64 > p.S);
+      else need_mask = (p.causal && ti >= 2 * rt) || ((ti + 1) * 64 > p.S);
+      mbar_wait(&xy_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(&m_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+      tc_fence_after();
+      const float* st_lse = stats + st * 128;
+      const float* st_dv = st_lse + 64;
+      uint8_t* m1row = M1 + st * M_BYTES + r * 128;
+      uint8_t* m2row = M2 + st * M_BYTES + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t xv[32], yv[32];
+        tmem_ld_32x32(tmem_base + lane_base + st * 64 + c, xv);
+        tmem_ld_32x32(tmem_base + lane_base + 128 + st * 64 + c, yv);
+        tmem_ld_wait();
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c + e;
+          float lse_e, dv_e;
+          if (MODE == 0) {
+            lse_e = st_lse[col] * LOG2E_F;
+            dv_e = st_dv[col];
+          } else {
+            lse_e = row_lse;
+            dv_e = row_dvec;
+          }
+          float pe = fast_exp2(__uint_as_float(xv[e]) * sl2 - lse_e);
+          float de = pe * (__uint_as_float(yv[e]) - dv_e);
+          if (need_mask) {
+            const int col_g = ti * 64 + col;
+            bool dead;
+            if (MODE == 0) dead = (p.causal && col_g < row_g) || col_g >= p.S;   // col = query, row = key
+            else dead = (p.causal && col_g > row_g) || col_g >= p.S;             // col = key, row = query
+            if (dead) {
+              pe = 0.f;
+              de = 0.f;
+            }
+          }
+          pv[e] = pe;
+          dsv[e] = de;
+        }
+        const int chunk0 = c >> 3;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int off = (((chunk0 + q4) ^ (r & 7)) & 7) << 4;
+          uint4 w;
+          if (MODE == 0) {
+            w.x = pack_bf16x2(pv[8 * q4 + 0], pv[8 * q4 + 1]);
+            w.y = pack_bf16x2(pv[8 * q4 + 2], pv[8 * q4 + 3]);
+            w.z = pack_bf16x2(pv[8 * q4 + 4], pv[8 * q4 + 5]);
+            w.w = pack_bf16x2(pv[8 * q4 + 6], pv[8 * q4 + 7]);
+            *reinterpret_cast<uint4*>(m1row + off) = w;
+          }
+          w.x = pack_bf16x2(dsv[8 * q4 + 0], dsv[8 * q4 + 1]);
+          w.y = pack_bf16x2(dsv[8 * q4 + 2], dsv[8 * q4 + 3]);
+          w.z = pack_bf16x2(dsv[8 * q4 + 4], dsv[8 * q4 + 5]);
+          w.w = pack_bf16x2(dsv[8 * q4 + 6], dsv[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>((MODE == 0 ? m2row : m1row) + off) = w;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&xy_empty[st]);
+        mbar_arrive(&m_full[st]);
+      }
+    }
+    // epilogue: accumulators -> global
+    mbar_wait(acc_full, 0, wctx, STATUS_TIMEOUT_TMEM_FULL);
+    tc_fence_after();
+    const bool live = row_g < p.S;
+    __nv_bfloat16* d1 = p.out1 + row_g * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
+    __nv_bfloat16* d2 = (MODE == 0) ? p.out2 + row_g * p.o2_ss + b * p.o2_bs + h * p.o2_hs : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < D; c += 32) {
+      uint32_t v[32];
+      // mode 0: ACC2 holds dK (scaled), ACC1 holds dV; mode 1: ACC1 holds dQ (scaled)
+      tmem_ld_32x32(tmem_base + lane_base + (MODE == 0 ? ACC2 : ACC1) + c, v);
+      tmem_ld_wait();
+      if (live) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * p.scale, __uint_as_float(v[8 * q4 + 1]) * p.scale);
+          w.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * p.scale, __uint_as_float(v[8 * q4 + 3]) * p.scale);
+          w.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * p.scale, __uint_as_float(v[8 * q4 + 5]) * p.scale);
+          w.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * p.scale, __uint_as_float(v[8 * q4 + 7]) * p.scale);
+          *reinterpret_cast<uint4*>(d1 + c + 8 * q4) = w;
+        }
+      }
+      if (MODE == 0) {
+        tmem_ld_32x32(tmem_base + lane_base + ACC1 + c, v);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]), __uint_as_float(v[8 * q4 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+            *reinterpret_cast<uint4*>(d2 + c + 8 * q4) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+const CUtensorMap* make_map(const void* base, int D, int S, int nh, int B, const long long* st, uint32_t box_rows) {
+  // st = {seq, batch, head} element strides
+  uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(nh),
+                      static_cast<uint64_t>(B)};
+  uint64_t strides[4] = {2, static_cast<uint64_t>(st[0]) * 2, static_cast<uint64_t>(st[2]) * 2,
+                         static_cast<uint64_t>(st[1]) * 2};
+  uint32_t box[4] = {64, box_rows, 1, 1};
+  return gfs_host::tmap_nd_cached(base, 4, dims, strides, box);
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -10;
+}
+
+bool strides_ok(const long long* st, int n) {
+  for (int i = 0; i < n; ++i)
+    if (st[i] & 7) return false;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+// strides: 12 element strides {q_seq,q_batch,q_head, k_.., v_.., o_..}. lse: fp32 [B, nh, S_pad],
+// S_pad = S rounded up to a multiple of 128.
+int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* lse, int S, int B, int nh, int D,
+                  const long long* strides, float scale, int causal, void* stream_) {
+  if (D != 64 && D != 128) return -1;
+  if (!strides_ok(strides, 12)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return -2;
+  if (S <= 0 || B <= 0 || nh <= 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const CUtensorMap* tq = make_map(q, D, S, nh, B, strides + 0, 128);
+  const CUtensorMap* tk = make_map(k, D, S, nh, B, strides + 3, 128);
+  const CUtensorMap* tv = make_map(v, D, S, nh, B, strides + 6, 128);
+  if (!tq || !tk || !tv) return -3;
+  FwdParams p;
+  p.O = static_cast<__nv_bfloat16*>(o);
+  p.o_ss = strides[9]; p.o_bs = strides[10]; p.o_hs = strides[11];
+  p.lse = static_cast<float*>(lse);
+  p.S = S; p.S_pad = ((S + 127) / 128) * 128; p.B = B; p.nh = nh;
+  p.scale = scale; p.causal = causal;
+  p.status = gfs_host::status_words();
+  const dim3 grid((S + 127) / 128, B * nh);
+  const int smem = (D / 64) * 16384 * 5 + 65536 + 256 + 1024;
+  static bool set64 = false, set128 = false;
+  if (D == 64) {
+    if (!set64) { if (set_smem(flash_fwd_kernel<64>, smem)) return -10; set64 = true; }
+    flash_fwd_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+  } else {
+    if (!set128) { if (set_smem(flash_fwd_kernel<128>, smem)) return -10; set128 = true; }
+    flash_fwd_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// strides: 24 element strides for {q, k, v, o, do, dq, dk, dv} x {seq, batch, head}.
+// lse, dvec: fp32 [B, nh, S_pad]; dvec is scratch written by the pre-pass.
+int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const void* lse,
+                  void* dvec, void* dq, void* dk, void* dv, int S, int B, int nh, int D, const long long* strides,
+                  float scale, int causal, void* stream_) {
+  if (D != 64 && D != 128) return -1;
+  if (!strides_ok(strides, 24)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+       reinterpret_cast<uintptr_t>(dv)) & 15)
+    return -2;
+  if (S <= 0 || B <= 0 || nh <= 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int S_pad = ((S + 127) / 128) * 128;
+  const long long *sq = strides, *sk = strides + 3, *sv = strides + 6, *so = strides + 9, *sdo = strides + 12,
+                  *sdq = strides + 15, *sdk = strides + 18, *sdv = strides + 21;
+  {
+    const long long rows = static_cast<long long>(S) * B * nh;
+    const int warps = 8;
+    attn_dvec_kernel<<<static_cast<int>((rows + warps - 1) / warps), warps * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec), S,
+        S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+    if (cudaGetLastError() != cudaSuccess) return -11;
+  }
+  const CUtensorMap* q128 = make_map(q, D, S, nh, B, sq, 128);
+  const CUtensorMap* k128 = make_map(k, D, S, nh, B, sk, 128);
+  const CUtensorMap* v128 = make_map(v, D, S, nh, B, sv, 128);
+  const CUtensorMap* do128 = make_map(dO, D, S, nh, B, sdo, 128);
+  const CUtensorMap* q64 = make_map(q, D, S, nh, B, sq, 64);
+  const CUtensorMap* k64 = make_map(k, D, S, nh, B, sk, 64);
+  const CUtensorMap* v64 = make_map(v, D, S, nh, B, sv, 64);
+  const CUtensorMap* do64 = make_map(dO, D, S, nh, B, sdo, 64);
+  if (!q128 || !k128 || !v128 || !do128 || !q64 || !k64 || !v64 || !do64) return -3;
+  BwdParams p;
+  p.lse = static_cast<const float*>(lse);
+  p.dvec = static_cast<const float*>(dvec);
+  p.S = S; p.S_pad = S_pad; p.B = B; p.nh = nh; p.scale = scale; p.causal = causal;
+  p.status = gfs_host::status_words();
+  const dim3 grid((S + 127) / 128, B * nh);
+  const int smem = 2 * (D / 64) * 16384 + 4 * (D / 64) * 8192 + 4 * 16384 + 1024 + 256 + 1024;
+  static bool set_done[4] = {false, false, false, false};
+  // mode 0: dK, dV
+  BwdParams p0 = p;
+  p0.out1 = static_cast<__nv_bfloat16*>(dk); p0.o1_ss = sdk[0]; p0.o1_bs = sdk[1]; p0.o1_hs = sdk[2];
+  p0.out2 = static_cast<__nv_bfloat16*>(dv); p0.o2_ss = sdv[0]; p0.o2_bs = sdv[1]; p0.o2_hs = sdv[2];
+  BwdParams p1 = p;
+  p1.out1 = static_cast<__nv_bfloat16*>(dq); p1.o1_ss = sdq[0]; p1.o1_bs = sdq[1]; p1.o1_hs = sdq[2];
+  p1.out2 = nullptr; p1.o2_ss = p1.o2_bs = p1.o2_hs = 0;
+  if (D == 64) {
+    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0>, smem)) return -10; set_done[0] = true; }
+    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1>, smem)) return -10; set_done[1] = true; }
+    flash_bwd_kernel<64, 0><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (cudaGetLastError() != cudaSuccess) return -12;
+    flash_bwd_kernel<64, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+  } else {
+    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0>, smem)) return -10; set_done[2] = true; }
+    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1>, smem)) return -10; set_done[3] = true; }
+    flash_bwd_kernel<128, 0><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (cudaGetLastError() != cudaSuccess) return -12;
+    flash_bwd_kernel<128, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -13;
+}
+
+}  // extern "C"

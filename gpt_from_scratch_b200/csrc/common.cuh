@@ -127,6 +127,13 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 1-D bulk copy global -> shared of this CTA (both 16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // Generic-proxy writes to shared memory that the async proxy (UMMA / TMA) will read.
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -240,6 +247,11 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
   return __bfloat1622float2(v);
 }
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf) = +0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -274,6 +286,8 @@ int encode_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_
 // Cached 2-D variant: tensor [rows, cols] with row pitch ld (elements), box [box_rows, 64 cols].
 const CUtensorMap* tmap_2d_cached(const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
                                   uint32_t box_rows, uint32_t box_cols);
+const CUtensorMap* tmap_nd_cached(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                                  const uint32_t* box);
 // Device status words owned by the library (allocated on first use per device).
 uint32_t* status_words();
 int sm_count();

@@ -101,9 +101,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int H, int rows_per_cta) {
-  extern __shared__ float red[];  // [NB_WARPS][H]
+  extern __shared__ float red[];  // [warps][H]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
   const int nvec = H >> 3;
   const int r0 = blockIdx.x * rows_per_cta;
   const int r1 = min(rows, r0 + rows_per_cta);
@@ -111,7 +112,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int i = lane; i < H; i += 32) my_red[i] = 0.f;
   __syncwarp();
 
-  for (int row = r0 + warp; row < r1; row += NB_WARPS) {
+  for (int row = r0 + warp; row < r1; row += nwarps) {
     const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
     const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
     __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
@@ -150,8 +151,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   float* outp = dw_partial + static_cast<size_t>(blockIdx.x) * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float s = 0.f;
-#pragma unroll
-    for (int wv = 0; wv < NB_WARPS; ++wv) s += red[static_cast<size_t>(wv) * H + i];
+    for (int wv = 0; wv < nwarps; ++wv) s += red[static_cast<size_t>(wv) * H + i];
     outp[i] = s;
   }
 }
@@ -335,7 +335,9 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int parts = gfs_rmsnorm_bwd_parts(rows);
   const int rows_per_cta = (rows + parts - 1) / parts;
-  const size_t smem = static_cast<size_t>(NB_WARPS) * H * sizeof(float);
+  int warps = NB_WARPS;
+  while (warps > 1 && static_cast<size_t>(warps) * H * sizeof(float) > 200 * 1024) warps >>= 1;
+  const size_t smem = static_cast<size_t>(warps) * H * sizeof(float);
   if (smem > 200 * 1024) return -1;
   static int smem_set = 0;
   if (smem > 48 * 1024 && smem_set < static_cast<int>(smem)) {
@@ -344,7 +346,7 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
       return -10;
     smem_set = 200 * 1024;
   }
-  rmsnorm_bwd_kernel<<<parts, NB_WARPS * 32, smem, stream>>>(
+  rmsnorm_bwd_kernel<<<parts, warps * 32, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
       static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), static_cast<float*>(partial), rows, H,

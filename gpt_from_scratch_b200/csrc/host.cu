@@ -96,6 +96,53 @@ const CUtensorMap* tmap_2d_cached(const void* base, uint64_t rows, uint64_t cols
   return m;
 }
 
+struct KeyND {
+  const void* base;
+  int rank;
+  uint64_t dims[4];
+  uint64_t strides[4];
+  uint32_t box[4];
+  bool operator==(const KeyND& o) const { return memcmp(this, &o, sizeof(KeyND)) == 0; }
+};
+struct KeyNDHash {
+  size_t operator()(const KeyND& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    size_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(KeyND) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+    return h;
+  }
+};
+
+// Cached tensor map of rank <= 4 (dims/strides innermost first, strides in bytes).
+const CUtensorMap* tmap_nd_cached(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                                  const uint32_t* box) {
+  static std::mutex mu;
+  static std::unordered_map<KeyND, CUtensorMap*, KeyNDHash> cache;
+  KeyND key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.strides[i] = strides_bytes[i];
+    key.box[i] = box[i];
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 8192) {
+    for (auto& kv : cache) delete kv.second;
+    cache.clear();
+  }
+  CUtensorMap* m = new CUtensorMap;
+  if (encode_tmap_bf16(m, base, rank, dims, strides_bytes, box) != 0) {
+    delete m;
+    return nullptr;
+  }
+  cache.emplace(key, m);
+  return m;
+}
+
 uint32_t* status_words() {
   static std::mutex mu;
   static uint32_t* per_dev[64] = {nullptr};

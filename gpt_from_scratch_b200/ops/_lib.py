@@ -50,6 +50,8 @@ def available() -> bool:
 
 def _declare(lib: ctypes.CDLL) -> None:
     vp, i, sz, f, i64 = c_void_p, c_int, c_size_t, c_float, c_int64
+    lp = POINTER(ctypes.c_longlong)
+    cl = ctypes.c_long
     sigs = {
         "gfs_read_status": ([POINTER(c_uint32), i], i),
         "gfs_sm_count": ([], i),
@@ -57,19 +59,22 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_gemm_bf16": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, vp, sz, i, vp], i),
         "gfs_gemm_bf16_launches": ([i, i, i, sz], i),
         "gfs_rmsnorm_fwd": ([vp, vp, vp, vp, i, i, f, vp], i),
-        "gfs_rmsnorm_bwd": ([vp, vp, vp, vp, vp, vp, vp, i, i, i, vp], i),
-        "gfs_rope_qk": ([vp, vp, vp, i, i, i, i, i, i, vp], i),
+        "gfs_rmsnorm_bwd_parts": ([i], i),
+        "gfs_rmsnorm_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp], i),
+        "gfs_rope": ([vp, vp, vp, i, i, i, i, i, cl, i, i, vp], i),
         "gfs_swiglu_fwd": ([vp, vp, i, i, vp], i),
         "gfs_swiglu_bwd": ([vp, vp, vp, i, i, vp], i),
-        "gfs_ce_fwd": ([vp, vp, vp, vp, vp, i, i, i, i, vp], i),
-        "gfs_ce_bwd": ([vp, vp, vp, vp, i, i, i, i, f, vp], i),
-        "gfs_embedding_fwd": ([vp, vp, vp, i, i, i, i, i, i, vp], i),
-        "gfs_embedding_bwd": ([vp, vp, vp, vp, vp, i, i, i, i, i, i, vp], i),
-        "gfs_adamw_step": ([vp, vp, vp, vp, vp, vp, i64, f, f, f, f, f, f, f, f, vp, i, vp], i),
-        "gfs_sumsq_bf16": ([vp, i64, vp, i, vp], i),
-        "gfs_flash_fwd": ([vp, vp, vp, i, i, i, i, f, vp], i),
-        "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp], i),
+        "gfs_embedding_fwd": ([vp, vp, vp, i, i, i, i, i, i, i, vp], i),
+        "gfs_embedding_bwd": ([vp, vp, vp, vp, i, i, i, i, vp], i),
+        "gfs_ce_fwd": ([vp, vp, vp, vp, vp, i, i, cl, i, i, vp], i),
+        "gfs_ce_combine": ([vp, vp, vp, i, i, vp], i),
+        "gfs_ce_bwd": ([vp, vp, vp, vp, i, i, cl, i, vp], i),
+        "gfs_sumsq_scratch_bytes": ([], i),
+        "gfs_sumsq_bf16": ([vp, i64, vp, vp, vp], i),
+        "gfs_adamw_step": ([vp, vp, vp, vp, vp, i64, vp, vp, f, f, f, f, f, f, f, f, f, vp], i),
         "gfs_wait_probe": ([vp, i64, vp], i),
+        "gfs_flash_fwd": ([vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
+        "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
     }
     for name, (argtypes, restype) in sigs.items():
         fn = getattr(lib, name, None)

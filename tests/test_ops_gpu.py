@@ -1,0 +1,136 @@
+"""Numerics of the single-GPU kernels against fp32 PyTorch references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, atol, rtol=0.0, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol)
+    assert not bad.any(), f"{what}: max err {err.max().item():.4g} (tol {atol}), {int(bad.sum())} bad of {a.numel()}"
+
+
+@pytest.mark.parametrize("B,nh,S,D", [(2, 2, 128, 64), (1, 3, 256, 64), (2, 2, 512, 128), (1, 2, 384, 128),
+                                      (4, 12, 1024, 64)])
+def test_flash_attention_fwd_bwd(cuda_device, B, nh, S, D):
+    from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
+    g = torch.Generator(device="cuda").manual_seed(S + D)
+    q, k, v = (torch.randn(B, nh, S, D, device=cuda_device, generator=g).bfloat16().requires_grad_() for _ in range(3))
+    do = torch.randn(B, nh, S, D, device=cuda_device, generator=g).bfloat16()
+    o = apply_flash_attn(q, k, v, True)
+    o.backward(do)
+    dq, dk, dv = q.grad.clone(), k.grad.clone(), v.grad.clone()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = attention_reference(qf, kf, vf, True)
+    of.backward(do.float())
+    # the reference repository's own tolerances: 1e-2 forward, 5e-2 gradients
+    _close(o, of, 1e-2, what="O")
+    _close(dq, qf.grad, 5e-2, what="dQ")
+    _close(dk, kf.grad, 5e-2, what="dK")
+    _close(dv, vf.grad, 5e-2, what="dV")
+    # and a tighter relative check on the aggregate error
+    for name, a, b in (("O", o, of), ("dQ", dq, qf.grad), ("dK", dk, kf.grad), ("dV", dv, vf.grad)):
+        rel = (a.float() - b).norm() / (b.norm() + 1e-12)
+        assert rel < 2e-2, f"{name}: relative error {rel:.4g}"
+
+
+def test_flash_attention_noncausal_and_ragged(cuda_device):
+    from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for S, causal in ((192, True), (320, False), (64, True)):
+        q, k, v = (torch.randn(1, 2, S, 64, device=cuda_device, generator=g).bfloat16().requires_grad_()
+                   for _ in range(3))
+        do = torch.randn(1, 2, S, 64, device=cuda_device, generator=g).bfloat16()
+        o = apply_flash_attn(q, k, v, causal)
+        o.backward(do)
+        qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+        of = attention_reference(qf, kf, vf, causal)
+        of.backward(do.float())
+        _close(o, of, 1e-2, what=f"O S={S}")
+        _close(q.grad, qf.grad, 5e-2, what=f"dQ S={S}")
+        _close(k.grad, kf.grad, 5e-2, what=f"dK S={S}")
+        _close(v.grad, vf.grad, 5e-2, what=f"dV S={S}")
+
+
+@pytest.mark.parametrize("S,B,nh,D", [(256, 2, 4, 64), (128, 1, 2, 128)])
+def test_fused_rope_attention_matches_composition(cuda_device, S, B, nh, D):
+    from gpt_from_scratch_b200.ops.attention import attention_reference, fused_rope_attention
+    from gpt_from_scratch_b200.ops.rope import rope_reference
+    g = torch.Generator(device="cuda").manual_seed(9)
+    qkv = torch.randn(S * B, 3 * nh * D, device=cuda_device, generator=g).bfloat16()
+    pos = torch.arange(S, device=cuda_device, dtype=torch.float32)
+    freqs = 10000.0 ** (-torch.arange(0, D, 2, device=cuda_device, dtype=torch.float32) / D)
+    ang = pos[:, None] * freqs[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    x = qkv.clone().requires_grad_()
+    do = torch.randn(S * B, nh * D, device=cuda_device, generator=g).bfloat16()
+    out = fused_rope_attention(x * 1, cos, sin, S, B, nh, D)
+    out.backward(do)
+    xf = qkv.float().requires_grad_()
+    q, k, v = xf.view(S, B, 3, nh, D).unbind(2)
+    qr, kr = rope_reference(q, cos, sin), rope_reference(k, cos, sin)
+    of = attention_reference(qr.permute(1, 2, 0, 3), kr.permute(1, 2, 0, 3), v.permute(1, 2, 0, 3), True)
+    of = of.permute(2, 0, 1, 3).reshape(S * B, nh * D)
+    of.backward(do.float())
+    _close(out, of, 1.5e-2, what="fused out")
+    _close(x.grad, xf.grad, 6e-2, what="fused dqkv")
+    rel = (x.grad.float() - xf.grad).norm() / xf.grad.norm()
+    assert rel < 2e-2, rel
+
+
+def test_rope_fwd_bwd(cuda_device):
+    from gpt_from_scratch_b200.ops.rope import apply_rope, rope_reference
+    S, B, nh, D = 96, 3, 5, 64
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(S, B, nh, D, device=cuda_device, generator=g).bfloat16().requires_grad_()
+    ang = torch.rand(S, D // 2, device=cuda_device, generator=g) * 6.28
+    cos, sin = ang.cos(), ang.sin()
+    y = apply_rope(x, cos, sin)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xf = x.detach().float().requires_grad_()
+    yf = rope_reference(xf, cos, sin)
+    yf.backward(gy.float())
+    _close(y, yf, 2e-2, what="rope y")
+    _close(x.grad, xf.grad, 2e-2, what="rope dx")
+    # strided input (an unbind view of a packed buffer) must give the same answer
+    packed = torch.randn(S, B, 3, nh, D, device=cuda_device, generator=g).bfloat16()
+    q = packed[:, :, 0]
+    _close(apply_rope(q, cos, sin), rope_reference(q.float(), cos, sin), 2e-2, what="rope strided")
+
+
+@pytest.mark.parametrize("rows,H", [(64, 768), (1000, 2048), (33, 4096), (17, 8192), (4096, 768)])
+def test_rmsnorm_fwd_bwd(cuda_device, rows, H):
+    from gpt_from_scratch_b200.ops.rmsnorm import rmsnorm, rmsnorm_reference
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = (torch.randn(rows, H, device=cuda_device, generator=g) * 2).bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device=cuda_device, generator=g)).bfloat16().requires_grad_()
+    dy = torch.randn(rows, H, device=cuda_device, generator=g).bfloat16()
+    y = rmsnorm(x, w, 1e-5)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = rmsnorm_reference(xf, wf, 1e-5)
+    yf.backward(dy.float())
+    _close(y, yf, 3e-2, 1e-2, what="rmsnorm y")
+    _close(x.grad, xf.grad, 3e-2, 2e-2, what="rmsnorm dx")
+    rel = (w.grad.float() - wf.grad).norm() / wf.grad.norm()
+    assert rel < 1e-2, f"rmsnorm dw rel {rel}"
+
+
+def test_swiglu_fwd_bwd(cuda_device):
+    from gpt_from_scratch_b200.ops.swiglu import swiglu, swiglu_reference
+    g = torch.Generator(device="cuda").manual_seed(4)
+    gu = torch.randn(300, 2 * 1408, device=cuda_device, generator=g).bfloat16().requires_grad_()
+    da = torch.randn(300, 1408, device=cuda_device, generator=g).bfloat16()
+    a = swiglu(gu)
+    a.backward(da)
+    gf = gu.detach().float().requires_grad_()
+    af = swiglu_reference(gf)
+    af.backward(da.float())
+    _close(a, af, 2e-2, 1e-2, what="swiglu")
+    _close(gu.grad, gf.grad, 2e-2, 1e-2, what="swiglu grad")
