@@ -88,13 +88,12 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // ---------------------------------------------------------------------------
-// RMSNorm backward. Each CTA owns a contiguous block of rows; every lane keeps the
-// weight-gradient partial of its own columns in registers across the rows of its
-// warp, so dw needs no atomics: partials [gridDim.x, H] are summed by a second kernel.
+// RMSNorm backward. Each CTA owns a contiguous block of rows; every warp keeps the
+// weight-gradient partial of the rows it handled in its own shared-memory row, so dw
+// needs no atomics: per-CTA partials [gridDim.x, H] are summed by a second kernel.
 //   g = dy * w;  dx = rstd * g - x * rstd^3 * mean(g * x)  (+ dres);  dw += dy * bf16(x * rstd)
 // ---------------------------------------------------------------------------
 constexpr int NB_WARPS = 8;
-constexpr int NB_MAXV = 4;  // register-cached column vectors per lane (H <= 1024); more are handled in column slabs
 
 __global__ void __launch_bounds__(NB_WARPS * 32)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,

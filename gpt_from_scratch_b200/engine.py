@@ -1,0 +1,54 @@
+"""Training engine: the public entry point that builds the model + distributed optimizer
+and runs one optimisation step. ``train.py`` and ``bench.py`` both drive this class.
+
+The step is the reference's loop body (train.py:172-187): ``zero_grad -> forward ->
+vocab-parallel cross entropy -> mean -> backward -> optimizer.step``; the loss stays on the
+device (the reference calls ``.item()`` every step, train.py:190)."""
+from __future__ import annotations
+
+import torch
+
+from .config import GPTConfig
+from .models.gpt import GPTModel
+from .optimizer import DistributedOptimizer
+from .parallel import parallel_state as ps
+from .parallel.loss import vocab_parallel_cross_entropy
+
+
+class TrainEngine:
+    def __init__(self, config: GPTConfig, *, lr: float = 3e-4, weight_decay: float = 0.1,
+                 betas: tuple[float, float] = (0.9, 0.95), clip_grad: float = 1.0,
+                 dtype: torch.dtype = torch.bfloat16, grad_reduce: str = "sum", seed: int | None = None):
+        if not ps.model_parallel_is_initialized():
+            ps.initialize_parallel_state(1)
+        if seed is not None:
+            ps.set_seed(seed)
+        self.config = config
+        self.device = ps.get_device()
+        self.model = GPTModel(config)
+        self.optimizer = DistributedOptimizer(
+            self.model, torch.optim.AdamW,
+            {"lr": lr, "weight_decay": weight_decay, "betas": betas},
+            clip_grad=clip_grad, dtype=dtype, grad_reduce=grad_reduce,
+            reference_quirks=getattr(config, "reference_quirks", False))
+        self.model.train()
+        self.steps_done = 0
+
+    @property
+    def params_per_tp_rank(self) -> int:
+        return sum(p.numel() for p in self.model.parameters())
+
+    def forward_loss(self, inputs: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """inputs, labels: ``[B, S]`` token ids on the engine's device -> mean loss (scalar)."""
+        logits = self.model(inputs)                               # [S, B, V/P]
+        labels_t = labels.transpose(0, 1).contiguous()            # [S, B]
+        loss = vocab_parallel_cross_entropy(logits, labels_t)     # [S, B]
+        return loss.mean()
+
+    def train_step(self, inputs: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        self.optimizer.zero_grad()
+        loss = self.forward_loss(inputs, labels)
+        loss.backward()
+        self.optimizer.step()
+        self.steps_done += 1
+        return loss.detach()

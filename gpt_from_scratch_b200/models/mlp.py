@@ -1,0 +1,29 @@
+"""SwiGLU feed-forward block. Reference: core/mlp.py:9-33 (gate_up_proj column-parallel
+``H -> 2I`` whose local rows are ``[gate_local | up_local]``, ``silu(gate) * up``,
+down_proj row-parallel ``I -> H``)."""
+from __future__ import annotations
+
+import torch.nn as nn
+
+from ..ops.swiglu import swiglu
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
+from .init import get_init_method
+
+
+class ParallelMLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.intermediate_size = getattr(config, "intermediate_size", None) or 4 * config.hidden_size
+        bias = getattr(config, "bias", False)
+        init_method = get_init_method(config)
+        self.gate_up_proj = ColumnParallelLinear(self.hidden_size, 2 * self.intermediate_size, bias=bias,
+                                                 init_method=init_method)
+        self.down_proj = RowParallelLinear(self.intermediate_size, self.hidden_size, bias=bias,
+                                           init_method=init_method)
+
+    def forward(self, hidden_states, residual=None):
+        gu = self.gate_up_proj(hidden_states)              # [S, B, 2I/P]
+        S, B, W = gu.shape
+        act = swiglu(gu.reshape(S * B, W)).view(S, B, W // 2)
+        return self.down_proj(act, residual)               # [S/P, B, H]

@@ -1,0 +1,278 @@
+"""DistributedOptimizer: bf16 compute with fp32 master weights, optimizer state sharded
+over the data-parallel group (ZeRO-1 style).
+
+Semantics follow the reference (core/optimizer.py:18-112):
+
+* every trainable parameter, in module registration order, becomes a view into one flat
+  ``param_buffer``; every ``.grad`` a view into one flat ``grad_buffer`` (same dtype);
+* the flat length is padded so the DP size divides it; DP rank ``r`` owns the contiguous
+  slice ``[r*shard_size, (r+1)*shard_size)`` and keeps an fp32 master copy plus the AdamW
+  moments for that slice only;
+* ``step()`` = reduce-scatter(SUM) of the gradients over DP -> clip by the global norm ->
+  AdamW on the fp32 shard -> all-gather of the bf16-rounded parameters;
+* ``state_dict()`` / ``load_state_dict()`` pass through to the inner ``torch.optim.AdamW``
+  (which here also carries the state used by the fused kernels).
+
+Differences that are deliberate:
+
+* On CUDA/bf16 the clip + AdamW + cast is one kernel and the clip decision stays on the
+  device (the reference synchronises the host on ``if norm > clip``, core/optimizer.py:103).
+* ``zero_grad()`` does not memset: backward kernels overwrite each gradient slice on first
+  use in a step (see ``ops/grad_sink.py``).
+* The gradient norm is global over TP x DP with replicated parameters counted once, and
+  the gradients of TP-replicated parameters (the RMSNorm weights, which only see their
+  sequence shard) are summed over the TP group before the step. ``reference_quirks=True``
+  restores the reference's per-TP-rank norm and missing TP reduction.
+* ``grad_reduce="mean"`` divides the DP-summed gradient by the DP size (the reference sums).
+* With ``comm_impl == "fused"`` and DP > 1 the reduce-scatter, norm partial, AdamW and
+  parameter all-gather run as peer-memory kernels (``parallel/fused_comm.py``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from .ops import adam as adam_ops
+from .parallel import mappings
+from .parallel import parallel_state as ps
+
+
+class DistributedOptimizer:
+    def __init__(self, model: torch.nn.Module, optimizer_cls=torch.optim.AdamW, optimizer_kwargs: dict | None = None,
+                 clip_grad: float = 1.0, dtype: torch.dtype = torch.bfloat16, grad_reduce: str = "sum",
+                 reference_quirks: bool = False, fused: bool | None = None):
+        self.model = model
+        self.optimizer_kwargs = dict(optimizer_kwargs or {})
+        self.dp_group = ps.get_data_parallel_group()
+        self.dp_rank = ps.get_data_parallel_group_rank()
+        self.dp_world_size = ps.get_data_parallel_world_size()
+        self.tp_world_size = ps.get_tensor_model_parallel_world_size()
+        self.clip_grad = clip_grad
+        self.dtype = dtype
+        self.grad_reduce = grad_reduce
+        self.reference_quirks = reference_quirks
+        assert grad_reduce in ("sum", "mean")
+
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        if not self.params:
+            raise ValueError("model has no trainable parameters")
+        device = self.params[0].device
+        self.device = device
+        total_numel = sum(p.numel() for p in self.params)
+        # pad so every DP shard is a whole number of 16-byte vectors (the reference pads to a
+        # multiple of the DP size; the extra zeros are inert)
+        align = self.dp_world_size * 8
+        self.padding_size = (align - total_numel % align) % align
+        self.padded_numel = total_numel + self.padding_size
+        self.shard_size = self.padded_numel // self.dp_world_size
+        self.total_numel = total_numel
+
+        self.use_fused_kernels = (device.type == "cuda" and dtype == torch.bfloat16) if fused is None else fused
+        self.use_fused_comm = (self.use_fused_kernels and self.dp_world_size > 1 and ps.get_comm_impl() == "fused")
+
+        if self.use_fused_comm:
+            from .parallel import fused_comm
+            self._dp_comm = fused_comm.DataParallelComm(self.padded_numel, self.shard_size, device)
+            self.param_buffer = self._dp_comm.param_buffer
+            self.grad_buffer = self._dp_comm.grad_buffer
+        else:
+            self._dp_comm = None
+            self.param_buffer = torch.zeros(self.padded_numel, dtype=dtype, device=device)
+            self.grad_buffer = torch.zeros(self.padded_numel, dtype=dtype, device=device)
+
+        # re-point parameters and gradients into the flat buffers
+        self.param_offsets: list[int] = []
+        offset = 0
+        replicated_ranges = []
+        for p in self.params:
+            n = p.numel()
+            self.param_buffer[offset:offset + n].copy_(p.data.reshape(-1))
+            p.data = self.param_buffer[offset:offset + n].view(p.shape)
+            p.grad = self.grad_buffer[offset:offset + n].view(p.shape)
+            p._grad_sink_ok = bool(self.use_fused_kernels)
+            p._grad_fresh = False
+            if getattr(p, "tp_replicated", False):
+                replicated_ranges.append((offset, offset + n))
+            self.param_offsets.append(offset)
+            offset += n
+
+        s0 = self.shard_size * self.dp_rank
+        s1 = s0 + self.shard_size
+        self.shard_start, self.shard_end = s0, s1
+        self.fp32_master_shard = (self.param_buffer[s0:s1].to(torch.float32).clone().detach().requires_grad_(True))
+        self.optimizer = optimizer_cls([self.fp32_master_shard], **self.optimizer_kwargs)
+        if self.dp_world_size > 1 and not self.use_fused_comm:
+            self.reduced_grad_shard = torch.zeros(self.shard_size, dtype=dtype, device=device)
+        else:
+            self.reduced_grad_shard = self.grad_buffer[s0:s1]
+
+        # indices of TP-replicated elements: whole buffer (for the TP gradient sum) and
+        # inside this rank's shard (for counting them once in the global norm)
+        self._rep_index_full = None
+        self._rep_index_shard = None
+        if self.tp_world_size > 1 and replicated_ranges:
+            full = torch.cat([torch.arange(a, b, device=device) for a, b in replicated_ranges])
+            self._rep_index_full = full
+            in_shard = full[(full >= s0) & (full < s1)] - s0
+            self._rep_index_shard = in_shard
+        self._sumsq = torch.zeros(2, dtype=torch.float32, device=device)
+        self._norm_out = torch.zeros(1, dtype=torch.float32, device=device)
+        self._step_count = 0
+        self.last_grad_norm: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ gradients
+    def zero_grad(self, set_to_zero: bool = False):
+        """Prepare the gradient buffer for a new step. Never sets ``.grad`` to None (the
+        views into the flat buffer must survive)."""
+        if self.use_fused_kernels and not set_to_zero:
+            for p in self.params:
+                p._grad_fresh = True
+        else:
+            self.grad_buffer.zero_()
+            for p in self.params:
+                p._grad_fresh = False
+
+    def _materialise_unwritten(self) -> None:
+        for p in self.params:
+            if getattr(p, "_grad_fresh", False):
+                p.grad.zero_()
+                p._grad_fresh = False
+
+    def _sum_replicated_grads_over_tp(self) -> None:
+        if self._rep_index_full is None or self.reference_quirks:
+            return
+        vals = self.grad_buffer.index_select(0, self._rep_index_full)
+        dist.all_reduce(vals, group=ps.get_tensor_model_parallel_group())
+        self.grad_buffer.index_copy_(0, self._rep_index_full, vals)
+
+    # ------------------------------------------------------------------ step
+    def step(self):
+        self._materialise_unwritten()
+        self._sum_replicated_grads_over_tp()
+        if self.use_fused_comm:
+            self._step_fused_comm()
+        elif self.use_fused_kernels:
+            self._step_fused_kernels()
+        else:
+            self._step_composition()
+        self._step_count += 1
+
+    def _hyper(self):
+        g = self.optimizer.param_groups[0]
+        beta1, beta2 = g.get("betas", (0.9, 0.999))
+        return g["lr"], beta1, beta2, g.get("eps", 1e-8), g.get("weight_decay", 0.0)
+
+    def _adam_state(self):
+        st = self.optimizer.state[self.fp32_master_shard]
+        if "exp_avg" not in st:
+            st["step"] = torch.tensor(0.0, dtype=torch.float32)
+            st["exp_avg"] = torch.zeros_like(self.fp32_master_shard, memory_format=torch.preserve_format)
+            st["exp_avg_sq"] = torch.zeros_like(self.fp32_master_shard, memory_format=torch.preserve_format)
+        return st
+
+    def _global_sumsq(self, local: torch.Tensor) -> torch.Tensor:
+        """local: fp32 [2] = {sum of squares of this shard, same over TP-replicated elements}."""
+        world_tp = self.tp_world_size
+        if self.reference_quirks or world_tp == 1:
+            if self.dp_world_size > 1:
+                dist.all_reduce(local[0:1], group=self.dp_group)
+            return local[0:1]
+        dist.all_reduce(local)  # over TP x DP
+        total = local[0:1] - local[1:2] * ((world_tp - 1) / world_tp)
+        return total
+
+    def _step_fused_kernels(self):
+        if self.dp_world_size > 1:
+            rs = mappings.reduce_scatter_dim0(self.grad_buffer, self.dp_group, self.dp_world_size, self.dp_rank)
+            self.reduced_grad_shard.copy_(rs) if rs.data_ptr() != self.reduced_grad_shard.data_ptr() else None
+        shard = self.reduced_grad_shard
+        sumsq = None
+        if self.clip_grad is not None and self.clip_grad > 0.0:
+            adam_ops.sumsq_bf16(shard, self._sumsq[0:1])
+            if self._rep_index_shard is not None and not self.reference_quirks:
+                self._sumsq[1] = shard.index_select(0, self._rep_index_shard).float().pow(2).sum()
+            else:
+                self._sumsq[1] = 0.0
+            sumsq = self._global_sumsq(self._sumsq)
+        lr, beta1, beta2, eps, wd = self._hyper()
+        st = self._adam_state()
+        st["step"] += 1
+        scale = 1.0 / self.dp_world_size if self.grad_reduce == "mean" else 1.0
+        out = self.param_buffer[self.shard_start:self.shard_end]
+        adam_ops.adamw_step(shard, self.fp32_master_shard.data, st["exp_avg"], st["exp_avg_sq"], out,
+                            step=self._step_count + 1, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=wd,
+                            sumsq=sumsq, clip=float(self.clip_grad or 0.0), grad_scale=scale,
+                            norm_out=self._norm_out)
+        self.last_grad_norm = self._norm_out
+        if self.dp_world_size > 1:
+            dist.all_gather_into_tensor(self.param_buffer, out.clone(), group=self.dp_group)
+
+    def _step_fused_comm(self):
+        lr, beta1, beta2, eps, wd = self._hyper()
+        st = self._adam_state()
+        st["step"] += 1
+        scale = 1.0 / self.dp_world_size if self.grad_reduce == "mean" else 1.0
+        self._dp_comm.step(self, st, step=self._step_count + 1, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                           weight_decay=wd, clip=float(self.clip_grad or 0.0), grad_scale=scale)
+        self.last_grad_norm = self._dp_comm.norm_out
+
+    def _step_composition(self):
+        """torch.distributed + torch.optim path (CPU/gloo, fp32, or fused=False): the reference's sequence."""
+        if self.dp_world_size > 1:
+            rs = mappings.reduce_scatter_dim0(self.grad_buffer, self.dp_group, self.dp_world_size, self.dp_rank)
+            self.reduced_grad_shard.copy_(rs)
+        shard = self.reduced_grad_shard
+        if self.grad_reduce == "mean" and self.dp_world_size > 1:
+            shard.div_(self.dp_world_size)
+        if self.clip_grad is not None and self.clip_grad > 0.0:
+            local = torch.zeros(2, dtype=torch.float32, device=shard.device)
+            local[0] = shard.float().pow(2).sum()
+            if self._rep_index_shard is not None and not self.reference_quirks:
+                local[1] = shard.index_select(0, self._rep_index_shard).float().pow(2).sum()
+            norm = torch.sqrt(self._global_sumsq(local))[0]
+            self.last_grad_norm = norm
+            if norm > self.clip_grad:
+                shard.mul_(self.clip_grad / (norm + 1e-6))
+        self.fp32_master_shard.grad = shard.to(torch.float32)
+        self.optimizer.step()
+        self.optimizer.zero_grad()
+        new_shard = self.fp32_master_shard.detach().to(self.dtype)
+        if self.dp_world_size > 1:
+            dist.all_gather_into_tensor(self.param_buffer, new_shard.contiguous(), group=self.dp_group)
+        else:
+            self.param_buffer.copy_(new_shard)
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self):
+        """The inner AdamW state (step, exp_avg, exp_avg_sq of the flat shard + param groups),
+        as the reference returns (core/optimizer.py:106-108)."""
+        return self.optimizer.state_dict()
+
+    def load_state_dict(self, state_dict):
+        self.optimizer.load_state_dict(state_dict)
+        st = self.optimizer.state.get(self.fp32_master_shard, {})
+        if "step" in st:
+            self._step_count = int(float(st["step"]))
+
+    def full_state_dict(self):
+        """Everything needed to resume exactly: inner state + the fp32 master shard (which the
+        reference's ``state_dict`` omits)."""
+        return {"optimizer": self.optimizer.state_dict(),
+                "fp32_master_shard": self.fp32_master_shard.detach().clone(),
+                "step_count": self._step_count,
+                "shard": (self.shard_start, self.shard_end, self.padded_numel)}
+
+    def load_full_state_dict(self, sd):
+        assert tuple(sd["shard"]) == (self.shard_start, self.shard_end, self.padded_numel), "sharding mismatch"
+        self.load_state_dict(sd["optimizer"])
+        with torch.no_grad():
+            self.fp32_master_shard.copy_(sd["fp32_master_shard"])
+        self._step_count = int(sd["step_count"])
+        # rebuild the low-precision parameters from the master weights
+        new_shard = self.fp32_master_shard.detach().to(self.dtype)
+        if self.dp_world_size > 1:
+            dist.all_gather_into_tensor(self.param_buffer, new_shard.contiguous(), group=self.dp_group)
+        else:
+            self.param_buffer.copy_(new_shard)
