@@ -414,3 +414,114 @@ int gfs_gemm_bf16_launches(int M, int N, int K, size_t ws_bytes) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Split-K GEMM for callers that cannot allocate device memory (see gfs_no_alloc.h).
+// The fp32 partial tiles live in this file-scope device array instead of a caller
+// workspace. In host code `g_static_splitk_scratch` is only a handle for the runtime's
+// symbol lookup, never a device pointer: the address the kernels get comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+// ---------------------------------------------------------------------------
+#include "gfs_no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_static_splitk_scratch[GFS_NO_ALLOC_SCRATCH_BYTES];
+
+namespace {
+
+float* static_scratch_for_current_device() {
+  static float* per_dev[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (per_dev[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_splitk_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "[gfs] gfs_gemm_bf16_splitk_static: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return nullptr;
+    }
+    per_dev[dev] = static_cast<float*>(p);
+  }
+  return per_dev[dev];
+}
+
+}  // namespace
+
+extern "C" int gfs_gemm_bf16_splitk_static(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                           int lda, int ldb, int ldc, int ldr, int a_mn_major, int b_mn_major,
+                                           int add, int splits, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || splits < 2) return GFS_NO_ALLOC_ERR_BAD_ARGUMENT;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || (add && (ldr & 7))) return GFS_NO_ALLOC_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       (add ? reinterpret_cast<uintptr_t>(R) : 0)) & 15)
+    return GFS_NO_ALLOC_ERR_ALIGNMENT;
+  const int kblocks = (K + BK - 1) / BK;
+  if (splits > kblocks) return GFS_NO_ALLOC_ERR_BAD_ARGUMENT;
+  const size_t need = static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
+  if (need > GFS_NO_ALLOC_SCRATCH_BYTES) {
+    fprintf(stderr,
+            "[gfs] gfs_gemm_bf16_splitk_static: %d splits of a %d x %d output need %zu bytes of partial tiles, the "
+            "built-in scratch holds %u\n",
+            splits, M, N, need, static_cast<unsigned>(GFS_NO_ALLOC_SCRATCH_BYTES));
+    return GFS_NO_ALLOC_ERR_TOO_LARGE;
+  }
+  float* scratch = static_scratch_for_current_device();
+  if (scratch == nullptr) return GFS_NO_ALLOC_ERR_SETUP;
+
+  const int BN = (N > 128) ? 256 : 128;
+  // tensor maps on the stack: nothing is cached or heap-allocated on this path
+  CUtensorMap ta, tb;
+  {
+    const uint64_t a_rows = a_mn_major ? K : M, a_cols = a_mn_major ? M : K;
+    const uint64_t b_rows = b_mn_major ? K : N, b_cols = b_mn_major ? N : K;
+    uint64_t dims[2] = {a_cols, a_rows};
+    uint64_t strides[2] = {2, static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, a_mn_major ? 64u : static_cast<uint32_t>(BM)};
+    if (gfs_host::encode_tmap_bf16(&ta, A, 2, dims, strides, box) != 0) return GFS_NO_ALLOC_ERR_TENSOR_MAP;
+    uint64_t dims_b[2] = {b_cols, b_rows};
+    uint64_t strides_b[2] = {2, static_cast<uint64_t>(ldb) * 2};
+    uint32_t box_b[2] = {64, b_mn_major ? 64u : static_cast<uint32_t>(BN)};
+    if (gfs_host::encode_tmap_bf16(&tb, B, 2, dims_b, strides_b, box_b) != 0) return GFS_NO_ALLOC_ERR_TENSOR_MAP;
+  }
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ldr = ldr;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.ws = scratch;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.kblocks_total = kblocks;
+  p.status = nullptr;  // no status buffer on this path
+  p.kblocks_per_split = (kblocks + splits - 1) / splits;
+  const int split = (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;  // no empty splits
+  p.split_k = split;
+  p.epi_mode = split > 1 ? EPI_PARTIAL_F32 : (add ? EPI_ADD : EPI_STORE);
+  const int sms = gfs_host::sm_count();
+  const int grid = std::min(p.tiles_m * p.tiles_n * split, sms);
+
+  int rc;
+  if (BN == 256) {
+    if (!a_mn_major && !b_mn_major) rc = launch_variant<false, false, 256, 4>(&ta, &tb, p, grid, stream);
+    else if (!a_mn_major && b_mn_major) rc = launch_variant<false, true, 256, 4>(&ta, &tb, p, grid, stream);
+    else if (a_mn_major && b_mn_major) rc = launch_variant<true, true, 256, 4>(&ta, &tb, p, grid, stream);
+    else rc = launch_variant<true, false, 256, 4>(&ta, &tb, p, grid, stream);
+  } else {
+    if (!a_mn_major && !b_mn_major) rc = launch_variant<false, false, 128, 6>(&ta, &tb, p, grid, stream);
+    else if (!a_mn_major && b_mn_major) rc = launch_variant<false, true, 128, 6>(&ta, &tb, p, grid, stream);
+    else if (a_mn_major && b_mn_major) rc = launch_variant<true, true, 128, 6>(&ta, &tb, p, grid, stream);
+    else rc = launch_variant<true, false, 128, 6>(&ta, &tb, p, grid, stream);
+  }
+  if (rc != 0) return GFS_NO_ALLOC_ERR_LAUNCH;
+  if (split > 1) {
+    const size_t groups = static_cast<size_t>(M) * (N >> 3);
+    const int threads = 256;
+    const int blocks =
+        static_cast<int>(std::min<size_t>((groups + threads - 1) / threads, static_cast<size_t>(sms) * 8));
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(scratch, p.C, p.R, M, N, ldc, ldr, split, add);
+    if (cudaGetLastError() != cudaSuccess) return GFS_NO_ALLOC_ERR_LAUNCH;
+  }
+  return 0;
+}
