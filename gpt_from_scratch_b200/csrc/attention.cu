@@ -25,6 +25,7 @@
 // Reference counterparts: core/myFlashAttn.py:460-728 (_attn_fwd), :740-790 (pre-pass),
 // :805-1066 (_attn_bwd_LoopQ), :1079-1317 (_attn_bwd_LoopKV).
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -76,21 +77,25 @@ struct FwdParams {
   uint32_t* status;
 };
 
-template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+// NBUF = 2: S / P / PV tiles double buffered, one CTA per SM (head_dim 128).
+// NBUF = 1: single buffers, half the shared memory and TMEM, so two CTAs share an SM and
+//           hide each other's softmax / MMA latencies (head_dim 64).
+template <int D, int NBUF>
+__global__ void __launch_bounds__(ATT_THREADS, NBUF == 1 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const FwdParams p) {
   constexpr int DB = D / 64;
   constexpr int TILE_BYTES = DB * 16384;  // [128 x D] bf16 as DB swizzled blocks
   constexpr int P_BYTES = 32768;          // [128 x 128] bf16 as 2 swizzled blocks
-  constexpr uint32_t TMEM_COLS = 512;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
+  constexpr uint32_t TMEM_COLS = (NBUF == 2) ? 512 : 256;
+  constexpr uint32_t OP_COL = NBUF * 128;  // PV tiles start after the S tiles
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;  // the launcher requests exactly the bytes used; the base must be 1024-aligned
   uint8_t* Qs = smem;
   uint8_t* Ks = Qs + TILE_BYTES;
   uint8_t* Vs = Ks + 2 * TILE_BYTES;
   uint8_t* Ps = Vs + 2 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + NBUF * P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* k_empty = bars + 3;
@@ -107,6 +112,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (smem_u32(smem_raw) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) record_status(p.status, STATUS_BAD_ARGUMENT, 0x5a11u);
+    return;
+  }
   const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest (most key blocks) first
   const int bh = blockIdx.y;
   const int b = bh / p.nh;
@@ -174,13 +183,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const uint32_t q_addr = smem_u32(Qs);
       mbar_wait(q_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
       auto issue_s = [&](int j) {
-        const int st = j & 1;
+        const int st = j & 1;                       // K/V stage
         const uint32_t par = (j >> 1) & 1;
+        const int sb = (NBUF == 2) ? (j & 1) : 0;   // S / P / PV buffer
+        const uint32_t spar = (NBUF == 2) ? ((j >> 1) & 1) : (j & 1);
         mbar_wait(&k_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
-        mbar_wait(&s_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        mbar_wait(&s_empty[sb], spar ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
-        mma_kk<D / 16>(tmem_base + st * 128, q_addr, 16384, smem_u32(Ks + st * TILE_BYTES), 16384, idesc_s, false);
-        umma_commit(&s_full[st]);
+        mma_kk<D / 16>(tmem_base + sb * 128, q_addr, 16384, smem_u32(Ks + st * TILE_BYTES), 16384, idesc_s, false);
+        umma_commit(&s_full[sb]);
         umma_commit(&k_empty[st]);
       };
       issue_s(0);
@@ -188,15 +199,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         if (j + 1 < n_kv) issue_s(j + 1);
         const int st = j & 1;
         const uint32_t par = (j >> 1) & 1;
-        mbar_wait(&p_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
+        const int sb = (NBUF == 2) ? (j & 1) : 0;
+        const uint32_t spar = (NBUF == 2) ? ((j >> 1) & 1) : (j & 1);
+        mbar_wait(&p_full[sb], spar, wctx, STATUS_TIMEOUT_SOFTMAX);
         mbar_wait(&v_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
-        mbar_wait(&o_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        mbar_wait(&o_empty[sb], spar ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
-        mma_kmn<8>(tmem_base + 256 + st * D, smem_u32(Ps + st * P_BYTES), 16384, smem_u32(Vs + st * TILE_BYTES),
+        mma_kmn<8>(tmem_base + OP_COL + sb * D, smem_u32(Ps + sb * P_BYTES), 16384, smem_u32(Vs + st * TILE_BYTES),
                    16384, idesc_o, false);
-        umma_commit(&o_full[st]);
+        umma_commit(&o_full[sb]);
         umma_commit(&v_empty[st]);
-        umma_commit(&p_empty[st]);
+        umma_commit(&p_empty[sb]);
       }
     }
   } else {
@@ -211,16 +224,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     for (int i = 0; i < D; ++i) o[i] = 0.f;
 
     auto fold_pv = [&](int j, float alpha) {
-      const int st = j & 1;
-      mbar_wait(&o_full[st], (j >> 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+      const int st = (NBUF == 2) ? (j & 1) : 0;
+      mbar_wait(&o_full[st], (NBUF == 2) ? ((j >> 1) & 1) : (j & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
       tc_fence_after();
+      const uint32_t o_addr = tmem_base + lane_base + OP_COL + st * D;
+      uint32_t wa[32], wb[32];
+      tmem_ld_32x32(o_addr, wa);
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_base + 256 + st * D + c, v);
-        tmem_ld_wait();
+      for (int c = 0; c < D; c += 64) {
+        tmem_ld_wait_for(wa);
+        tmem_ld_32x32(o_addr + c + 32, wb);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c + e] = o[c + e] * alpha + __uint_as_float(v[e]);
+        for (int e = 0; e < 32; ++e) o[c + e] = fmaf(o[c + e], alpha, __uint_as_float(wa[e]));
+        tmem_ld_wait_for(wb);
+        if (c + 64 < D) tmem_ld_32x32(o_addr + c + 64, wa);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c + 32 + e] = fmaf(o[c + 32 + e], alpha, __uint_as_float(wb[e]));
       }
       tc_fence_before();
       __syncwarp();
@@ -228,19 +247,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     };
 
     for (int j = 0; j < n_kv; ++j) {
-      const int st = j & 1;
-      const uint32_t par = (j >> 1) & 1;
+      const int st = (NBUF == 2) ? (j & 1) : 0;
+      const uint32_t par = (NBUF == 2) ? ((j >> 1) & 1) : (j & 1);
       const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
       mbar_wait(&s_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_base + st * 128;
-      // pass 1: row maximum
+      // pass 1: row maximum (TMEM loads double buffered against the arithmetic)
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c, v);
-        tmem_ld_wait();
+      uint32_t va[32], vb[32];
+      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
         if (need_mask) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
@@ -252,7 +268,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
         }
-      }
+      };
+      tmem_ld_32x32(s_addr + 0, va);
+      tmem_ld_wait_for(va);
+      tmem_ld_32x32(s_addr + 32, vb);
+      max_chunk(va, 0);
+      tmem_ld_wait_for(vb);
+      tmem_ld_32x32(s_addr + 64, va);
+      max_chunk(vb, 32);
+      tmem_ld_wait_for(va);
+      tmem_ld_32x32(s_addr + 96, vb);
+      max_chunk(va, 64);
+      tmem_ld_wait_for(vb);
+      tmem_ld_32x32(s_addr + 0, va);  // first chunk of pass 2
+      max_chunk(vb, 96);
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // row with no live key so far
       const float alpha = fast_exp2((m - m_use) * sl2);
@@ -261,34 +290,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
       float rs = 0.f;
       uint8_t* prow = Ps + st * P_BYTES + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c, v);
-        tmem_ld_wait();
-        float pv[32];
+      auto prob_chunk_impl = [&](auto mask_tag, const uint32_t (&v)[32], int c) {
+        constexpr bool MASKED = decltype(mask_tag)::value;
+        uint32_t packed[16];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = fast_exp2(__uint_as_float(v[e]) * sl2 - moff);
-          if (need_mask) {
+        for (int e = 0; e < 32; e += 2) {
+          float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
+          float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
+          if constexpr (MASKED) {
             const int col_g = j * 128 + c + e;
-            if ((p.causal && col_g > row_g) || col_g >= p.S) x = 0.f;
+            const bool dead0 = (p.causal && col_g > row_g) || col_g >= p.S;
+            const bool dead1 = (p.causal && col_g + 1 > row_g) || col_g + 1 >= p.S;
+            x0 = dead0 ? 0.f : x0;
+            x1 = dead1 ? 0.f : x1;
           }
-          pv[e] = x;
-          rs += x;
+          rs += x0 + x1;
+          packed[e >> 1] = pack_bf16x2(x0, x1);
         }
         uint8_t* blk = prow + (c >> 6) * 16384;
         const int chunk0 = (c & 63) >> 3;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(pv[8 * q4 + 0], pv[8 * q4 + 1]);
-          w.y = pack_bf16x2(pv[8 * q4 + 2], pv[8 * q4 + 3]);
-          w.z = pack_bf16x2(pv[8 * q4 + 4], pv[8 * q4 + 5]);
-          w.w = pack_bf16x2(pv[8 * q4 + 6], pv[8 * q4 + 7]);
+          const uint4 w = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
           *reinterpret_cast<uint4*>(blk + ((((chunk0 + q4) ^ (r & 7)) & 7) << 4)) = w;
         }
-      }
+      };
+      auto prob_chunk = [&](const uint32_t (&v)[32], int c) {
+        if (need_mask) prob_chunk_impl(std::true_type{}, v, c);
+        else prob_chunk_impl(std::false_type{}, v, c);
+      };
+      tmem_ld_wait_for(va);
+      tmem_ld_32x32(s_addr + 32, vb);
+      prob_chunk(va, 0);
+      tmem_ld_wait_for(vb);
+      tmem_ld_32x32(s_addr + 64, va);
+      prob_chunk(vb, 32);
+      tmem_ld_wait_for(va);
+      tmem_ld_32x32(s_addr + 96, vb);
+      prob_chunk(va, 64);
+      tmem_ld_wait_for(vb);
+      prob_chunk(vb, 96);
       l = l * alpha + rs;
       m = m_new;
       tc_fence_before();
@@ -369,8 +410,8 @@ struct BwdParams {
   uint32_t* status;
 };
 
-template <int D, int MODE>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+template <int D, int MODE, int NBUF>
+__global__ void __launch_bounds__(ATT_THREADS, NBUF == 1 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
                  const __grid_constant__ CUtensorMap tt1, const __grid_constant__ CUtensorMap tt2,
                  const BwdParams p) {
@@ -378,8 +419,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   constexpr int R_BYTES = DB * 16384;  // resident [128 x D]
   constexpr int T_BYTES = DB * 8192;   // streamed [64 x D]
   constexpr int M_BYTES = 16384;       // [128 x 64] bf16
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t ACC1 = 256, ACC2 = 256 + D;
+  constexpr uint32_t TMEM_COLS = (NBUF == 1 && D == 64) ? 256 : 512;
+  constexpr uint32_t Y_COL = 64 * NBUF;  // X tiles at [0, 64*NBUF), Y tiles after them
+  constexpr uint32_t ACC1 = 128 * NBUF, ACC2 = 128 * NBUF + D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* R1 = smem;
@@ -387,8 +429,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   uint8_t* T1 = R2 + R_BYTES;        // 2 stages
   uint8_t* T2 = T1 + 2 * T_BYTES;    // 2 stages
   uint8_t* M1 = T2 + 2 * T_BYTES;    // 2 buffers
-  uint8_t* M2 = M1 + 2 * M_BYTES;    // 2 buffers
-  float* stats = reinterpret_cast<float*>(M2 + 2 * M_BYTES);  // mode 0: [2 stages][lse 64 | dvec 64]
+  uint8_t* M2 = M1 + NBUF * M_BYTES;
+  float* stats = reinterpret_cast<float*>(M2 + NBUF * M_BYTES);  // mode 0: [2 stages][lse 64 | dvec 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + 1024);
   uint64_t* r_full = bars;
   uint64_t* t_full = bars + 1;
@@ -483,34 +525,37 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
       mbar_wait(r_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
       auto issue_xy = [&](int t) {
-        const int st = t & 1;
+        const int st = t & 1;                       // streamed-tile stage
         const uint32_t par = (t >> 1) & 1;
+        const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
+        const uint32_t spar = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
         mbar_wait(&t_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
-        mbar_wait(&xy_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+        mbar_wait(&xy_empty[sb], spar ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
-        mma_kk<D / 16>(tmem_base + st * 64, r1, 16384, smem_u32(T1 + st * T_BYTES), 8192, idesc_xy, false);
-        mma_kk<D / 16>(tmem_base + 128 + st * 64, r2, 16384, smem_u32(T2 + st * T_BYTES), 8192, idesc_xy, false);
-        umma_commit(&xy_full[st]);
+        mma_kk<D / 16>(tmem_base + sb * 64, r1, 16384, smem_u32(T1 + st * T_BYTES), 8192, idesc_xy, false);
+        mma_kk<D / 16>(tmem_base + Y_COL + sb * 64, r2, 16384, smem_u32(T2 + st * T_BYTES), 8192, idesc_xy, false);
+        umma_commit(&xy_full[sb]);
       };
       if (n_t > 0) issue_xy(0);
       for (int t = 0; t < n_t; ++t) {
         if (t + 1 < n_t) issue_xy(t + 1);
         const int st = t & 1;
-        mbar_wait(&m_full[st], (t >> 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+        const int sb = (NBUF == 2) ? (t & 1) : 0;
+        mbar_wait(&m_full[sb], (NBUF == 2) ? ((t >> 1) & 1) : (t & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
         if (MODE == 0) {
           // dV += P^T dO ; dK += dS^T Q
-          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + st * M_BYTES), 0, smem_u32(T2 + st * T_BYTES), 8192, idesc_acc,
+          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + sb * M_BYTES), 0, smem_u32(T2 + st * T_BYTES), 8192, idesc_acc,
                      t > 0);
-          mma_kmn<4>(tmem_base + ACC2, smem_u32(M2 + st * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
+          mma_kmn<4>(tmem_base + ACC2, smem_u32(M2 + sb * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
                      t > 0);
         } else {
           // dQ += dS K
-          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + st * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
+          mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + sb * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
                      t > 0);
         }
         umma_commit(&t_empty[st]);
-        umma_commit(&m_empty[st]);
+        umma_commit(&m_empty[sb]);
       }
       umma_commit(acc_full);
     }
@@ -526,77 +571,86 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       row_dvec = p.dvec[static_cast<size_t>(bh) * p.S_pad + row_g];
     }
     for (int t = 0; t < n_t; ++t) {
-      const int st = t & 1;
-      const uint32_t par = (t >> 1) & 1;
+      const int st = t & 1;                       // streamed-tile stage (for the column statistics)
+      const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
+      const uint32_t par = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
       const int ti = t_begin + t;
       bool need_mask;
       if (MODE == 0) need_mask = (p.causal && ti < 2 * rt + 2) || ((ti + 1) * 64 > p.S);
       else need_mask = (p.causal && ti >= 2 * rt) || ((ti + 1) * 64 > p.S);
-      mbar_wait(&xy_full[st], par, wctx, STATUS_TIMEOUT_SOFTMAX);
-      mbar_wait(&m_empty[st], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(&xy_full[sb], par, wctx, STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(&m_empty[sb], par ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
       tc_fence_after();
       const float* st_lse = stats + st * 128;
       const float* st_dv = st_lse + 64;
-      uint8_t* m1row = M1 + st * M_BYTES + r * 128;
-      uint8_t* m2row = M2 + st * M_BYTES + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t xv[32], yv[32];
-        tmem_ld_32x32(tmem_base + lane_base + st * 64 + c, xv);
-        tmem_ld_32x32(tmem_base + lane_base + 128 + st * 64 + c, yv);
-        tmem_ld_wait();
-        float pv[32], dsv[32];
+      uint8_t* m1row = M1 + sb * M_BYTES + r * 128;
+      uint8_t* m2row = M2 + sb * M_BYTES + r * 128;
+      uint32_t xa[32], ya[32], xb[32], yb[32];
+      auto grad_chunk_impl = [&](auto mask_tag, const uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
+        constexpr bool MASKED = decltype(mask_tag)::value;
+        uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c + e;
-          float lse_e, dv_e;
-          if (MODE == 0) {
-            lse_e = st_lse[col] * LOG2E_F;
-            dv_e = st_dv[col];
-          } else {
-            lse_e = row_lse;
-            dv_e = row_dvec;
-          }
-          float pe = fast_exp2(__uint_as_float(xv[e]) * sl2 - lse_e);
-          float de = pe * (__uint_as_float(yv[e]) - dv_e);
-          if (need_mask) {
-            const int col_g = ti * 64 + col;
-            bool dead;
-            if (MODE == 0) dead = (p.causal && col_g < row_g) || col_g >= p.S;   // col = query, row = key
-            else dead = (p.causal && col_g > row_g) || col_g >= p.S;             // col = key, row = query
-            if (dead) {
-              pe = 0.f;
-              de = 0.f;
+        for (int e = 0; e < 32; e += 2) {
+          float pe[2], de[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c + e + u;
+            float lse_e, dv_e;
+            if (MODE == 0) {
+              lse_e = st_lse[col] * LOG2E_F;
+              dv_e = st_dv[col];
+            } else {
+              lse_e = row_lse;
+              dv_e = row_dvec;
+            }
+            pe[u] = fast_exp2(fmaf(__uint_as_float(xv[e + u]), sl2, -lse_e));
+            de[u] = pe[u] * (__uint_as_float(yv[e + u]) - dv_e);
+            if constexpr (MASKED) {
+              const int col_g = ti * 64 + col;
+              bool dead;
+              if (MODE == 0) dead = (p.causal && col_g < row_g) || col_g >= p.S;  // col = query, row = key
+              else dead = (p.causal && col_g > row_g) || col_g >= p.S;            // col = key, row = query
+              pe[u] = dead ? 0.f : pe[u];
+              de[u] = dead ? 0.f : de[u];
             }
           }
-          pv[e] = pe;
-          dsv[e] = de;
+          pp[e >> 1] = pack_bf16x2(pe[0], pe[1]);
+          dd[e >> 1] = pack_bf16x2(de[0], de[1]);
         }
         const int chunk0 = c >> 3;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int off = (((chunk0 + q4) ^ (r & 7)) & 7) << 4;
-          uint4 w;
           if (MODE == 0) {
-            w.x = pack_bf16x2(pv[8 * q4 + 0], pv[8 * q4 + 1]);
-            w.y = pack_bf16x2(pv[8 * q4 + 2], pv[8 * q4 + 3]);
-            w.z = pack_bf16x2(pv[8 * q4 + 4], pv[8 * q4 + 5]);
-            w.w = pack_bf16x2(pv[8 * q4 + 6], pv[8 * q4 + 7]);
-            *reinterpret_cast<uint4*>(m1row + off) = w;
+            *reinterpret_cast<uint4*>(m1row + off) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2],
+                                                                 pp[4 * q4 + 3]);
           }
-          w.x = pack_bf16x2(dsv[8 * q4 + 0], dsv[8 * q4 + 1]);
-          w.y = pack_bf16x2(dsv[8 * q4 + 2], dsv[8 * q4 + 3]);
-          w.z = pack_bf16x2(dsv[8 * q4 + 4], dsv[8 * q4 + 5]);
-          w.w = pack_bf16x2(dsv[8 * q4 + 6], dsv[8 * q4 + 7]);
-          *reinterpret_cast<uint4*>((MODE == 0 ? m2row : m1row) + off) = w;
+          *reinterpret_cast<uint4*>((MODE == 0 ? m2row : m1row) + off) =
+              make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]);
         }
-      }
+      };
+      auto grad_chunk = [&](const uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
+        if (need_mask) grad_chunk_impl(std::true_type{}, xv, yv, c);
+        else grad_chunk_impl(std::false_type{}, xv, yv, c);
+      };
+      const uint32_t x_addr = tmem_base + lane_base + sb * 64;
+      const uint32_t y_addr = tmem_base + lane_base + Y_COL + sb * 64;
+      tmem_ld_32x32(x_addr, xa);
+      tmem_ld_32x32(y_addr, ya);
+      tmem_ld_wait_for(xa);
+      tmem_ld_wait_for(ya);
+      tmem_ld_32x32(x_addr + 32, xb);
+      tmem_ld_32x32(y_addr + 32, yb);
+      grad_chunk(xa, ya, 0);
+      tmem_ld_wait_for(xb);
+      tmem_ld_wait_for(yb);
+      grad_chunk(xb, yb, 32);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&xy_empty[st]);
-        mbar_arrive(&m_full[st]);
+        mbar_arrive(&xy_empty[sb]);
+        mbar_arrive(&m_full[sb]);
       }
     }
     // epilogue: accumulators -> global
@@ -694,14 +748,15 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   p.scale = scale; p.causal = causal;
   p.status = gfs_host::status_words();
   const dim3 grid((S + 127) / 128, B * nh);
-  const int smem = (D / 64) * 16384 * 5 + 65536 + 256 + 1024;
   static bool set64 = false, set128 = false;
   if (D == 64) {
-    if (!set64) { if (set_smem(flash_fwd_kernel<64>, smem)) return -10; set64 = true; }
-    flash_fwd_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+    const int smem = 16384 * 5 + 1 * 32768 + 256;   // single-buffered: two CTAs per SM
+    if (!set64) { if (set_smem(flash_fwd_kernel<64, 1>, smem)) return -10; set64 = true; }
+    flash_fwd_kernel<64, 1><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
   } else {
-    if (!set128) { if (set_smem(flash_fwd_kernel<128>, smem)) return -10; set128 = true; }
-    flash_fwd_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+    const int smem = 32768 * 5 + 2 * 32768 + 256;
+    if (!set128) { if (set_smem(flash_fwd_kernel<128, 2>, smem)) return -10; set128 = true; }
+    flash_fwd_kernel<128, 2><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
@@ -745,7 +800,8 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p.S = S; p.S_pad = S_pad; p.B = B; p.nh = nh; p.scale = scale; p.causal = causal;
   p.status = gfs_host::status_words();
   const dim3 grid((S + 127) / 128, B * nh);
-  const int smem = 2 * (D / 64) * 16384 + 4 * (D / 64) * 8192 + 4 * 16384 + 1024 + 256 + 1024;
+  const int nbuf = (D == 64) ? 1 : 2;
+  const int smem = 2 * (D / 64) * 16384 + 4 * (D / 64) * 8192 + 2 * nbuf * 16384 + 1024 + 256 + 1024;
   static bool set_done[4] = {false, false, false, false};
   // mode 0: dK, dV
   BwdParams p0 = p;
@@ -755,17 +811,17 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p1.out1 = static_cast<__nv_bfloat16*>(dq); p1.o1_ss = sdq[0]; p1.o1_bs = sdq[1]; p1.o1_hs = sdq[2];
   p1.out2 = nullptr; p1.o2_ss = p1.o2_bs = p1.o2_hs = 0;
   if (D == 64) {
-    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0>, smem)) return -10; set_done[0] = true; }
-    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1>, smem)) return -10; set_done[1] = true; }
-    flash_bwd_kernel<64, 0><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 1>, smem)) return -10; set_done[0] = true; }
+    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 1>, smem)) return -10; set_done[1] = true; }
+    flash_bwd_kernel<64, 0, 1><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<64, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<64, 1, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
   } else {
-    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0>, smem)) return -10; set_done[2] = true; }
-    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1>, smem)) return -10; set_done[3] = true; }
-    flash_bwd_kernel<128, 0><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2>, smem)) return -10; set_done[2] = true; }
+    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2>, smem)) return -10; set_done[3] = true; }
+    flash_bwd_kernel<128, 0, 2><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<128, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<128, 1, 2><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }

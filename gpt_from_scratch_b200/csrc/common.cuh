@@ -87,17 +87,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false if the wait was abandoned (status recorded).
+// Bounded wait. Returns false if the wait was abandoned (status recorded). The global timer
+// is slow to read, so it is only consulted every 4096 failed polls; the first reading
+// starts the budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*ctx.abort_flag) return false;
-  const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
+  uint64_t t0 = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 0xffu) == 0u) {
+    if (((++it) & 0xfffu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > ctx.limit_ns) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > ctx.limit_ns) {
         *ctx.abort_flag = 1u;
         record_status(ctx.status, code, (blockIdx.x << 8) | (threadIdx.x >> 5));
         return false;
@@ -199,6 +204,18 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, but naming the destination registers so the compiler cannot schedule their
+// consumers above it when loads and arithmetic are software-pipelined.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 
 // ----------------------------------------------------------------------------
 // UMMA descriptors (bf16, 128-byte swizzle)
