@@ -375,23 +375,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                                  float* __restrict__ dvec, int S, int S_pad, int B, int nh, int D, long long do_ss,
                                  long long do_bs, long long do_hs, long long o_ss, long long o_bs, long long o_hs) {
-  const int lane = threadIdx.x & 31;
-  const long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  // D/8 threads per (s, b, h) row, 16-byte loads; rows ordered h fastest (memory order of [S,B,nh,D]).
+  const int tpr = D >> 3;                       // 8 or 16 threads per row
+  const int rows_per_block = blockDim.x / tpr;
+  const long long row = blockIdx.x * static_cast<long long>(rows_per_block) + threadIdx.x / tpr;
+  const int sub = threadIdx.x % tpr;
   const long long total = static_cast<long long>(S) * B * nh;
-  if (row >= total) return;
-  const int h = static_cast<int>(row % nh);
-  const int b = static_cast<int>((row / nh) % B);
-  const int s = static_cast<int>(row / (static_cast<long long>(nh) * B));
-  const __nv_bfloat16* a = dO + s * do_ss + b * do_bs + h * do_hs;
-  const __nv_bfloat16* c = O + s * o_ss + b * o_bs + h * o_hs;
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + d));
-    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(c + d));
-    acc += x.x * y.x + x.y * y.y;
+  int h = 0, b = 0, s = 0;
+  if (row < total) {
+    h = static_cast<int>(row % nh);
+    b = static_cast<int>((row / nh) % B);
+    s = static_cast<int>(row / (static_cast<long long>(nh) * B));
+    const uint4 x = *reinterpret_cast<const uint4*>(dO + s * do_ss + b * do_bs + h * do_hs + sub * 8);
+    const uint4 y = *reinterpret_cast<const uint4*>(O + s * o_ss + b * o_bs + h * o_hs + sub * 8);
+    const float2 x0 = unpack_bf16x2(x.x), x1 = unpack_bf16x2(x.y), x2 = unpack_bf16x2(x.z), x3 = unpack_bf16x2(x.w);
+    const float2 y0 = unpack_bf16x2(y.x), y1 = unpack_bf16x2(y.y), y2 = unpack_bf16x2(y.z), y3 = unpack_bf16x2(y.w);
+    acc = x0.x * y0.x + x0.y * y0.y + x1.x * y1.x + x1.y * y1.y + x2.x * y2.x + x2.y * y2.y + x3.x * y3.x +
+          x3.y * y3.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) dvec[(static_cast<size_t>(b) * nh + h) * S_pad + s] = acc;
+  for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (row < total && sub == 0) dvec[(static_cast<size_t>(b) * nh + h) * S_pad + s] = acc;
 }
 
 // ---------------------------------------------------------------------------
@@ -408,6 +412,9 @@ struct BwdParams {
   float scale;
   int causal;
   uint32_t* status;
+  // optional: inverse rotary embedding applied to dQ and dK rows before they are stored
+  const float* rope_cos;
+  const float* rope_sin;
 };
 
 template <int D, int MODE, int NBUF>
@@ -668,11 +675,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       if (live) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * q4 + e]) * p.scale;
+          if (p.rope_cos != nullptr) {  // inverse rotation: sin -> -sin
+            const size_t ti = static_cast<size_t>(row_g) * (D / 2) + ((c + 8 * q4) >> 1);
+            const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
+            const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
+            const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
+            f[0] = a0 * cs.x + a1 * sn.x; f[1] = a1 * cs.x - a0 * sn.x;
+            f[2] = a2 * cs.y + a3 * sn.y; f[3] = a3 * cs.y - a2 * sn.y;
+            f[4] = a4 * cs.z + a5 * sn.z; f[5] = a5 * cs.z - a4 * sn.z;
+            f[6] = a6 * cs.w + a7 * sn.w; f[7] = a7 * cs.w - a6 * sn.w;
+          }
           uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * p.scale, __uint_as_float(v[8 * q4 + 1]) * p.scale);
-          w.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * p.scale, __uint_as_float(v[8 * q4 + 3]) * p.scale);
-          w.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * p.scale, __uint_as_float(v[8 * q4 + 5]) * p.scale);
-          w.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * p.scale, __uint_as_float(v[8 * q4 + 7]) * p.scale);
+          w.x = pack_bf16x2(f[0], f[1]);
+          w.y = pack_bf16x2(f[2], f[3]);
+          w.z = pack_bf16x2(f[4], f[5]);
+          w.w = pack_bf16x2(f[6], f[7]);
           *reinterpret_cast<uint4*>(d1 + c + 8 * q4) = w;
         }
       }
@@ -763,9 +783,12 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
 
 // strides: 24 element strides for {q, k, v, o, do, dq, dk, dv} x {seq, batch, head}.
 // lse, dvec: fp32 [B, nh, S_pad]; dvec is scratch written by the pre-pass.
+// rope_cos / rope_sin (optional, fp32 [>=S, D/2]): when given, dq and dk are rotated back
+// (inverse rotary embedding) as they are written, i.e. they are gradients w.r.t. the
+// un-rotated projections.
 int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const void* lse,
                   void* dvec, void* dq, void* dk, void* dv, int S, int B, int nh, int D, const long long* strides,
-                  float scale, int causal, void* stream_) {
+                  float scale, int causal, const void* rope_cos, const void* rope_sin, void* stream_) {
   if (D != 64 && D != 128) return -1;
   if (!strides_ok(strides, 24)) return -1;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
@@ -779,8 +802,9 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
                   *sdq = strides + 15, *sdk = strides + 18, *sdv = strides + 21;
   {
     const long long rows = static_cast<long long>(S) * B * nh;
-    const int warps = 8;
-    attn_dvec_kernel<<<static_cast<int>((rows + warps - 1) / warps), warps * 32, 0, stream>>>(
+    const int threads = 256;
+    const int rows_per_block = threads / (D >> 3);
+    attn_dvec_kernel<<<static_cast<int>((rows + rows_per_block - 1) / rows_per_block), threads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec), S,
         S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
     if (cudaGetLastError() != cudaSuccess) return -11;
@@ -799,6 +823,8 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p.dvec = static_cast<const float*>(dvec);
   p.S = S; p.S_pad = S_pad; p.B = B; p.nh = nh; p.scale = scale; p.causal = causal;
   p.status = gfs_host::status_words();
+  p.rope_cos = static_cast<const float*>(rope_cos);
+  p.rope_sin = static_cast<const float*>(rope_sin);
   const dim3 grid((S + 127) / 128, B * nh);
   const int nbuf = (D == 64) ? 1 : 2;
   const int smem = 2 * (D / 64) * 16384 + 4 * (D / 64) * 8192 + 2 * nbuf * 16384 + 1024 + 256 + 1024;

@@ -48,6 +48,11 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int epi_mode;
   uint32_t* status;
+  // optional rotary embedding applied to the first rope_cols output columns (interleaved
+  // pairs inside heads of rope_d columns); output row r belongs to position r / rope_b
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_cols, rope_d, rope_b;
 };
 
 template <int BN, int STAGES>
@@ -229,6 +234,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * j + e]);
+                if (p.rope_cos != nullptr && col0 + 8 * j < p.rope_cols) {
+                  const int half = p.rope_d >> 1;
+                  const size_t ti = static_cast<size_t>(row / p.rope_b) * half + (((col0 + 8 * j) % p.rope_d) >> 1);
+                  const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
+                  const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
+                  const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
+                  f[0] = a0 * cs.x - a1 * sn.x; f[1] = a0 * sn.x + a1 * cs.x;
+                  f[2] = a2 * cs.y - a3 * sn.y; f[3] = a2 * sn.y + a3 * cs.y;
+                  f[4] = a4 * cs.z - a5 * sn.z; f[5] = a4 * sn.z + a5 * cs.z;
+                  f[6] = a6 * cs.w - a7 * sn.w; f[7] = a6 * sn.w + a7 * cs.w;
+                }
                 if (p.epi_mode == EPI_ADD) {
                   const uint4 rr = *reinterpret_cast<const uint4*>(res + 8 * j);
                   const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
@@ -340,10 +356,30 @@ extern "C" {
 // ws/ws_bytes: fp32 workspace for split-K (may be null: split-K is then disabled).
 // force_split: 0 = automatic, >0 = use exactly that many splits (tests).
 // Returns 0 on success, a negative value if the arguments cannot be served.
+int gfs_gemm_bf16_rope(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                       int ldc, int ldr, int a_mn_major, int b_mn_major, int add, void* ws, size_t ws_bytes,
+                       int force_split, const void* rope_cos, const void* rope_sin, int rope_cols, int rope_d,
+                       int rope_b, void* stream_);
+
 int gfs_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc,
                   int ldr, int a_mn_major, int b_mn_major, int add, void* ws, size_t ws_bytes, int force_split,
                   void* stream_) {
+  return gfs_gemm_bf16_rope(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn_major, b_mn_major, add, ws, ws_bytes,
+                            force_split, nullptr, nullptr, 0, 0, 1, stream_);
+}
+
+// Same product with a rotary-embedding epilogue: the first rope_cols output columns are
+// rotated pairwise with cos/sin[row / rope_b][(col % rope_d) / 2] (fp32 tables [positions, rope_d/2]).
+// Split-K is disabled when the rotation is requested.
+int gfs_gemm_bf16_rope(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb,
+                       int ldc, int ldr, int a_mn_major, int b_mn_major, int add, void* ws, size_t ws_bytes,
+                       int force_split, const void* rope_cos, const void* rope_sin, int rope_cols, int rope_d,
+                       int rope_b, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rope_cos != nullptr) {
+    if ((rope_d & 7) || (rope_cols & 7) || rope_b <= 0) return -1;
+    ws = nullptr;
+  }
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || (add && (ldr & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
@@ -356,12 +392,15 @@ int gfs_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, i
                                      : gfs_host::tmap_2d_cached(B, N, K, ldb, BN, 64);
   if (ta == nullptr || tb == nullptr) return -3;
 
-  GemmParams p;
+  GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.ldc = ldc; p.ldr = ldr;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.R = static_cast<const __nv_bfloat16*>(R);
   p.ws = static_cast<float*>(ws);
+  p.rope_cos = static_cast<const float*>(rope_cos);
+  p.rope_sin = static_cast<const float*>(rope_sin);
+  p.rope_cols = rope_cols; p.rope_d = rope_d; p.rope_b = rope_b;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.kblocks_total = (K + BK - 1) / BK;
@@ -485,7 +524,7 @@ extern "C" int gfs_gemm_bf16_splitk_static(const void* A, const void* B, void* C
     if (gfs_host::encode_tmap_bf16(&tb, B, 2, dims_b, strides_b, box_b) != 0) return GFS_NO_ALLOC_ERR_TENSOR_MAP;
   }
 
-  GemmParams p;
+  GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.ldc = ldc; p.ldr = ldr;
   p.C = static_cast<__nv_bfloat16*>(C);

@@ -17,5 +17,5 @@ class RMSNorm(nn.Module):
         # replicated across TP ranks: its gradient is summed over the TP group by the optimizer
         self.weight.tp_replicated = True
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return rmsnorm(x, self.weight, self.eps, GradSink.of(self.weight))
+    def forward(self, x: torch.Tensor, fork: bool = False):
+        return rmsnorm(x, self.weight, self.eps, GradSink.of(self.weight), fork)

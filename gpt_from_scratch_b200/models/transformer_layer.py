@@ -9,8 +9,8 @@ the reference's CLI can reach) the residual adds run inside the row-parallel GEM
 """
 from __future__ import annotations
 
+import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops.attention import attention_reference, fused_rope_attention
 from ..ops.rope import rope_reference
@@ -42,12 +42,24 @@ class ParallelAttention(nn.Module):
         self.attention_impl = getattr(config, "attention_impl", "fused")
 
     def forward(self, hidden_states, residual=None):
-        qkv = self.qkv_proj(hidden_states)                 # [S, B, 3H/P]
-        S, B, W = qkv.shape
         nh, D = self.num_heads_per_partition, self.head_dim
-        cos, sin = self.rotary_emb(qkv, S)
+        world = ps.get_tensor_model_parallel_world_size()
+        S_full, B_ = hidden_states.shape[0] * world, hidden_states.shape[1]
+        w = self.qkv_proj.weight
+        rope_in_gemm = (self.attention_impl == "fused" and w.is_cuda and w.dtype == hidden_states.dtype ==
+                        torch.bfloat16 and D in (64, 128) and self.qkv_proj.bias is None)
+        if rope_in_gemm:
+            # q and k are rotated by the projection GEMM's epilogue
+            cos, sin = self.rotary_emb(hidden_states, S_full)
+            qkv = self.qkv_proj(hidden_states, rope=(cos, sin, 2 * nh * D, D, B_))
+        else:
+            qkv = self.qkv_proj(hidden_states)             # [S, B, 3H/P]
+        S, B, W = qkv.shape
+        if not rope_in_gemm:
+            cos, sin = self.rotary_emb(qkv, S)
         if self.attention_impl == "fused":
-            ctx = fused_rope_attention(qkv.reshape(S * B, W), cos, sin, S, B, nh, D).view(S, B, nh * D)
+            ctx = fused_rope_attention(qkv.reshape(S * B, W), cos, sin, S, B, nh, D,
+                                       pre_rotated=rope_in_gemm).view(S, B, nh * D)
         else:
             q, k, v = qkv.view(S, B, 3, nh, D).unbind(2)
             q, k = rope_reference(q, cos, sin), rope_reference(k, cos, sin)
@@ -69,7 +81,9 @@ class TransformerLayer(nn.Module):
 
     def forward(self, hidden_states):
         if self.dropout_prob == 0.0 or not self.training:
-            x = self.attention(self.input_norm(hidden_states), residual=hidden_states)
-            return self.mlp(self.post_attention_norm(x), residual=x)
+            h, res = self.input_norm(hidden_states, fork=True)
+            x = self.attention(h, residual=res)
+            h, res = self.post_attention_norm(x, fork=True)
+            return self.mlp(h, residual=res)
         x = hidden_states + self.dropout(self.attention(self.input_norm(hidden_states)))
         return x + self.dropout(self.mlp(self.post_attention_norm(x)))

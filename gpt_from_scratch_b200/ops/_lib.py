@@ -74,7 +74,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_adamw_step": ([vp, vp, vp, vp, vp, i64, vp, vp, f, f, f, f, f, f, f, f, f, vp], i),
         "gfs_wait_probe": ([vp, i64, vp], i),
         "gfs_flash_fwd": ([vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
-        "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
+        "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
+        "gfs_gemm_bf16_rope": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, vp, sz, i, vp, vp, i, i, i, vp], i),
     }
     for name, (argtypes, restype) in sigs.items():
         fn = getattr(lib, name, None)

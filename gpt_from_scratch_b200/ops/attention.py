@@ -56,14 +56,17 @@ def flash_fwd_native(q, k, v, out, causal: bool, scale: float) -> torch.Tensor:
     return lse
 
 
-def flash_bwd_native(q, k, v, out, dout, lse, dq, dk, dv, causal: bool, scale: float) -> None:
+def flash_bwd_native(q, k, v, out, dout, lse, dq, dk, dv, causal: bool, scale: float, rope=None) -> None:
+    """``rope = (cos, sin)``: dq and dk are rotated back (inverse RoPE) as they are written."""
     S, B, nh, D = q.shape
     dvec = torch.empty_like(lse)
     st = (ctypes.c_longlong * 24)(*_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out), *_strides3(dout),
                                   *_strides3(dq), *_strides3(dk), *_strides3(dv))
     rc = _lib.lib().gfs_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
                                   lse.data_ptr(), dvec.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                  S, B, nh, D, st, scale, 1 if causal else 0, _lib.stream_ptr())
+                                  S, B, nh, D, st, scale, 1 if causal else 0,
+                                  rope[0].data_ptr() if rope else 0, rope[1].data_ptr() if rope else 0,
+                                  _lib.stream_ptr())
     _lib.check(rc, "gfs_flash_bwd")
     _lib.add_launches(2)  # pre-pass + two main kernels
 
@@ -106,9 +109,10 @@ def apply_flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal_m
 
 class _FusedRopeAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv2d, cos, sin, S, B, nh, D):
+    def forward(ctx, qkv2d, cos, sin, S, B, nh, D, pre_rotated):
         qkv = qkv2d.view(S, B, 3, nh, D)
-        rope_inplace_native(qkv, cos, sin, S, B, nh, D, parts=2, token_stride=3 * nh * D, backward=False)
+        if not pre_rotated:
+            rope_inplace_native(qkv, cos, sin, S, B, nh, D, parts=2, token_stride=3 * nh * D, backward=False)
         out = torch.empty((S, B, nh, D), dtype=qkv2d.dtype, device=qkv2d.device)
         scale = 1.0 / math.sqrt(D)
         lse = flash_fwd_native(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out, True, scale)
@@ -123,21 +127,24 @@ class _FusedRopeAttention(torch.autograd.Function):
         qkv = qkv2d.view(S, B, 3, nh, D)
         dout = dout2d.contiguous().view(S, B, nh, D)
         dqkv = torch.empty_like(qkv)
+        # the inverse rotation of dq / dk happens in the backward kernels' epilogues
         flash_bwd_native(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out, dout, lse,
-                         dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2], True, scale)
-        rope_inplace_native(dqkv, cos, sin, S, B, nh, D, parts=2, token_stride=3 * nh * D, backward=True)
-        return dqkv.view(S * B, 3 * nh * D), None, None, None, None, None, None
+                         dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2], True, scale, rope=(cos, sin))
+        return dqkv.view(S * B, 3 * nh * D), None, None, None, None, None, None, None
 
 
 def fused_rope_attention(qkv2d: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, S: int, B: int, nh: int,
-                         D: int) -> torch.Tensor:
+                         D: int, pre_rotated: bool = False) -> torch.Tensor:
     """RoPE on q,k + causal attention from the packed ``[S*B, 3*nh*D]`` projection output.
 
     ``cos``/``sin`` are fp32 ``[>=S, D/2]`` tables. On CUDA bf16 the input buffer is
-    rotated in place (it is an intermediate owned by the caller's projection).
+    rotated in place (it is an intermediate owned by the caller's projection), unless
+    ``pre_rotated`` says the producing GEMM already rotated q and k in its epilogue; either
+    way the returned gradient is w.r.t. the un-rotated projection output.
     """
     if qkv2d.is_cuda and qkv2d.dtype == torch.bfloat16 and D in (64, 128):
-        return _FusedRopeAttention.apply(qkv2d.contiguous(), cos, sin, S, B, nh, D)
+        return _FusedRopeAttention.apply(qkv2d.contiguous(), cos, sin, S, B, nh, D, pre_rotated)
+    assert not pre_rotated, "pre_rotated inputs exist only on the native path"
     qkv = qkv2d.view(S, B, 3, nh, D)
     q, k, v = qkv.unbind(2)
     q = rope_reference(q, cos[:S], sin[:S])

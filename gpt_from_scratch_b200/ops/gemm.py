@@ -40,11 +40,14 @@ def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
               out: torch.Tensor | None = None, addend: torch.Tensor | None = None,
-              force_split: int = 0) -> torch.Tensor:
+              force_split: int = 0, rope: tuple | None = None) -> torch.Tensor:
     """``out[M,N] = op(a) @ op(b) (+ addend)`` with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (K-major) or ``[K,M]`` (``a_mn_major``); ``b`` is ``[N,K]``
     (K-major) or ``[K,N]`` (``b_mn_major``). ``addend`` may alias ``out``.
+    ``rope = (cos, sin, rope_cols, head_dim, batch)`` rotates the first ``rope_cols`` output
+    columns in the epilogue (fp32 tables ``[positions, head_dim/2]``; row ``r`` is position
+    ``r // batch``).
     """
     a = _rowmajor_2d(a)
     b = _rowmajor_2d(b)
@@ -61,21 +64,34 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_m
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     assert out.shape == (M, N) and out.stride(1) == 1
     ws = _workspace(a.device)
-    rc = _lib.lib().gfs_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(addend),
-        M, N, K, a.stride(0), b.stride(0), out.stride(0),
-        addend.stride(0) if addend is not None else 0,
-        1 if a_mn_major else 0, 1 if b_mn_major else 0, 1 if addend is not None else 0,
-        ws.data_ptr(), ws.numel() * 4, force_split, _lib.stream_ptr())
+    if rope is None:
+        rc = _lib.lib().gfs_gemm_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(addend),
+            M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            addend.stride(0) if addend is not None else 0,
+            1 if a_mn_major else 0, 1 if b_mn_major else 0, 1 if addend is not None else 0,
+            ws.data_ptr(), ws.numel() * 4, force_split, _lib.stream_ptr())
+    else:
+        cos, sin, rope_cols, head_dim, batch = rope
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape[1] == head_dim // 2 and cos.shape[0] * batch >= M
+        rc = _lib.lib().gfs_gemm_bf16_rope(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(addend),
+            M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            addend.stride(0) if addend is not None else 0,
+            1 if a_mn_major else 0, 1 if b_mn_major else 0, 1 if addend is not None else 0,
+            ws.data_ptr(), ws.numel() * 4, force_split, cos.data_ptr(), sin.data_ptr(), rope_cols, head_dim, batch,
+            _lib.stream_ptr())
     _lib.check(rc, "gfs_gemm_bf16")
     return out
 
 
 def linear_fwd(x2d: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x2d[M,K] @ w[N,K]^T (+ residual[M,N])``."""
+               out: torch.Tensor | None = None, rope: tuple | None = None) -> torch.Tensor:
+    """``x2d[M,K] @ w[N,K]^T (+ residual[M,N])``; ``rope`` only on the native path."""
     if use_native(x2d, w):
-        return gemm_bf16(x2d, w, out=out, addend=residual)
+        return gemm_bf16(x2d, w, out=out, addend=residual, rope=rope)
+    assert rope is None, "the rotary epilogue exists only in the native GEMM"
     y = x2d @ w.t()
     if residual is not None:
         y = y + residual

@@ -22,7 +22,7 @@ def _parts(rows: int) -> int:
 
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, eps, grad_sink):
+    def forward(ctx, x, w, eps, grad_sink, fork):
         H = x.shape[-1]
         x2 = x.contiguous().view(-1, H)
         rows = x2.shape[0]
@@ -34,10 +34,15 @@ class _RMSNorm(torch.autograd.Function):
         ctx.save_for_backward(x2, w, rstd)
         ctx.grad_sink = grad_sink
         ctx.xshape = x.shape
+        ctx.fork = fork
+        if fork:
+            # second output: the input itself, to be used as the residual branch, so that the
+            # gradient arriving on that branch is added inside the backward kernel
+            return y.view(x.shape), x
         return y.view(x.shape)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x2, w, rstd = ctx.saved_tensors
         rows, H = x2.shape
         dy2 = dy.contiguous().view(rows, H)
@@ -49,16 +54,23 @@ class _RMSNorm(torch.autograd.Function):
             dw, acc = sink.target(), sink.consume_accumulate()
         else:
             dw, acc = torch.empty_like(w), False
-        rc = _lib.lib().gfs_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), rstd.data_ptr(), 0,
+        dres_ptr = 0
+        if dres is not None:
+            dres = dres.contiguous().view(rows, H)
+            dres_ptr = dres.data_ptr()
+        rc = _lib.lib().gfs_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres_ptr,
                                         dx.data_ptr(), dw.data_ptr(), partial.data_ptr(), rows, H, 1 if acc else 0,
                                         _lib.stream_ptr())
         _lib.check(rc, "gfs_rmsnorm_bwd")
         _lib.add_launches(1)
-        return dx.view(ctx.xshape), (None if sink is not None else dw), None, None
+        return dx.view(ctx.xshape), (None if sink is not None else dw), None, None, None
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, grad_sink=None) -> torch.Tensor:
-    """``grad_sink``: optional :class:`GradSink` that receives the weight gradient in place."""
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, grad_sink=None, fork: bool = False):
+    """``grad_sink``: optional :class:`GradSink` that receives the weight gradient in place.
+    ``fork=True`` returns ``(y, x)``: use the second value as the residual-branch input and the
+    backward kernel adds that branch's gradient to ``dx`` itself (no separate add kernel)."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
-        return _RMSNorm.apply(x, w, eps, grad_sink)
-    return rmsnorm_reference(x, w, eps)
+        return _RMSNorm.apply(x, w, eps, grad_sink, fork)
+    y = rmsnorm_reference(x, w, eps)
+    return (y, x) if fork else y

@@ -55,11 +55,11 @@ class _LinearFn(torch.autograd.Function):
     to a :class:`GradSink`."""
 
     @staticmethod
-    def forward(ctx, x, weight, residual, sink):
+    def forward(ctx, x, weight, residual, sink, rope=None):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         res2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
-        y2 = gemm_ops.linear_fwd(x2, weight, res2)
+        y2 = gemm_ops.linear_fwd(x2, weight, res2, rope=rope)
         ctx.save_for_backward(x2, weight)
         ctx.sink = sink
         ctx.has_res = residual is not None
@@ -84,11 +84,15 @@ class _LinearFn(torch.autograd.Function):
         elif ctx.needs_input_grad[1]:
             dw = gemm_ops.linear_wgrad(dy2, x2)
         dres = dy if ctx.has_res else None
-        return dx, dw, dres, None
+        return dx, dw, dres, None, None
 
 
-def linear_with_sink(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-    return _LinearFn.apply(x, weight, residual, GradSink.of(weight))
+def linear_with_sink(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
+                     rope: tuple | None = None) -> torch.Tensor:
+    """``rope``: rotary epilogue of the native GEMM. Its inverse is NOT applied by this
+    function's backward: the caller's next operator must return gradients w.r.t. the
+    un-rotated output (the fused attention backward does)."""
+    return _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope)
 
 
 class ColumnParallelLinear(nn.Module):
@@ -113,14 +117,14 @@ class ColumnParallelLinear(nn.Module):
         ColumnParallelLinear._salt += 1
         _init_sharded(self.weight, init_method, ColumnParallelLinear._salt)
 
-    def forward(self, input_):
+    def forward(self, input_, rope=None):
         world = ps.get_tensor_model_parallel_world_size()
         if world > 1 and ps.get_comm_impl() == "fused" and input_.is_cuda:
             from . import fused_comm
-            out = fused_comm.allgather_linear(input_, self.weight)
+            out = fused_comm.allgather_linear(input_, self.weight, rope=rope)
         else:
             full = mappings.gather_from_sequence_parallel_region(input_)
-            out = linear_with_sink(full, self.weight)
+            out = linear_with_sink(full, self.weight, rope=rope)
         if self.bias is not None:
             out = out + self.bias
         return out

@@ -69,3 +69,20 @@ def test_gemm_strided_views(cuda_device):
     gemm_bf16(a, b, out=out)
     _check(out, a.float() @ b.float().t(), 512)
     assert big_c[:, :640].abs().max().item() == 0
+
+
+def test_gemm_rope_epilogue(cuda_device):
+    """Rotary embedding applied by the GEMM epilogue to the q and k thirds of a qkv projection."""
+    from gpt_from_scratch_b200.ops.gemm import gemm_bf16
+    from gpt_from_scratch_b200.ops.rope import rope_reference
+    S, B, nh, D, K = 64, 3, 4, 64, 256
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(S * B, K, device=cuda_device, generator=g).bfloat16()
+    w = (torch.randn(3 * nh * D, K, device=cuda_device, generator=g) * 0.05).bfloat16()
+    ang = torch.rand(S, D // 2, device=cuda_device, generator=g) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    out = gemm_bf16(x, w, rope=(cos, sin, 2 * nh * D, D, B))
+    ref = (x.float() @ w.float().t()).view(S, B, 3, nh, D)
+    q, k, v = ref.unbind(2)
+    ref = torch.stack((rope_reference(q, cos, sin), rope_reference(k, cos, sin), v), dim=2).view(S * B, -1)
+    _check(out, ref, K)
