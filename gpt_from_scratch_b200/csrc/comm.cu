@@ -1,0 +1,394 @@
+// Collectives done by our own kernels over peer memory (NVLink / NVSwitch), fused with the
+// elementwise work around them. Buffers are symmetric allocations: every rank passes the
+// table of all ranks' pointers. Signalling uses monotonically growing uint32 counters in
+// the destination's memory (flags[dst][src]) and host-tracked cumulative targets; every
+// wait is bounded and reports STATUS_TIMEOUT_PEER_FLAG instead of hanging.
+//
+//   gfs_symm_barrier        cross-rank barrier (used sparingly, e.g. once per optimizer step)
+//   gfs_allgather           push-style all-gather of a row block
+//   gfs_embedding_scatter   vocab-parallel embedding lookup whose rows are written straight
+//                           into the sequence-shard owner's output (lookup + reduce-scatter)
+//   gfs_ce_exchange         vocab-parallel cross entropy: exchange of (max, sum-exp, target
+//                           logit) and the combine into lse / loss, replacing two all-reduces
+//   gfs_dp_reduce_norm      data-parallel gradient reduce-scatter by peer loads + squared-norm partial
+//   gfs_dp_adam_gather      global-norm clip + AdamW on the fp32 shard + bf16 parameter
+//                           all-gather by peer stores
+//
+// Reference counterparts: the NCCL calls in core/tensor_parallel/mappings.py:22,35,
+// core/tensor_parallel/loss.py:15,45, core/tensor_parallel/layers.py:134 and
+// core/optimizer.py:81,95,101.
+#include <algorithm>
+
+#include "common.cuh"
+
+using namespace gfs;
+
+namespace {
+
+constexpr int MAX_PEERS = 8;
+
+struct PeerTable {
+  void* buf[MAX_PEERS];
+  uint32_t* flags[MAX_PEERS];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+// Every CTA signals each destination once, then waits until each source has signalled
+// `target` times in total. Called by all threads of the CTA after their stores.
+__device__ __forceinline__ void cta_signal_all_and_wait(const PeerTable& t, int world, int rank, int slot0,
+                                                        uint32_t target, unsigned long long wait_ns,
+                                                        uint32_t* status) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) red_release_sys_add_u32(t.flags[threadIdx.x] + slot0 + rank, 1u);
+  if (threadIdx.x < world)
+    wait_flag_reached(t.flags[rank] + slot0 + threadIdx.x, target, wait_ns, status,
+                      0xC0000000u | (slot0 << 8) | (threadIdx.x << 4) | rank);
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+__global__ void symm_barrier_kernel(PeerTable t, int world, int rank, int slot0, uint32_t target,
+                                    unsigned long long wait_ns, uint32_t* status) {
+  cta_signal_all_and_wait(t, world, rank, slot0, target, wait_ns, status);
+}
+
+// ---------------------------------------------------------------------------
+// All-gather: src [rows, cols] (pitch ld) -> rows [rank*rows, (rank+1)*rows) of every rank's buffer.
+__global__ void allgather_kernel(PeerTable t, const __nv_bfloat16* __restrict__ src, int rows, int cols, int ld,
+                                 int world, int rank, int slot0, uint32_t target, unsigned long long wait_ns,
+                                 uint32_t* status) {
+  const int vpr = cols >> 3;
+  const size_t total = static_cast<size_t>(rows) * vpr;
+  for (int i = 0; i < world; ++i) {
+    const int peer = (rank + i) % world;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(t.buf[peer]) + static_cast<size_t>(rank) * rows * cols;
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
+         v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      const size_t row = v / vpr;
+      const int col = static_cast<int>(v % vpr) << 3;
+      *reinterpret_cast<uint4*>(dst + row * cols + col) = *reinterpret_cast<const uint4*>(src + row * ld + col);
+    }
+  }
+  cta_signal_all_and_wait(t, world, rank, slot0, target, wait_ns, status);
+}
+
+// ---------------------------------------------------------------------------
+// Embedding: ids [B, S]; this rank owns vocabulary rows [v0, v1). For every token whose id
+// it owns it writes the embedding row into the output shard of the rank that owns the
+// token's sequence position: out_p[(s - p*S_shard), b, :]. Each output row is written by
+// exactly one rank, so the "reduce" of the reference's reduce-scatter needs no additions.
+__global__ void embedding_scatter_kernel(PeerTable t, const long long* __restrict__ ids,
+                                         const __nv_bfloat16* __restrict__ W, int B, int S, int H, int v0, int v1,
+                                         int world, int rank, int slot0, uint32_t target,
+                                         unsigned long long wait_ns, uint32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int S_shard = S / world;
+  const int nvec = H >> 3;
+  const long long total = static_cast<long long>(S) * B;
+  for (long long tok = blockIdx.x * static_cast<long long>(warps_per_cta) + (threadIdx.x >> 5); tok < total;
+       tok += static_cast<long long>(gridDim.x) * warps_per_cta) {
+    const int s = static_cast<int>(tok / B);
+    const int b = static_cast<int>(tok % B);
+    const long long id = ids[static_cast<size_t>(b) * S + s];
+    if (id < v0 || id >= v1) continue;
+    const int owner = s / S_shard;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(t.buf[owner]) +
+                         (static_cast<size_t>(s - owner * S_shard) * B + b) * H;
+    const __nv_bfloat16* src = W + static_cast<size_t>(id - v0) * H;
+    for (int v = lane; v < nvec; v += 32)
+      *reinterpret_cast<uint4*>(dst + 8 * v) = *reinterpret_cast<const uint4*>(src + 8 * v);
+  }
+  cta_signal_all_and_wait(t, world, rank, slot0, target, wait_ns, status);
+}
+
+// ---------------------------------------------------------------------------
+// Cross entropy: stats [M, 3] of this rank -> slot `rank` of every rank's [world, M, 3]
+// buffer; after all ranks have delivered, combine into lse / loss (identical on all ranks).
+__global__ void ce_exchange_kernel(PeerTable t, const float* __restrict__ stats, float* __restrict__ lse,
+                                   float* __restrict__ loss, int M, int world, int rank, int slot0,
+                                   uint32_t target, unsigned long long wait_ns, uint32_t* status) {
+  const size_t n = static_cast<size_t>(M) * 3;
+  for (int i = 0; i < world; ++i) {
+    const int peer = (rank + i) % world;
+    float* dst = static_cast<float*>(t.buf[peer]) + static_cast<size_t>(rank) * n;
+    for (size_t k = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; k < n;
+         k += static_cast<size_t>(gridDim.x) * blockDim.x)
+      dst[k] = stats[k];
+  }
+  cta_signal_all_and_wait(t, world, rank, slot0, target, wait_ns, status);
+  const float* all = static_cast<const float*>(t.buf[rank]);
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < M; row += gridDim.x * blockDim.x) {
+    float gm = -INFINITY;
+    for (int r = 0; r < world; ++r) gm = fmaxf(gm, all[(static_cast<size_t>(r) * M + row) * 3]);
+    float gs = 0.f, tz = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const float* st = all + (static_cast<size_t>(r) * M + row) * 3;
+      gs += st[1] * __expf(st[0] - gm);
+      tz += st[2];
+    }
+    const float l = gm + __logf(gs);
+    lse[row] = l;
+    loss[row] = l - tz;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Data-parallel optimizer, phase 1: reduced[i] = sum over ranks of grad_r[s0 + i] (peer
+// loads, fp32 sum in rank order, rounded to bf16 like a bf16 reduce-scatter), plus the
+// squared norm of the reduced shard. The last CTA to finish adds the per-CTA partials in
+// index order and publishes the shard's total to every rank's norm slots.
+__global__ void __launch_bounds__(256)
+dp_reduce_norm_kernel(PeerTable grads, PeerTable norm, __nv_bfloat16* __restrict__ reduced, long long s0,
+                      long long n, int world, int rank, int slot_ready, uint32_t target_ready, int slot_norm,
+                      float* __restrict__ partials, unsigned int* __restrict__ ticket,
+                      unsigned long long wait_ns, uint32_t* status) {
+  // every rank's backward must be complete before its gradients are read
+  if (threadIdx.x < world && blockIdx.x == 0)
+    red_release_sys_add_u32(grads.flags[threadIdx.x] + slot_ready + rank, 1u);
+  if (threadIdx.x < world)
+    wait_flag_reached(grads.flags[rank] + slot_ready + threadIdx.x, target_ready, wait_ns, status,
+                      0xD1000000u | (threadIdx.x << 4) | rank);
+  __syncthreads();
+  float acc = 0.f;
+  const long long nvec = n >> 3;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      load8(static_cast<const __nv_bfloat16*>(grads.buf[r]) + s0 + 8 * v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum[e] += f[e];
+    }
+    uint4 o;
+    o.x = pack_bf16x2(sum[0], sum[1]);
+    o.y = pack_bf16x2(sum[2], sum[3]);
+    o.z = pack_bf16x2(sum[4], sum[5]);
+    o.w = pack_bf16x2(sum[6], sum[7]);
+    *reinterpret_cast<uint4*>(reduced + 8 * v) = o;
+    const float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), d = unpack_bf16x2(o.w);
+    acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+  }
+  __shared__ float sm[8];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  acc = warp_sum(acc);
+  if (lane == 0) sm[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float b = 0.f;
+    for (int i = 0; i < 8; ++i) b += sm[i];
+    partials[blockIdx.x] = b;
+    __threadfence();
+    is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    __threadfence();
+    float total = 0.f;
+    for (unsigned int i = 0; i < gridDim.x; ++i) total += reinterpret_cast<volatile float*>(partials)[i];
+    *ticket = 0u;
+    for (int r = 0; r < world; ++r) {
+      static_cast<float*>(norm.buf[r])[rank] = total;
+      red_release_sys_add_u32(norm.flags[r] + slot_norm + rank, 1u);
+    }
+  }
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_corr1, bias_corr2_sqrt;
+  float clip, grad_scale;
+};
+
+// Phase 2: wait for every rank's squared-norm, clip, AdamW on the fp32 master shard, and
+// write the bf16 parameters into every rank's parameter buffer (all-gather by peer
+// stores). Ends with a signal/wait so that when the kernel completes, this rank's own
+// parameter buffer has received all shards.
+__global__ void __launch_bounds__(256)
+dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __restrict__ reduced,
+                      float* __restrict__ master, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
+                      long long s0, long long n, int world, int rank, int slot_norm, uint32_t target_norm,
+                      int slot_param, uint32_t target_param, const float* __restrict__ extern_sumsq,
+                      float* __restrict__ norm_out, AdamArgs a, unsigned long long wait_ns, uint32_t* status) {
+  __shared__ float s_coef;
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    if (extern_sumsq != nullptr) {
+      total = *extern_sumsq;
+    } else {
+      for (int r = 0; r < world; ++r) {
+        wait_flag_reached(norm.flags[rank] + slot_norm + r, target_norm, wait_ns, status,
+                          0xD2000000u | (r << 4) | rank);
+        total += reinterpret_cast<volatile float*>(norm.buf[rank])[r];
+      }
+    }
+    const float nrm = sqrtf(total) * a.grad_scale;
+    float coef = a.grad_scale;
+    if (a.clip > 0.f && nrm > a.clip) coef *= a.clip / (nrm + 1e-6f);
+    s_coef = coef;
+    if (norm_out != nullptr && blockIdx.x == 0) *norm_out = nrm;
+  }
+  __syncthreads();
+  const float coef = s_coef;
+  const float decay = 1.f - a.lr * a.weight_decay;
+  const float step = a.lr / a.bias_corr1;
+  const float ob1 = 1.f - a.beta1, ob2 = 1.f - a.beta2;
+  const long long nvec = n >> 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint2 gr = reinterpret_cast<const uint2*>(reduced)[i];
+    float4 p = reinterpret_cast<float4*>(master)[i];
+    float4 m = reinterpret_cast<float4*>(exp_avg)[i];
+    float4 v = reinterpret_cast<float4*>(exp_avg_sq)[i];
+    const float2 g01 = unpack_bf16x2(gr.x), g23 = unpack_bf16x2(gr.y);
+    float g[4] = {g01.x * coef, g01.y * coef, g23.x * coef, g23.y * coef};
+    float* pp = &p.x; float* mm = &m.x; float* vv = &v.x;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      pp[e] *= decay;
+      mm[e] = a.beta1 * mm[e] + ob1 * g[e];
+      vv[e] = a.beta2 * vv[e] + ob2 * g[e] * g[e];
+      pp[e] -= step * (mm[e] / (sqrtf(vv[e]) / a.bias_corr2_sqrt + a.eps));
+    }
+    reinterpret_cast<float4*>(master)[i] = p;
+    reinterpret_cast<float4*>(exp_avg)[i] = m;
+    reinterpret_cast<float4*>(exp_avg_sq)[i] = v;
+    const uint2 o = make_uint2(pack_bf16x2(p.x, p.y), pack_bf16x2(p.z, p.w));
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(params.buf[r]) + s0)[i] = o;
+  }
+  cta_signal_all_and_wait(params, world, rank, slot_param, target_param, wait_ns, status);
+}
+
+int fill_table(PeerTable& t, const unsigned long long* bufs, const unsigned long long* flags, int world) {
+  if (world < 1 || world > MAX_PEERS) return -1;
+  for (int i = 0; i < MAX_PEERS; ++i) {
+    t.buf[i] = i < world && bufs ? reinterpret_cast<void*>(bufs[i]) : nullptr;
+    t.flags[i] = i < world && flags ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
+  }
+  return 0;
+}
+
+unsigned long long limit_of(long long wait_ns) {
+  return wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : 20000000000ull;
+}
+
+int resident_grid(int want) { return std::max(1, std::min(want, gfs_host::sm_count() * 2)); }
+
+}  // namespace
+
+extern "C" {
+
+// In every function: peer_bufs / peer_flags are host arrays of `world` device pointers (this
+// rank's entry included); slot0 is the first of `world` consecutive uint32 counters reserved
+// for the call site inside each rank's flag array; *target_inout is the cumulative count and
+// is advanced by the call (identically on all ranks). Grids are sized so that all CTAs are
+// co-resident, because CTAs wait for signals produced by other GPUs' CTAs.
+
+int gfs_symm_barrier(const unsigned long long* peer_flags, int world, int rank, int slot0,
+                     unsigned int* target_inout, long long wait_ns, void* stream) {
+  PeerTable t;
+  if (fill_table(t, nullptr, peer_flags, world)) return -1;
+  *target_inout += 1;
+  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, world, rank, slot0, *target_inout,
+                                                                      limit_of(wait_ns), gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_allgather(const void* src, int rows, int cols, int ld, const unsigned long long* peer_bufs,
+                  const unsigned long long* peer_flags, int world, int rank, int slot0, unsigned int* target_inout,
+                  long long wait_ns, void* stream) {
+  PeerTable t;
+  if (fill_table(t, peer_bufs, peer_flags, world) || (cols & 7) || (ld & 7)) return -1;
+  const size_t total = static_cast<size_t>(rows) * (cols >> 3);
+  const int grid = resident_grid(static_cast<int>((total + 255) / 256));
+  *target_inout += static_cast<unsigned int>(grid);
+  allgather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, static_cast<const __nv_bfloat16*>(src), rows, cols, ld, world, rank, slot0, *target_inout, limit_of(wait_ns),
+      gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_embedding_scatter(const void* ids, const void* W, int B, int S, int H, int v0, int v1,
+                          const unsigned long long* peer_out, const unsigned long long* peer_flags, int world,
+                          int rank, int slot0, unsigned int* target_inout, long long wait_ns, void* stream) {
+  PeerTable t;
+  if (fill_table(t, peer_out, peer_flags, world) || (H & 7) || (S % world)) return -1;
+  const long long tokens = static_cast<long long>(S) * B;
+  const int grid = resident_grid(static_cast<int>((tokens + 7) / 8));
+  *target_inout += static_cast<unsigned int>(grid);
+  embedding_scatter_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, static_cast<const long long*>(ids), static_cast<const __nv_bfloat16*>(W), B, S, H, v0, v1, world, rank, slot0,
+      *target_inout, limit_of(wait_ns), gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_ce_exchange(const void* stats, void* lse, void* loss, int M, const unsigned long long* peer_bufs,
+                    const unsigned long long* peer_flags, int world, int rank, int slot0,
+                    unsigned int* target_inout, long long wait_ns, void* stream) {
+  PeerTable t;
+  if (fill_table(t, peer_bufs, peer_flags, world)) return -1;
+  const int grid = resident_grid((M * 3 + 255) / 256);
+  *target_inout += static_cast<unsigned int>(grid);
+  ce_exchange_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, static_cast<const float*>(stats), static_cast<float*>(lse), static_cast<float*>(loss), M, world, rank, slot0,
+      *target_inout, limit_of(wait_ns), gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// scratch: fp32 [grid + 1] zero-initialised once (per-CTA partials followed by the ticket);
+// gfs_dp_reduce_norm_scratch_floats() gives its size.
+int gfs_dp_reduce_norm_scratch_floats() { return gfs_host::sm_count() * 2 + 8; }
+
+int gfs_dp_reduce_norm(const unsigned long long* peer_grads, const unsigned long long* peer_flags,
+                       const unsigned long long* peer_norm_slots, void* reduced, long long shard_start,
+                       long long shard_numel, int world, int rank, int slot_ready, unsigned int* target_ready_inout,
+                       int slot_norm, unsigned int* target_norm_inout, void* scratch, long long wait_ns,
+                       void* stream) {
+  PeerTable g, nm;
+  if (fill_table(g, peer_grads, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
+  if ((shard_numel & 7) || (shard_start & 7)) return -1;
+  const int grid = resident_grid(static_cast<int>(((shard_numel >> 3) + 255) / 256));
+  *target_ready_inout += 1;
+  *target_norm_inout += 1;
+  float* partials = static_cast<float*>(scratch);
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(partials + gfs_host::sm_count() * 2 + 4);
+  dp_reduce_norm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, nm, static_cast<__nv_bfloat16*>(reduced), shard_start, shard_numel, world, rank, slot_ready,
+      *target_ready_inout, slot_norm, partials, ticket, limit_of(wait_ns), gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// extern_sumsq: device scalar with the global squared gradient norm computed elsewhere
+// (e.g. reduced over tensor-parallel ranks as well), or null to use the per-rank values
+// exchanged by gfs_dp_reduce_norm (target_norm = the value that call left in its counter).
+int gfs_dp_adam_gather(const unsigned long long* peer_params, const unsigned long long* peer_flags,
+                       const unsigned long long* peer_norm_slots, const void* reduced, void* master, void* exp_avg,
+                       void* exp_avg_sq, long long shard_start, long long shard_numel, int world, int rank,
+                       int slot_norm, unsigned int target_norm, int slot_param, unsigned int* target_param_inout,
+                       const void* extern_sumsq, void* norm_out, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, float bias_corr1, float bias_corr2_sqrt, float clip, float grad_scale,
+                       long long wait_ns, void* stream) {
+  PeerTable pr, nm;
+  if (fill_table(pr, peer_params, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
+  if ((shard_numel & 7) || (shard_start & 7)) return -1;
+  const int grid = resident_grid(static_cast<int>(((shard_numel >> 2) + 255) / 256));
+  *target_param_inout += static_cast<unsigned int>(grid);
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2_sqrt, clip, grad_scale};
+  dp_adam_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pr, nm, static_cast<const __nv_bfloat16*>(reduced), static_cast<float*>(master), static_cast<float*>(exp_avg),
+      static_cast<float*>(exp_avg_sq), shard_start, shard_numel, world, rank, slot_norm, target_norm, slot_param,
+      *target_param_inout, static_cast<const float*>(extern_sumsq), static_cast<float*>(norm_out), a,
+      limit_of(wait_ns), gfs_host::status_words());
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // extern "C"

@@ -289,6 +289,45 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ----------------------------------------------------------------------------
+// Cross-GPU flags (peer memory over NVLink). Counters only grow; a waiter compares
+// against a cumulative target kept by the host, so no flag is ever reset.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until *p has reached `target` (wrap-safe). On expiry records
+// STATUS_TIMEOUT_PEER_FLAG with `detail` and returns false.
+__device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t target, uint64_t limit_ns,
+                                                  uint32_t* status, uint32_t detail) {
+  uint32_t it = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    __nanosleep(64);
+    if (((++it) & 0x3ffu) == 0u) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        record_status(status, STATUS_TIMEOUT_PEER_FLAG, detail);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 }  // namespace gfs
 
 // ----------------------------------------------------------------------------

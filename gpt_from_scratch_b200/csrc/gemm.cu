@@ -33,6 +33,28 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int COMM_THREADS = 64;        // two extra warps in the fused-collective variants
+constexpr int MAX_PEERS = 8;
+
+enum CommMode : int { COMM_NONE = 0, COMM_ALLGATHER = 1, COMM_REDUCE_SCATTER = 2 };
+
+// Arguments of the fused collective (all-gather of A's rows before the product, or
+// reduce-scatter of the product's rows after it) over peer memory.
+struct CommParams {
+  int world, rank;
+  int rows_per_rank;                    // rows of the sharded dimension per rank (multiple of BM)
+  // all-gather: the local shard is pushed into every rank's gathered buffer
+  const __nv_bfloat16* ag_src;          // [rows_per_rank, ag_cols], pitch ag_ld
+  int ag_ld, ag_cols;
+  __nv_bfloat16* peer_buf[MAX_PEERS];   // AG: gathered [world*rows_per_rank, ag_cols]; RS: staging [world][rows_per_rank][N]
+  // reduce-scatter: out[rows_per_rank, N] = sum over ranks of their partial rows (+ residual)
+  __nv_bfloat16* rs_out;
+  const __nv_bfloat16* rs_res;
+  int rs_ld_out, rs_ld_res;
+  uint32_t* peer_flags[MAX_PEERS];      // flags[p][src]: progress of rank src's writes into rank p
+  uint32_t target;                      // value flags[rank][src] must reach in this call
+  unsigned long long wait_ns;
+};
 
 enum EpiMode : int { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL_F32 = 2 };
 
@@ -53,7 +75,31 @@ struct GemmParams {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols, rope_d, rope_b;
+  CommParams comm;
 };
+
+// Tile order. Plain: n fastest. Fused collectives walk the row chunks of the ranks in a
+// rotated order: all-gather starts with the local chunk (already in place), reduce-scatter
+// ends with it (its rows need no transfer), so remote traffic overlaps the other chunks' math.
+template <int BN, int COMM>
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& z, int& m0, int& n0, int& chunk) {
+  if (COMM == COMM_NONE) {
+    const int tiles_mn = p.tiles_m * p.tiles_n;
+    z = t / tiles_mn;
+    const int mn = t - z * tiles_mn;
+    m0 = (mn / p.tiles_n) * BM;
+    n0 = (mn % p.tiles_n) * BN;
+    chunk = 0;
+  } else {
+    const int tiles_per_chunk = (p.comm.rows_per_rank / BM) * p.tiles_n;
+    const int ci = t / tiles_per_chunk;
+    const int rem = t - ci * tiles_per_chunk;
+    chunk = (p.comm.rank + ci + (COMM == COMM_REDUCE_SCATTER ? 1 : 0)) % p.comm.world;
+    z = 0;
+    m0 = chunk * p.comm.rows_per_rank + (rem / p.tiles_n) * BM;
+    n0 = (rem % p.tiles_n) * BN;
+  }
+}
 
 template <int BN, int STAGES>
 struct SmemCfg {
@@ -64,8 +110,8 @@ struct SmemCfg {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-B alignment
 };
 
-template <bool A_MN, bool B_MN, int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <bool A_MN, bool B_MN, int BN, int STAGES, int COMM>
+__global__ void __launch_bounds__(GEMM_THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   using Cfg = SmemCfg<BN, STAGES>;
@@ -116,11 +162,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t chunk_ready = 0;  // all-gather: chunks whose arrival has been observed
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const int z = t / tiles_mn;
-        const int mn = t - z * tiles_mn;
-        const int m0 = (mn / p.tiles_n) * BM;
-        const int n0 = (mn % p.tiles_n) * BN;
+        int z, m0, n0, chunk;
+        decode_tile<BN, COMM>(p, t, z, m0, n0, chunk);
+        if (COMM == COMM_ALLGATHER && !((chunk_ready >> chunk) & 1u)) {
+          // rows of this chunk are written into our gathered buffer by rank `chunk`
+          if (!*abort_flag &&
+              !wait_flag_reached(p.comm.peer_flags[p.comm.rank] + chunk, p.comm.target, p.comm.wait_ns, p.status,
+                                 0xA6000000u | (chunk << 8) | p.comm.rank))
+            *abort_flag = 1u;
+          fence_proxy_async_global();  // peer's generic-proxy stores -> our TMA (async proxy) loads
+          chunk_ready |= 1u << chunk;
+        }
         const int kb0 = z * p.kblocks_per_split;
         const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -161,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const int z = t / tiles_mn;
+        const int z = (COMM == COMM_NONE) ? t / tiles_mn : 0;
         const int kb0 = z * p.kblocks_per_split;
         const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_split);
         mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, wctx, STATUS_TIMEOUT_TMEM_EMPTY);
@@ -193,16 +247,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const int z = t / tiles_mn;
-      const int mn = t - z * tiles_mn;
-      const int m0 = (mn / p.tiles_n) * BM;
-      const int n0 = (mn % p.tiles_n) * BN;
+      int z, m0, n0, chunk;
+      decode_tile<BN, COMM>(p, t, z, m0, n0, chunk);
       mbar_wait(&tmem_full[acc], acc_phase, wctx, STATUS_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -226,7 +278,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           } else {
-            __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
+            __nv_bfloat16* dst;
+            if (COMM == COMM_REDUCE_SCATTER) {
+              // partial rows go to their owner's staging area, slot of this (source) rank
+              dst = p.comm.peer_buf[chunk] +
+                    (static_cast<size_t>(p.comm.rank) * p.comm.rows_per_rank + (row - chunk * p.comm.rows_per_rank)) *
+                        p.N + col0;
+            } else {
+              dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
+            }
             const __nv_bfloat16* res = p.R + static_cast<size_t>(row) * p.ldr + col0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -264,12 +324,91 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      __syncwarp();  // orders every lane's (peer) stores before lane 0's release below
+      if (lane == 0) {
+        mbar_arrive(&tmem_empty[acc]);
+        if (COMM == COMM_REDUCE_SCATTER) red_release_sys_add_u32(p.comm.peer_flags[chunk] + p.comm.rank, 1u);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
       }
+    }
+  } else if (COMM == COMM_ALLGATHER) {
+    // ------------------------------ all-gather push (warps 6-7) ------------------------------
+    // Every CTA pushes its slice of the local shard into every rank's gathered buffer
+    // (own rank first), then bumps that rank's counter for this source.
+    const CommParams& c = p.comm;
+    const int ct = threadIdx.x - GEMM_THREADS;
+    const int rpc = (c.rows_per_rank + gridDim.x - 1) / gridDim.x;
+    const int r0 = min(c.rows_per_rank, static_cast<int>(blockIdx.x) * rpc);
+    const int r1 = min(c.rows_per_rank, r0 + rpc);
+    const int vpr = c.ag_cols >> 3;
+    const int nvec = (r1 - r0) * vpr;
+    for (int i = 0; i < c.world; ++i) {
+      const int peer = (c.rank + i) % c.world;
+      __nv_bfloat16* dst = c.peer_buf[peer] + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
+      for (int v = ct; v < nvec; v += COMM_THREADS * 4) {
+        uint4 tmp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int vv = v + u * COMM_THREADS;
+          if (vv < nvec) {
+            const int row = r0 + vv / vpr;
+            tmp[u] = *reinterpret_cast<const uint4*>(c.ag_src + static_cast<size_t>(row) * c.ag_ld + (vv % vpr) * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int vv = v + u * COMM_THREADS;
+          if (vv < nvec) {
+            const int row = r0 + vv / vpr;
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * c.ag_cols + (vv % vpr) * 8) = tmp[u];
+          }
+        }
+      }
+      __threadfence_system();
+      named_barrier_sync(1, COMM_THREADS);
+      if (ct == 0) red_release_sys_add_u32(c.peer_flags[peer] + c.rank, 1u);
+    }
+  } else if (COMM == COMM_REDUCE_SCATTER) {
+    // ------------------------------ reduce (warps 6-7) ------------------------------
+    // Wait until every rank (this one included) has delivered all partial tiles of our row
+    // chunk, then sum the staged partials in rank order, add the residual, round once.
+    const CommParams& c = p.comm;
+    const int ct = threadIdx.x - GEMM_THREADS;
+    bool ok = true;
+    for (int src = 0; src < c.world; ++src)
+      ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
+                             0xB5000000u | (src << 8) | c.rank) && ok;
+    if (!ok) *abort_flag = 1u;
+    const __nv_bfloat16* stage = c.peer_buf[c.rank];
+    const int vpr = p.N >> 3;
+    const size_t total = static_cast<size_t>(c.rows_per_rank) * vpr;
+    const size_t chunk_elems = static_cast<size_t>(c.rows_per_rank) * p.N;
+    for (size_t v = static_cast<size_t>(blockIdx.x) * COMM_THREADS + ct; v < total;
+         v += static_cast<size_t>(gridDim.x) * COMM_THREADS) {
+      const int row = static_cast<int>(v / vpr);
+      const int col = static_cast<int>(v % vpr) << 3;
+      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int src = 0; src < c.world; ++src) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + src * chunk_elems + static_cast<size_t>(row) * p.N + col);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
+      }
+      if (c.rs_res != nullptr) {
+        const uint4 u = *reinterpret_cast<const uint4*>(c.rs_res + static_cast<size_t>(row) * c.rs_ld_res + col);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc8[0], acc8[1]);
+      o.y = pack_bf16x2(acc8[2], acc8[3]);
+      o.z = pack_bf16x2(acc8[4], acc8[5]);
+      o.w = pack_bf16x2(acc8[6], acc8[7]);
+      *reinterpret_cast<uint4*>(c.rs_out + static_cast<size_t>(row) * c.rs_ld_out + col) = o;
     }
   }
 
@@ -312,10 +451,10 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16
   }
 }
 
-template <bool A_MN, bool B_MN, int BN, int STAGES>
+template <bool A_MN, bool B_MN, int BN, int STAGES, int COMM = COMM_NONE>
 int launch_variant(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = SmemCfg<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, STAGES>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, STAGES, COMM>;
   static bool attr_set = false;
   static int attr_dev = -1;
   int dev = 0;
@@ -325,7 +464,7 @@ int launch_variant(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParam
     attr_set = true;
     attr_dev = dev;
   }
-  kern<<<grid, GEMM_THREADS, Cfg::TOTAL, stream>>>(*ta, *tb, p);
+  kern<<<grid, GEMM_THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), Cfg::TOTAL, stream>>>(*ta, *tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -441,6 +580,93 @@ int gfs_gemm_bf16_rope(const void* A, const void* B, void* C, const void* R, int
     if (cudaGetLastError() != cudaSuccess) return -12;
   }
   return 0;
+}
+
+// Fused collective + GEMM over peer memory (one kernel, no NCCL):
+//   mode 1 (all-gather -> GEMM): `a` is this rank's shard [M/world, K]; every rank's kernel
+//     pushes its shard into all gathered buffers (peer_bufs[p] = rank p's [M, K] buffer) while
+//     its tensor cores already work on the chunks that have arrived; out = gathered @ op(B) -> [M, N].
+//   mode 2 (GEMM -> reduce-scatter): `a` is the full [M, K] operand; partial output rows are
+//     stored straight into their owner's staging area (peer_bufs[p] = rank p's [world, M/world, N])
+//     and the owner sums them (+ residual) into out [M/world, N].
+// peer_flags[p] = rank p's uint32 counters for this call site (>= world entries, zero at start,
+// never reset); *target_inout is the cumulative value the counters must reach: the function
+// advances it by this call's increment, identically on every rank.
+// A is K-major; B is [N, K] or, with b_mn_major, [K, N]. M/world must be a multiple of 128.
+int gfs_gemm_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
+                       const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
+                       const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
+                       unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
+                       int rope_d, int rope_b, long long wait_ns, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (mode != COMM_ALLGATHER && mode != COMM_REDUCE_SCATTER) return -1;
+  if (world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return -1;
+  if (M <= 0 || N <= 0 || K <= 0 || (M % world) != 0 || ((M / world) % BM) != 0) return -1;
+  if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
+  const int rows_per_rank = M / world;
+  const int BN = (N > 128) ? 256 : 128;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.kblocks_total = (K + BK - 1) / BK;
+  p.kblocks_per_split = p.kblocks_total;
+  p.split_k = 1;
+  p.epi_mode = EPI_STORE;
+  p.status = gfs_host::status_words();
+  p.rope_cos = static_cast<const float*>(rope_cos);
+  p.rope_sin = static_cast<const float*>(rope_sin);
+  p.rope_cols = rope_cols; p.rope_d = rope_d; p.rope_b = rope_b > 0 ? rope_b : 1;
+  CommParams& c = p.comm;
+  c.world = world; c.rank = rank; c.rows_per_rank = rows_per_rank;
+  c.wait_ns = wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : 20000000000ull;
+  for (int i = 0; i < world; ++i) {
+    c.peer_buf[i] = reinterpret_cast<__nv_bfloat16*>(peer_bufs[i]);
+    c.peer_flags[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+  }
+  const int sms = gfs_host::sm_count();
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = std::min(tiles, sms);
+  const void* a_base;
+  int a_ld;
+  if (mode == COMM_ALLGATHER) {
+    c.ag_src = static_cast<const __nv_bfloat16*>(a);
+    c.ag_ld = lda;
+    c.ag_cols = K;
+    a_base = c.peer_buf[rank];   // the GEMM reads the local gathered buffer
+    a_ld = K;
+    p.C = static_cast<__nv_bfloat16*>(out);
+    p.ldc = ldo;
+    *target_inout += static_cast<unsigned int>(grid);   // every CTA of a source signals once per destination
+  } else {
+    a_base = a;
+    a_ld = lda;
+    c.rs_out = static_cast<__nv_bfloat16*>(out);
+    c.rs_ld_out = ldo;
+    c.rs_res = static_cast<const __nv_bfloat16*>(residual);
+    c.rs_ld_res = ldr;
+    *target_inout += static_cast<unsigned int>((rows_per_rank / BM) * p.tiles_n * 4);  // 4 epilogue warps per tile
+  }
+  c.target = *target_inout;
+  if ((reinterpret_cast<uintptr_t>(a_base) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return -2;
+  const CUtensorMap* ta = gfs_host::tmap_2d_cached(a_base, M, K, a_ld, BM, 64);
+  const CUtensorMap* tb = b_mn_major ? gfs_host::tmap_2d_cached(B, K, N, ldb, 64, 64)
+                                     : gfs_host::tmap_2d_cached(B, N, K, ldb, BN, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+  int rc;
+  if (mode == COMM_ALLGATHER) {
+    if (BN == 256) rc = b_mn_major ? launch_variant<false, true, 256, 4, COMM_ALLGATHER>(ta, tb, p, grid, stream)
+                                   : launch_variant<false, false, 256, 4, COMM_ALLGATHER>(ta, tb, p, grid, stream);
+    else rc = b_mn_major ? launch_variant<false, true, 128, 6, COMM_ALLGATHER>(ta, tb, p, grid, stream)
+                         : launch_variant<false, false, 128, 6, COMM_ALLGATHER>(ta, tb, p, grid, stream);
+  } else {
+    if (BN == 256) rc = b_mn_major ? launch_variant<false, true, 256, 4, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream)
+                                   : launch_variant<false, false, 256, 4, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream);
+    else rc = b_mn_major ? launch_variant<false, true, 128, 6, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream)
+                         : launch_variant<false, false, 128, 6, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream);
+  }
+  return rc;
 }
 
 // Number of kernels gfs_gemm_bf16 launches for this problem (1, or 2 with split-K).

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from ..parallel.layers import ColumnParallelLinear, VocabParallelEmbedding
+from ..parallel.layers import ColumnParallelLinear, VocabParallelEmbedding, reset_init_salts
 from .init import get_init_method
 from .normalization import RMSNorm
 from .transformer_layer import TransformerLayer
@@ -16,6 +16,7 @@ class GPTModel(nn.Module):
     def __init__(self, config):
         super().__init__()
         self.config = config
+        reset_init_salts()
         init_method = get_init_method(config)
         self.embedding = VocabParallelEmbedding(config.vocab_size, config.hidden_size, init_method=init_method)
         self.layers = nn.ModuleList([TransformerLayer(i, config) for i in range(config.num_layers)])

@@ -51,6 +51,8 @@ def available() -> bool:
 def _declare(lib: ctypes.CDLL) -> None:
     vp, i, sz, f, i64 = c_void_p, c_int, c_size_t, c_float, c_int64
     lp = POINTER(ctypes.c_longlong)
+    ulp = POINTER(ctypes.c_ulonglong)
+    uip = POINTER(ctypes.c_uint)
     cl = ctypes.c_long
     sigs = {
         "gfs_read_status": ([POINTER(c_uint32), i], i),
@@ -75,6 +77,17 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_wait_probe": ([vp, i64, vp], i),
         "gfs_flash_fwd": ([vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
         "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
+        "gfs_gemm_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
+                                ctypes.c_longlong, vp], i),
+        "gfs_symm_barrier": ([ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
+        "gfs_allgather": ([vp, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
+        "gfs_embedding_scatter": ([vp, vp, i, i, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
+        "gfs_ce_exchange": ([vp, vp, vp, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
+        "gfs_dp_reduce_norm_scratch_floats": ([], i),
+        "gfs_dp_reduce_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i, uip, i, uip, vp,
+                                ctypes.c_longlong, vp], i),
+        "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i,
+                                ctypes.c_uint, i, uip, vp, vp, f, f, f, f, f, f, f, f, f, ctypes.c_longlong, vp], i),
         "gfs_gemm_bf16_rope": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, vp, sz, i, vp, vp, i, i, i, vp], i),
     }
     for name, (argtypes, restype) in sigs.items():

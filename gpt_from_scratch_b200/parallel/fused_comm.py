@@ -1,0 +1,321 @@
+"""Fused compute + collective operators (``--comm-impl fused``).
+
+Each operator here replaces "NCCL collective, then (or after) a library kernel" of the
+reference with ONE of our kernels that moves the data over peer memory while it computes:
+
+* :func:`allgather_linear`      sequence-parallel all-gather -> GEMM   (column-parallel forward,
+                                row-parallel dgrad)            csrc/gemm.cu, mode 1
+* :func:`linear_reduce_scatter` GEMM -> reduce-scatter (+ residual)    (row-parallel forward,
+                                column-parallel dgrad)         csrc/gemm.cu, mode 2
+* :func:`embedding_reduce_scatter` embedding lookup written straight into the owner's
+                                sequence shard                 csrc/comm.cu
+* :func:`ce_exchange_combine`   cross-entropy statistics exchange + combine   csrc/comm.cu
+* :class:`DataParallelComm`     gradient reduce-scatter + norm, clip + AdamW + parameter
+                                all-gather                     csrc/comm.cu
+
+Reference call sites: core/tensor_parallel/mappings.py:22,35 (N1, N2),
+core/tensor_parallel/layers.py:134, core/tensor_parallel/loss.py:15,45,
+core/optimizer.py:81,95,101.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import torch
+
+from ..ops import _lib
+from ..ops import gemm as gemm_ops
+from ..ops.embedding import embedding_bwd_native
+from ..ops.grad_sink import GradSink
+from . import parallel_state as ps
+from . import symm
+
+WAIT_NS = int(float(os.environ.get("GFS_PEER_WAIT_NS", "20e9")))
+MODE_AG, MODE_RS = 1, 2
+
+
+def _site_flag_ptrs(grp: symm.SymmGroup, site: symm.Site):
+    cache = grp.__dict__.setdefault("_site_flag_ptrs", {})
+    ptrs = cache.get(site.slot0)
+    if ptrs is None:
+        ptrs = (ctypes.c_ulonglong * grp.world)(*[int(p) + 4 * site.slot0 for p in grp.flag_ptrs])
+        cache[site.slot0] = ptrs
+    return ptrs
+
+
+def _gemm_comm(mode: int, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, residual, M: int, N: int, K: int,
+               b_mn_major: bool, grp: symm.SymmGroup, buf: symm.SymmBuffer, site: symm.Site, rope=None) -> None:
+    if rope is not None:
+        cos, sin, rope_cols, head_dim, batch = rope
+        rc_args = (cos.data_ptr(), sin.data_ptr(), rope_cols, head_dim, batch)
+    else:
+        rc_args = (0, 0, 0, 0, 1)
+    rc = _lib.lib().gfs_gemm_bf16_comm(
+        mode, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
+        _lib.ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, 1 if b_mn_major else 0,
+        grp.world, grp.rank, buf.ptrs, _site_flag_ptrs(grp, site), ctypes.byref(site.target), *rc_args, WAIT_NS,
+        _lib.stream_ptr())
+    _lib.check(rc, "gfs_gemm_bf16_comm")
+
+
+def _as2d(t: torch.Tensor, cols: int) -> torch.Tensor:
+    t2 = t.reshape(-1, cols)
+    if not t2.is_contiguous() or t2.data_ptr() % 16:
+        t2 = t2.contiguous()
+    return t2
+
+
+def supported(rows_per_rank: int, *dims: int) -> bool:
+    return rows_per_rank % 128 == 0 and all(d % 8 == 0 for d in dims)
+
+
+# --------------------------------------------------------------------------- column parallel
+class _AllGatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, weight, sink, rope, site_key):
+        grp = symm.get_group("tp")
+        K = x_shard.shape[-1]
+        N = weight.shape[0]
+        x2 = _as2d(x_shard, K)
+        Ms = x2.shape[0]
+        M = Ms * grp.world
+        gathered = grp.alloc(("ag", site_key), M * K, torch.bfloat16)     # lives until backward
+        site = grp.site(("ag", site_key))
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
+        _gemm_comm(MODE_AG, x2, weight, out, None, M, N, K, False, grp, gathered, site, rope)
+        ctx.save_for_backward(weight)
+        ctx.gathered = gathered
+        ctx.sink = sink
+        ctx.dims = (M, N, K, Ms, x_shard.shape)
+        return out.view(x_shard.shape[0] * grp.world, *x_shard.shape[1:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (weight,) = ctx.saved_tensors
+        grp = symm.get_group("tp")
+        M, N, K, Ms, in_shape = ctx.dims
+        dy2 = _as2d(dy, N)
+        # dX = reduce_scatter(dY @ W): GEMM with the reduce-scatter in its epilogue
+        stage, site = grp.pooled("rs", M * K, torch.bfloat16)
+        dx = torch.empty((Ms, K), dtype=torch.bfloat16, device=dy2.device)
+        _gemm_comm(MODE_RS, dy2, weight, dx, None, M, K, N, True, grp, stage, site)
+        x_full = ctx.gathered.tensor.view(M, K)
+        sink = ctx.sink
+        dw = None
+        if sink is not None:
+            gemm_ops.linear_wgrad(dy2, x_full, out=sink.target(), accumulate=sink.consume_accumulate())
+            sink.done()
+        else:
+            dw = gemm_ops.linear_wgrad(dy2, x_full)
+        return dx.view(in_shape), dw, None, None, None
+
+
+def allgather_linear(x_shard: torch.Tensor, weight: torch.Tensor, rope=None) -> torch.Tensor:
+    """``gather_S(x_shard) @ weight^T`` with the all-gather done by the GEMM kernel."""
+    world = ps.get_tensor_model_parallel_world_size()
+    rows = x_shard.numel() // x_shard.shape[-1]
+    if not (x_shard.dtype == weight.dtype == torch.bfloat16 and supported(rows, x_shard.shape[-1], weight.shape[0])):
+        from . import mappings
+        from .layers import linear_with_sink
+        return linear_with_sink(mappings.gather_from_sequence_parallel_region(x_shard), weight, rope=rope)
+    return _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, id(weight))
+
+
+# --------------------------------------------------------------------------- row parallel
+class _LinearReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, residual, sink):
+        grp = symm.get_group("tp")
+        Kp = x.shape[-1]
+        N = weight.shape[0]
+        x2 = _as2d(x, Kp)
+        M = x2.shape[0]
+        Ms = M // grp.world
+        stage, site = grp.pooled("rs", M * N, torch.bfloat16)
+        out = torch.empty((Ms, N), dtype=torch.bfloat16, device=x2.device)
+        res2 = _as2d(residual, N) if residual is not None else None
+        _gemm_comm(MODE_RS, x2, weight, out, res2, M, N, Kp, False, grp, stage, site)
+        ctx.save_for_backward(x2, weight)
+        ctx.sink = sink
+        ctx.has_res = residual is not None
+        ctx.dims = (M, N, Kp, Ms, x.shape)
+        return out.view(x.shape[0] // grp.world, *x.shape[1:-1], N)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, weight = ctx.saved_tensors
+        grp = symm.get_group("tp")
+        M, N, Kp, Ms, in_shape = ctx.dims
+        d2 = _as2d(dout, N)
+        # dX = gather_S(dOut) @ W: all-gather fused into the dgrad GEMM; the gathered dOut is
+        # then reused by the wgrad GEMM (gathered once, used twice)
+        gathered, site = grp.pooled("agb", M * N, torch.bfloat16)
+        dx = torch.empty((M, Kp), dtype=torch.bfloat16, device=d2.device)
+        _gemm_comm(MODE_AG, d2, weight, dx, None, M, Kp, N, True, grp, gathered, site)
+        dy_full = gathered.tensor.view(M, N)
+        sink = ctx.sink
+        dw = None
+        if sink is not None:
+            gemm_ops.linear_wgrad(dy_full, x2, out=sink.target(), accumulate=sink.consume_accumulate())
+            sink.done()
+        else:
+            dw = gemm_ops.linear_wgrad(dy_full, x2)
+        return dx.view(in_shape), dw, (dout if ctx.has_res else None), None
+
+
+def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None):
+    """``reduce_scatter_S(x @ weight^T) (+ residual)`` with the reduction done by the GEMM kernel."""
+    world = ps.get_tensor_model_parallel_world_size()
+    rows = x.numel() // x.shape[-1]
+    if not (x.dtype == weight.dtype == torch.bfloat16 and rows % world == 0 and
+            supported(rows // world, x.shape[-1], weight.shape[0])):
+        from . import mappings
+        from .layers import linear_with_sink
+        out = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(x, weight))
+        return out + residual if residual is not None else out
+    return _LinearReduceScatter.apply(x, weight, residual, GradSink.of(weight))
+
+
+# --------------------------------------------------------------------------- generic all-gather
+def allgather_rows(x2d: torch.Tensor, kind: str) -> torch.Tensor:
+    """Push-style all-gather of a ``[rows, cols]`` block over the TP group -> ``[world*rows, cols]``
+    (a view of a pooled symmetric buffer, valid until two later calls of the same kind and size)."""
+    grp = symm.get_group("tp")
+    rows, cols = x2d.shape
+    buf, site = grp.pooled(kind, grp.world * rows * cols, x2d.dtype)
+    rc = _lib.lib().gfs_allgather(x2d.data_ptr(), rows, cols, x2d.stride(0), buf.ptrs, grp.flag_ptrs, grp.world,
+                                  grp.rank, site.slot0, ctypes.byref(site.target), WAIT_NS, _lib.stream_ptr())
+    _lib.check(rc, "gfs_allgather")
+    return buf.tensor.view(grp.world * rows, cols)
+
+
+# --------------------------------------------------------------------------- embedding
+class _EmbeddingReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, v0, v1, sink):
+        grp = symm.get_group("tp")
+        B, S = ids.shape
+        H = weight.shape[1]
+        Ss = S // grp.world
+        out, site = grp.pooled("emb", Ss * B * H, torch.bfloat16)
+        rc = _lib.lib().gfs_embedding_scatter(ids.data_ptr(), weight.data_ptr(), B, S, H, v0, v1, out.ptrs,
+                                              grp.flag_ptrs, grp.world, grp.rank, site.slot0,
+                                              ctypes.byref(site.target), WAIT_NS, _lib.stream_ptr())
+        _lib.check(rc, "gfs_embedding_scatter")
+        ctx.save_for_backward(ids)
+        ctx.meta = (v0, v1, sink, weight.shape, S, B, H)
+        return out.tensor.view(Ss, B, H)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        v0, v1, sink, wshape, S, B, H = ctx.meta
+        full = allgather_rows(_as2d(dout, B * H), "embb").view(S, B, H)
+        if sink is not None:
+            embedding_bwd_native(ids, full, sink.target(), v0, v1, accumulate=sink.consume_accumulate())
+            sink.done()
+            return None, None, None, None, None
+        dw = torch.zeros(wshape, dtype=dout.dtype, device=dout.device)
+        embedding_bwd_native(ids, full, dw, v0, v1, accumulate=True)
+        return None, dw, None, None, None
+
+
+def embedding_reduce_scatter(input_ids: torch.Tensor, module) -> torch.Tensor:
+    """Vocab-parallel lookup + reduce-scatter along the sequence as one kernel: every rank writes
+    the rows it owns directly into the output shard of the rank that owns the position."""
+    ids = input_ids.contiguous()
+    if ids.dtype != torch.int64:
+        ids = ids.long()
+    w = module.weight
+    return _EmbeddingReduceScatter.apply(ids, w, module.vocab_start_index, module.vocab_end_index, GradSink.of(w))
+
+
+# --------------------------------------------------------------------------- cross entropy
+def ce_exchange_combine(stats: torch.Tensor):
+    """stats ``[M, 3]`` (local max, sum-exp, target logit) -> global ``(lse, loss)``, each ``[M]``."""
+    grp = symm.get_group("tp")
+    M = stats.shape[0]
+    buf = grp.alloc(("ce", M), grp.world * M * 3, torch.float32)
+    site = grp.site(("ce", M))
+    lse = torch.empty(M, dtype=torch.float32, device=stats.device)
+    loss = torch.empty(M, dtype=torch.float32, device=stats.device)
+    rc = _lib.lib().gfs_ce_exchange(stats.data_ptr(), lse.data_ptr(), loss.data_ptr(), M, buf.ptrs, grp.flag_ptrs,
+                                    grp.world, grp.rank, site.slot0, ctypes.byref(site.target), WAIT_NS,
+                                    _lib.stream_ptr())
+    _lib.check(rc, "gfs_ce_exchange")
+    return lse, loss
+
+
+def barrier(kind: str = "tp") -> None:
+    grp = symm.get_group(kind)
+    site = grp.site("barrier")
+    rc = _lib.lib().gfs_symm_barrier(grp.flag_ptrs, grp.world, grp.rank, site.slot0, ctypes.byref(site.target),
+                                     WAIT_NS, _lib.stream_ptr())
+    _lib.check(rc, "gfs_symm_barrier")
+
+
+# --------------------------------------------------------------------------- data-parallel optimizer
+class DataParallelComm:
+    """Symmetric parameter / gradient buffers of the distributed optimizer and its two fused
+    kernels: (1) gradient reduce-scatter by peer loads + squared-norm partial, (2) global-norm
+    clip + AdamW + bf16 parameter all-gather by peer stores. No NCCL call, no host sync."""
+
+    def __init__(self, padded_numel: int, shard_size: int, device: torch.device):
+        self.grp = symm.get_group("dp")
+        g = self.grp
+        self._param = g.alloc("dp:params", padded_numel, torch.bfloat16, zero=True)
+        self._grad = g.alloc("dp:grads", padded_numel, torch.bfloat16, zero=True)
+        self._norm = g.alloc("dp:norm", 16, torch.float32, zero=True)
+        self.param_buffer = self._param.tensor
+        self.grad_buffer = self._grad.tensor
+        self.shard_size = shard_size
+        self.shard_start = shard_size * g.rank
+        self.reduced = torch.zeros(shard_size, dtype=torch.bfloat16, device=device)
+        self.norm_out = torch.zeros(1, dtype=torch.float32, device=device)
+        self.scratch = torch.zeros(_lib.lib().gfs_dp_reduce_norm_scratch_floats(), dtype=torch.float32,
+                                   device=device)
+        self.site_ready = g.site("dp:ready")
+        self.site_norm = g.site("dp:norm")
+        self.site_param = g.site("dp:param")
+
+    def reduce_and_norm(self) -> None:
+        g = self.grp
+        rc = _lib.lib().gfs_dp_reduce_norm(
+            self._grad.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), self.shard_start,
+            self.shard_size, g.world, g.rank, self.site_ready.slot0, ctypes.byref(self.site_ready.target),
+            self.site_norm.slot0, ctypes.byref(self.site_norm.target), self.scratch.data_ptr(), WAIT_NS,
+            _lib.stream_ptr())
+        _lib.check(rc, "gfs_dp_reduce_norm")
+
+    def adam_and_gather(self, master, exp_avg, exp_avg_sq, *, step, lr, beta1, beta2, eps, weight_decay, clip,
+                        grad_scale, extern_sumsq=None) -> None:
+        g = self.grp
+        bc1 = 1.0 - beta1 ** step
+        bc2_sqrt = math.sqrt(1.0 - beta2 ** step)
+        rc = _lib.lib().gfs_dp_adam_gather(
+            self._param.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), master.data_ptr(),
+            exp_avg.data_ptr(), exp_avg_sq.data_ptr(), self.shard_start, self.shard_size, g.world, g.rank,
+            self.site_norm.slot0, self.site_norm.target.value, self.site_param.slot0,
+            ctypes.byref(self.site_param.target), _lib.ptr(extern_sumsq), self.norm_out.data_ptr(),
+            lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, clip, grad_scale, WAIT_NS, _lib.stream_ptr())
+        _lib.check(rc, "gfs_dp_adam_gather")
+
+    def step(self, opt, state, *, step, lr, beta1, beta2, eps, weight_decay, clip, grad_scale) -> None:
+        self.reduce_and_norm()
+        extern = None
+        if opt.tp_world_size > 1 and not opt.reference_quirks and clip > 0:
+            # global norm over TP x DP with replicated parameters counted once: the tiny
+            # cross-TP part goes through torch.distributed
+            local = opt._sumsq
+            from ..ops import adam as adam_ops
+            adam_ops.sumsq_bf16(self.reduced, local[0:1])
+            if opt._rep_index_shard is not None:
+                local[1] = self.reduced.index_select(0, opt._rep_index_shard).float().pow(2).sum()
+            else:
+                local[1] = 0.0
+            extern = opt._global_sumsq(local)
+        self.adam_and_gather(opt.fp32_master_shard.data, state["exp_avg"], state["exp_avg_sq"], step=step, lr=lr,
+                             beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip,
+                             grad_scale=grad_scale, extern_sumsq=extern)

@@ -41,6 +41,13 @@ def _init_sharded(weight: torch.Tensor, init_method, salt: int) -> None:
         init_method(weight)
 
 
+def reset_init_salts() -> None:
+    """Restart the per-layer salt sequence of the weight initialisers, so that two models built
+    in the same process with the same seed get identical weights."""
+    ColumnParallelLinear._salt = 0
+    RowParallelLinear._salt = 1000
+
+
 def normal_init(std: float = 0.02):
     """``normal(0, std)`` initialiser usable as ``init_method`` (deterministic per TP rank)."""
     def fn(weight, gen):

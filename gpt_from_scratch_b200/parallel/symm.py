@@ -1,10 +1,121 @@
-"""Symmetric-memory workspaces shared by the fused communication kernels (filled in by
-``fused_comm``). ``reset`` drops every cached workspace (called when the parallel state
-is destroyed)."""
+"""Symmetric-memory workspaces for the fused communication kernels.
+
+A :class:`SymmGroup` wraps one process group (TP or DP). It hands out symmetric buffers
+(``torch.distributed._symmetric_memory``: the same-size allocation on every rank, mapped
+into every peer's address space, so a kernel can load/store a peer's copy directly over
+NVLink) together with the table of all ranks' device pointers, and manages the signalling
+counters: one symmetric ``uint32`` array per group out of which every call site reserves
+``world`` consecutive slots, plus a host-side cumulative target per site. Counters are
+never reset; a waiter compares against the target, so no reset races exist.
+
+Allocation is collective: all ranks of the group must create the same buffers in the same
+order, which holds because they run the same program.
+"""
 from __future__ import annotations
 
-_workspaces: dict = {}
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+NUM_FLAG_SLOTS = 8192
+_groups: dict = {}
+
+
+class SymmBuffer:
+    __slots__ = ("tensor", "ptrs", "handle")
+
+    def __init__(self, tensor, ptrs, handle):
+        self.tensor = tensor
+        self.ptrs = ptrs          # ctypes array of `world` device pointers (this rank included)
+        self.handle = handle
+
+
+class Site:
+    """Flag slots + cumulative target of one call site."""
+    __slots__ = ("slot0", "target")
+
+    def __init__(self, slot0: int):
+        self.slot0 = slot0
+        self.target = ctypes.c_uint(0)
+
+
+class SymmGroup:
+    def __init__(self, group, world: int, rank: int, device: torch.device):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = world
+        self.rank = rank
+        self.device = device
+        self._buffers: dict = {}
+        self._sites: dict = {}
+        self._pools: dict = {}
+        self._next_slot = 0
+        flags = self.alloc("__flags__", NUM_FLAG_SLOTS, torch.int32, zero=True)
+        self.flags = flags
+        self.flag_ptrs = flags.ptrs
+        # make sure every rank has zeroed its flags before anyone signals
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
+
+    def alloc(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> SymmBuffer:
+        import torch.distributed._symmetric_memory as symm_mem
+        key = (name, numel, dtype)
+        buf = self._buffers.get(key)
+        if buf is not None:
+            return buf
+        t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+        if zero:
+            t.zero_()
+        handle = symm_mem.rendezvous(t, self.group)
+        ptrs = (ctypes.c_ulonglong * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        assert int(ptrs[self.rank]) == t.data_ptr()
+        buf = SymmBuffer(t, ptrs, handle)
+        self._buffers[key] = buf
+        return buf
+
+    def site(self, name) -> Site:
+        s = self._sites.get(name)
+        if s is None:
+            if self._next_slot + self.world > NUM_FLAG_SLOTS:
+                raise RuntimeError("out of flag slots")
+            s = Site(self._next_slot)
+            self._next_slot += self.world
+            self._sites[name] = s
+        return s
+
+    def pooled(self, kind: str, numel: int, dtype: torch.dtype):
+        """One of two alternating buffers shared by all call sites of this kind and size.
+        Two are enough: a rank can only be one collective ahead of its slowest peer, because
+        finishing a fused collective needs data that every peer produces inside the same call."""
+        key = (kind, numel, dtype)
+        st = self._pools.get(key)
+        if st is None:
+            st = {"count": 0,
+                  "bufs": [self.alloc(f"pool:{kind}:{i}", numel, dtype) for i in range(2)],
+                  "sites": [self.site(("pool", kind, numel, dtype, i)) for i in range(2)]}
+            self._pools[key] = st
+        i = st["count"] & 1
+        st["count"] += 1
+        return st["bufs"][i], st["sites"][i]
+
+
+def get_group(kind: str) -> SymmGroup:
+    """``kind``: "tp" or "dp"."""
+    from . import parallel_state as ps
+    g = _groups.get(kind)
+    if g is None:
+        dev = ps.get_device()
+        if kind == "tp":
+            g = SymmGroup(ps.get_tensor_model_parallel_group(), ps.get_tensor_model_parallel_world_size(),
+                          ps.get_tensor_model_parallel_group_rank(), dev)
+        elif kind == "dp":
+            g = SymmGroup(ps.get_data_parallel_group(), ps.get_data_parallel_world_size(),
+                          ps.get_data_parallel_group_rank(), dev)
+        else:
+            raise ValueError(kind)
+        _groups[kind] = g
+    return g
 
 
 def reset() -> None:
-    _workspaces.clear()
+    _groups.clear()

@@ -1,0 +1,169 @@
+"""Worker for the multi-GPU fused-collective tests; launched by torchrun with N ranks.
+Compares every fused operator against the NCCL + single-GPU-kernel composition on the same
+inputs, then whole training steps (TP=N, and DP=N with the fused optimizer)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gpt_from_scratch_b200.config import GPTConfig  # noqa: E402
+from gpt_from_scratch_b200.engine import TrainEngine  # noqa: E402
+from gpt_from_scratch_b200.ops import _lib  # noqa: E402
+from gpt_from_scratch_b200.parallel import fused_comm, mappings  # noqa: E402
+from gpt_from_scratch_b200.parallel import parallel_state as ps  # noqa: E402
+from gpt_from_scratch_b200.parallel.layers import VocabParallelEmbedding, linear_with_sink  # noqa: E402
+from gpt_from_scratch_b200.parallel.loss import vocab_parallel_cross_entropy  # noqa: E402
+
+
+def close(a, b, what, rel=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).norm() / (b.norm() + 1e-9)
+    mx = (a - b).abs().max().item()
+    assert err < rel, f"{what}: relative error {err:.4g}, max abs {mx:.4g}"
+    return float(err.detach())
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ps.set_device(dev)
+    ps.initialize_parallel_state(world)          # TP = world
+    log = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
+
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    S, B, K, N = 512, 2, 256, 384
+    Ss = S // world
+    # ---- all-gather -> GEMM (column parallel) ----
+    x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    dy = torch.randn(S, B, N, device=dev, generator=g).bfloat16()
+    dist.broadcast(dy, 0)   # the gradient w.r.t. a column-parallel output differs per rank in general; any value works
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    ya = fused_comm.allgather_linear(xa, wa)
+    ya.backward(dy)
+    xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+    yb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
+    yb.backward(dy)
+    torch.cuda.synchronize()
+    assert torch.equal(ya, yb), "AG->GEMM forward differs from NCCL all-gather + GEMM"
+    close(xa.grad, xb.grad, "AG->GEMM dX (GEMM->RS)")
+    close(wa.grad, wb.grad, "AG->GEMM dW", 1e-3)
+    log("allgather_linear ok")
+
+    # ---- GEMM -> reduce-scatter (row parallel) ----
+    xr = torch.randn(S, B, K, device=dev, generator=g).bfloat16()
+    wr = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    res = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+    dout = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+    for use_res in (False, True):
+        xa, wa = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+        ra = res.clone().requires_grad_() if use_res else None
+        ya = fused_comm.linear_reduce_scatter(xa, wa, ra)
+        ya.backward(dout)
+        xb, wb = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+        yb = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(xb, wb))
+        if use_res:
+            yb = yb + res
+        yb.backward(dout)
+        torch.cuda.synchronize()
+        close(ya, yb, f"GEMM->RS forward (residual={use_res})")
+        close(xa.grad, xb.grad, "GEMM->RS dX (AG->GEMM)", 1e-3)
+        close(wa.grad, wb.grad, "GEMM->RS dW", 1e-3)
+        if use_res:
+            assert torch.equal(ra.grad, dout)
+    log("linear_reduce_scatter ok")
+
+    # ---- embedding -> reduce-scatter ----
+    V, H = 1024, 256
+    ps.set_comm_impl("nccl")
+    emb = VocabParallelEmbedding(V, H)
+    emb.weight.data = emb.weight.data.bfloat16()
+    ids = torch.randint(0, V, (B, S), device=dev, generator=torch.Generator(device="cuda").manual_seed(5))
+    dsh = torch.randn(Ss, B, H, device=dev, generator=g).bfloat16()
+    out_n = emb(ids)
+    out_n.backward(dsh)
+    gw_n = emb.weight.grad.clone()
+    emb.weight.grad = None
+    ps.set_comm_impl("fused")
+    out_f = emb(ids)
+    out_f.backward(dsh)
+    torch.cuda.synchronize()
+    assert torch.equal(out_f, out_n), "embedding fused forward differs"
+    close(emb.weight.grad, gw_n, "embedding dW", 1e-3)
+    log("embedding_reduce_scatter ok")
+
+    # ---- vocab-parallel cross entropy ----
+    Vp = 512
+    logits = (torch.randn(S, B, Vp, device=dev, generator=g) * 2).bfloat16()
+    tgt = torch.randint(0, Vp * world, (S, B), device=dev, generator=torch.Generator(device="cuda").manual_seed(6))
+    outs = {}
+    for impl in ("nccl", "fused"):
+        ps.set_comm_impl(impl)
+        lg = logits.clone().requires_grad_()
+        loss = vocab_parallel_cross_entropy(lg * 1, tgt)
+        loss.mean().backward()
+        outs[impl] = (loss.detach().clone(), lg.grad.clone())
+    torch.cuda.synchronize()
+    assert (outs["fused"][0] - outs["nccl"][0]).abs().max().item() < 1e-5
+    assert torch.equal(outs["fused"][1], outs["nccl"][1])
+    log("ce_exchange_combine ok")
+
+    # ---- whole model, TP = world: fused vs NCCL composition ----
+    cfg = GPTConfig(vocab_size=2048, hidden_size=256, num_layers=2, num_attention_heads=4,
+                    max_position_embeddings=512, intermediate_size=512, init_method="normal")
+    data = [torch.randint(0, 2048, (2, 513), generator=torch.Generator().manual_seed(50 + i)) for i in range(4)]
+    traj = {}
+    for impl in ("nccl", "fused"):
+        ps.set_comm_impl(impl)
+        eng = TrainEngine(cfg, lr=1e-3, seed=3)
+        traj[impl] = [float(eng.train_step(t[:, :-1].contiguous().to(dev), t[:, 1:].contiguous().to(dev)))
+                      for t in data]
+        torch.cuda.synchronize()
+        _lib.raise_on_status()
+    log("TP losses nccl ", traj["nccl"])
+    log("TP losses fused", traj["fused"])
+    for a, b in zip(traj["fused"], traj["nccl"]):
+        assert abs(a - b) < 2e-2, (traj)
+    log("TP training ok")
+
+    # ---- DP = world with the fused distributed optimizer ----
+    ps.destroy_model_parallel()
+    ps.initialize_parallel_state(1)
+    traj = {}
+    finals = {}
+    for impl in ("nccl", "fused"):
+        ps.set_comm_impl(impl)
+        eng = TrainEngine(cfg, lr=1e-3, seed=3)
+        losses = []
+        for t in data:
+            tt = t[rank::world] if t.shape[0] >= world else t
+            losses.append(float(eng.train_step(tt[:, :-1].contiguous().to(dev), tt[:, 1:].contiguous().to(dev))))
+        traj[impl] = losses
+        finals[impl] = eng.optimizer.param_buffer.float().clone()
+        torch.cuda.synchronize()
+        _lib.raise_on_status()
+        # replicas must agree after the parameter all-gather
+        chk = finals[impl].double().sum().reshape(1)
+        allc = [torch.zeros_like(chk) for _ in range(world)]
+        dist.all_gather(allc, chk)
+        assert all(float(c) == float(allc[0]) for c in allc), f"{impl}: DP replicas diverged"
+    log("DP losses nccl ", traj["nccl"])
+    log("DP losses fused", traj["fused"])
+    for a, b in zip(traj["fused"], traj["nccl"]):
+        assert abs(a - b) < 2e-2, traj
+    close(finals["fused"], finals["nccl"], "DP final parameters", 2e-3)
+    log("DP training ok")
+    torch.cuda.synchronize()
+    dist.barrier()
+    log("WORKER OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
