@@ -154,7 +154,7 @@ def build_ours(cfgd, args, world):
     if args.comm_impl:
         ps.set_comm_impl(args.comm_impl)
     elif world > 1:
-        ps.set_comm_impl(os.environ.get("GFS_COMM_IMPL", "nccl"))
+        ps.set_comm_impl(os.environ.get("GFS_COMM_IMPL", "fused"))
     _lib.lib()
     cfg = GPTConfig(vocab_size=cfgd["vocab_size"], hidden_size=cfgd["hidden_size"], num_layers=cfgd["num_layers"],
                     num_attention_heads=cfgd["num_attention_heads"], max_position_embeddings=cfgd["seq_len"],
@@ -177,7 +177,11 @@ def build_reference(cfgd, args):
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "core")):
         return None, "baseline/_ref is missing (reference not installed)"
-    sys.path.insert(0, ref_root)
+    # the reference's `core` is a namespace package (no __init__.py); this repository's own
+    # `core/` alias package would shadow it, so the repository root leaves the import path
+    sys.path[:] = [ref_root] + [q for q in sys.path if os.path.abspath(q or ".") != REPO]
+    for name in [m for m in sys.modules if m == "core" or m.startswith("core.") or m == "train"]:
+        del sys.modules[name]
     try:
         import train as ref_train
         from core.models.gpt import GPTModel
@@ -229,6 +233,7 @@ def main():
     dp = world // tp
     B, S = cfgd["micro_batch"], cfgd["seq_len"]
 
+    from gpt_from_scratch_b200.utils.timing import ClockSampler   # timing harness only (no kernels)
     launches = None
     check = None
     comm = "nccl"
@@ -246,7 +251,6 @@ def main():
     n_batches = max(args.steps, args.warmup, 4)
     batches = make_batches(n_batches, B, S, seed=4321 + dp_rank)
 
-    from gpt_from_scratch_b200.utils.timing import ClockSampler
     timed_loop(step_fn, batches, args.warmup, "device")          # warm-up (untimed)
     if check:
         check()

@@ -1,0 +1,235 @@
+"""Single-process CPU unit tests: group math, flat-buffer layout, resharding, data loading,
+CLI, reference formulas of the operators, checkpoint round trip."""
+import math
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from gpt_from_scratch_b200.config import GPTConfig
+from gpt_from_scratch_b200.parallel import parallel_state as ps
+
+
+@pytest.fixture(autouse=True)
+def _cpu_state():
+    ps.destroy_model_parallel()
+    ps.set_device("cpu")
+    ps.initialize_parallel_state(1)
+    yield
+    ps.destroy_model_parallel()
+
+
+def test_parallel_state_single_process():
+    assert ps.get_tensor_model_parallel_world_size() == 1
+    assert ps.get_data_parallel_world_size() == 1
+    assert ps.get_tensor_model_parallel_group() is None
+    with pytest.raises(RuntimeError):
+        ps.initialize_parallel_state(2)
+
+
+def test_flops_and_param_count_match_survey_numbers():
+    cfg = GPTConfig()
+    assert abs(cfg.flops_per_token(1024) / 1e9 - 0.968) < 1e-3
+    assert abs(cfg.num_parameters() / 1e6 - 190.5) < 0.1
+    big = GPTConfig(hidden_size=4096, num_layers=32, num_attention_heads=32, intermediate_size=11008)
+    assert abs(big.flops_per_token(4096) / 1e9 - 43.3) < 0.1
+
+
+def test_state_dict_layout_matches_reference_keys():
+    from gpt_from_scratch_b200.models.gpt import GPTModel
+    cfg = GPTConfig(vocab_size=64, hidden_size=32, num_layers=2, num_attention_heads=4,
+                    max_position_embeddings=16, intermediate_size=48)
+    sd = GPTModel(cfg).state_dict()
+    expect = {"embedding.weight": (64, 32), "final_norm.weight": (32,), "output.weight": (64, 32)}
+    for i in range(2):
+        expect.update({
+            f"layers.{i}.input_norm.weight": (32,),
+            f"layers.{i}.attention.qkv_proj.weight": (96, 32),
+            f"layers.{i}.attention.out_proj.weight": (32, 32),
+            f"layers.{i}.attention.rotary_emb.freqs": (4,),
+            f"layers.{i}.post_attention_norm.weight": (32,),
+            f"layers.{i}.mlp.gate_up_proj.weight": (96, 32),
+            f"layers.{i}.mlp.down_proj.weight": (32, 48),
+        })
+    assert {k: tuple(v.shape) for k, v in sd.items()} == expect
+
+
+def test_reshard_roundtrip():
+    from gpt_from_scratch_b200.utils.reshard import merge_state_dicts, shard_state_dict
+    g = torch.Generator().manual_seed(0)
+    H, I, V, nh = 16, 24, 32, 4
+    full = {"embedding.weight": torch.randn(V, H, generator=g),
+            "layers.0.attention.qkv_proj.weight": torch.randn(3 * H, H, generator=g),
+            "layers.0.attention.out_proj.weight": torch.randn(H, H, generator=g),
+            "layers.0.mlp.gate_up_proj.weight": torch.randn(2 * I, H, generator=g),
+            "layers.0.mlp.down_proj.weight": torch.randn(H, I, generator=g),
+            "layers.0.input_norm.weight": torch.randn(H, generator=g),
+            "output.weight": torch.randn(V, H, generator=g)}
+    for P in (2, 4):
+        shards = [shard_state_dict(full, r, P) for r in range(P)]
+        # q block of rank 1 = q rows [H/P, 2H/P) of the full tensor
+        q1 = shards[1]["layers.0.attention.qkv_proj.weight"][: H // P]
+        assert torch.equal(q1, full["layers.0.attention.qkv_proj.weight"][H // P: 2 * H // P])
+        up0 = shards[0]["layers.0.mlp.gate_up_proj.weight"][I // P:]
+        assert torch.equal(up0, full["layers.0.mlp.gate_up_proj.weight"][I: I + I // P])
+        merged = merge_state_dicts(shards)
+        for k in full:
+            assert torch.equal(merged[k], full[k]), k
+
+
+def test_optimizer_flat_buffer_layout_and_padding():
+    from gpt_from_scratch_b200.models.gpt import GPTModel
+    from gpt_from_scratch_b200.optimizer import DistributedOptimizer
+    cfg = GPTConfig(vocab_size=64, hidden_size=32, num_layers=1, num_attention_heads=4,
+                    max_position_embeddings=16, intermediate_size=48)
+    model = GPTModel(cfg)
+    names = [n for n, _ in model.named_parameters()]
+    assert names == ["embedding.weight", "layers.0.input_norm.weight", "layers.0.attention.qkv_proj.weight",
+                     "layers.0.attention.out_proj.weight", "layers.0.post_attention_norm.weight",
+                     "layers.0.mlp.gate_up_proj.weight", "layers.0.mlp.down_proj.weight", "final_norm.weight",
+                     "output.weight"]
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    opt = DistributedOptimizer(model, torch.optim.AdamW, {"lr": 1e-3}, dtype=torch.float32)
+    off = 0
+    for (n, p), o in zip(model.named_parameters(), opt.param_offsets):
+        assert o == off and p.data_ptr() == opt.param_buffer[off:].data_ptr()
+        assert p.grad.data_ptr() == opt.grad_buffer[off:].data_ptr()
+        assert torch.equal(p.detach(), before[n])
+        off += p.numel()
+    assert opt.padded_numel % 8 == 0 and opt.padded_numel >= off
+    assert torch.equal(opt.fp32_master_shard.detach(), opt.param_buffer)
+    sd = opt.state_dict()
+    assert set(sd) == {"state", "param_groups"}
+
+
+def test_adamw_step_formula_and_clip():
+    """One step of the optimizer == the closed-form AdamW update with the reference's clip rule."""
+    lin = torch.nn.Linear(8, 8, bias=False)
+    from gpt_from_scratch_b200.optimizer import DistributedOptimizer
+    w0 = lin.weight.detach().clone()
+    opt = DistributedOptimizer(lin, torch.optim.AdamW, {"lr": 0.1, "weight_decay": 0.1, "betas": (0.9, 0.95)},
+                               clip_grad=1.0, dtype=torch.float32)
+    opt.zero_grad()
+    g = torch.full((8, 8), 0.5)
+    lin.weight.grad.copy_(g)
+    opt.step()
+    norm = g.norm()
+    gc = g * (1.0 / (norm + 1e-6))
+    m = 0.1 * gc
+    v = 0.05 * gc * gc
+    expect = w0 * (1 - 0.1 * 0.1) - 0.1 * (m / 0.1) / ((v / 0.05).sqrt() + 1e-8)
+    assert torch.allclose(lin.weight.detach(), expect, atol=1e-6)
+    assert abs(float(opt.last_grad_norm) - float(norm)) < 1e-5
+
+
+def test_rope_rmsnorm_swiglu_reference_formulas():
+    from gpt_from_scratch_b200.ops.rmsnorm import rmsnorm_reference
+    from gpt_from_scratch_b200.ops.rope import rope_reference
+    from gpt_from_scratch_b200.ops.swiglu import swiglu_reference
+    x = torch.arange(8, dtype=torch.float32).view(1, 1, 1, 8)
+    ang = torch.tensor([[0.1, 0.2, 0.3, 0.4]])
+    y = rope_reference(x, ang.cos(), ang.sin())
+    for i in range(4):
+        e, o = x[0, 0, 0, 2 * i], x[0, 0, 0, 2 * i + 1]
+        assert abs(y[0, 0, 0, 2 * i] - (e * math.cos(ang[0, i]) - o * math.sin(ang[0, i]))) < 1e-5
+        assert abs(y[0, 0, 0, 2 * i + 1] - (e * math.sin(ang[0, i]) + o * math.cos(ang[0, i]))) < 1e-5
+    # rotation is orthogonal: inverse rotation restores the input
+    back = rope_reference(y, ang.cos(), -ang.sin())
+    assert torch.allclose(back, x, atol=1e-5)
+    h = torch.randn(3, 16)
+    w = torch.rand(16) + 0.5
+    assert torch.allclose(rmsnorm_reference(h, w, 1e-5), h / (h.pow(2).mean(-1, keepdim=True) + 1e-5).sqrt() * w,
+                          atol=1e-6)
+    gu = torch.randn(4, 12)
+    assert torch.allclose(swiglu_reference(gu), torch.nn.functional.silu(gu[:, :6]) * gu[:, 6:])
+
+
+def test_vocab_parallel_ce_equals_torch_ce_on_one_rank():
+    from gpt_from_scratch_b200.parallel.loss import _VocabParallelCrossEntropy
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(5, 2, 11, generator=g, requires_grad=True)
+    tgt = torch.randint(0, 11, (5, 2), generator=g)
+    loss = _VocabParallelCrossEntropy.apply(logits, tgt)
+    ref = torch.nn.functional.cross_entropy(logits.detach().view(-1, 11), tgt.view(-1), reduction="none").view(5, 2)
+    assert torch.allclose(loss, ref, atol=1e-5)
+    loss.mean().backward()
+    lf = logits.detach().clone().requires_grad_()
+    torch.nn.functional.cross_entropy(lf.view(-1, 11), tgt.view(-1)).backward()
+    assert torch.allclose(logits.grad, lf.grad, atol=1e-6)
+
+
+def test_dataset_shift_and_sampler_sharding(tmp_path):
+    from gpt_from_scratch_b200.data import DistributedDataset, create_distributed_dataloader, write_synthetic_tokens
+    path = str(tmp_path / "tok.bin")
+    write_synthetic_tokens(path, 8 * 10 + 1, vocab_size=100, seed=1)
+    raw = np.fromfile(path, dtype=np.uint16)
+    assert raw.max() < 100
+    ds = DistributedDataset(path, 8)
+    assert len(ds) == 10
+    s = ds[3]
+    assert s["input"].dtype == torch.int64
+    assert s["input"].tolist() == raw[24:32].tolist() and s["label"].tolist() == raw[25:33].tolist()
+    loader, sampler = create_distributed_dataloader(path, 8, 2, num_workers=0)
+    sampler.set_epoch(0)
+    batches = list(loader)
+    assert len(batches) == 5 and batches[0]["input"].shape == (2, 8)
+    with pytest.raises(FileNotFoundError):
+        DistributedDataset(str(tmp_path / "missing.bin"), 8)
+
+
+def test_cli_defaults_match_reference():
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import train
+    a = train.parse_args([])
+    assert (a.vocab_size, a.hidden_size, a.num_layers, a.num_attention_heads) == (50304, 768, 12, 12)
+    assert (a.max_position_embeddings, a.intermediate_size, a.seq_len, a.batch_size) == (1024, 3072, 1024, 8)
+    assert (a.num_workers, a.lr, a.weight_decay, a.max_steps, a.clip_grad, a.log_interval) == \
+        (4, 3e-4, 0.1, 100000, 1.0, 10)
+    assert a.tensor_model_parallel_size == 1
+    cfg = train.build_config(train.parse_args(["--seq-len", "2048"]))
+    assert cfg.max_position_embeddings == 2048      # no crash for seq_len > max positions
+
+
+def test_rotary_cache_grows():
+    from gpt_from_scratch_b200.models.position_embeddings import RotaryEmbedding
+    r = RotaryEmbedding(8, max_position_embeddings=4)
+    cos, sin = r(torch.zeros(1), 10)
+    assert cos.shape == (10, 4)
+    assert "freqs" in r.state_dict() and "cos_cached" not in r.state_dict()
+
+
+def test_checkpoint_resume_is_exact_cpu(tmp_path):
+    from gpt_from_scratch_b200.checkpoint import load_checkpoint, save_checkpoint
+    from gpt_from_scratch_b200.engine import TrainEngine
+    cfg = GPTConfig(vocab_size=64, hidden_size=32, num_layers=1, num_attention_heads=4,
+                    max_position_embeddings=16, intermediate_size=48, attention_impl="torch")
+    g = torch.Generator().manual_seed(0)
+    data = [torch.randint(0, 64, (2, 17), generator=g) for _ in range(6)]
+    step = lambda e, t: float(e.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous()))  # noqa: E731
+    a = TrainEngine(cfg, lr=1e-2, dtype=torch.float32, seed=1)
+    for t in data[:3]:
+        step(a, t)
+    save_checkpoint(str(tmp_path), 3, a.model, a.optimizer, {"epoch": 0})
+    tail_a = [step(a, t) for t in data[3:]]
+    b = TrainEngine(cfg, lr=1e-2, dtype=torch.float32, seed=2)
+    payload = load_checkpoint(str(tmp_path), b.model, b.optimizer)
+    assert payload["step"] == 3
+    tail_b = [step(b, t) for t in data[3:]]
+    assert tail_a == tail_b
+    # a corrupted shard is detected
+    bad = os.path.join(str(tmp_path), "step_00000003", "tp00_dp00.pt")
+    with open(bad, "r+b") as f:
+        f.seek(100)
+        f.write(b"\0" * 64)
+    with pytest.raises(Exception):
+        load_checkpoint(str(tmp_path), b.model, b.optimizer)
+
+
+def test_native_library_is_required_on_request(monkeypatch, tmp_path):
+    from gpt_from_scratch_b200.ops import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "_LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_lib.NativeLibraryError):
+        _lib.lib()
