@@ -107,7 +107,8 @@ struct SmemCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-B alignment
+  static constexpr int EPI_BYTES = 4 * 4096;  // one [32 rows x 128 B] transpose buffer per epilogue warp
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + slack for 1024-B alignment
 };
 
 template <bool A_MN, bool B_MN, int BN, int STAGES, int COMM>
@@ -119,7 +120,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // 128B swizzle wants tile bases aligned to 1024 B.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
   uint64_t* full_bar = bars;                  // [STAGES]
   uint64_t* empty_bar = bars + STAGES;        // [STAGES]
   uint64_t* tmem_full = bars + 2 * STAGES;    // [2]
@@ -259,15 +261,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (p.epi_mode == EPI_PARTIAL_F32) {
+        // split-K partial tile: fp32 rows straight to the workspace
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        const int col0 = n0 + c;
-        if (col0 >= p.N) break;
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c, v);
-        tmem_ld_wait();
-        if (row < p.M) {
-          if (p.epi_mode == EPI_PARTIAL_F32) {
+        for (int c = 0; c < BN; c += 32) {
+          const int col0 = n0 + c;
+          if (col0 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c, v);
+          tmem_ld_wait();
+          if (row < p.M) {
             float* dst = p.ws + (static_cast<size_t>(z) * p.M + row) * p.N + col0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -277,26 +280,56 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 *reinterpret_cast<float4*>(dst + 4 * j) = o;
               }
             }
-          } else {
-            __nv_bfloat16* dst;
-            if (COMM == COMM_REDUCE_SCATTER) {
-              // partial rows go to their owner's staging area, slot of this (source) rank
-              dst = p.comm.peer_buf[chunk] +
-                    (static_cast<size_t>(p.comm.rank) * p.comm.rows_per_rank + (row - chunk * p.comm.rows_per_rank)) *
-                        p.N + col0;
-            } else {
-              dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
-            }
-            const __nv_bfloat16* res = p.R + static_cast<size_t>(row) * p.ldr + col0;
+          }
+        }
+      } else {
+        // bf16 output. Each lane owns one accumulator row; a per-warp shared-memory transpose
+        // turns that into stores where 8 lanes write one full 128-byte line of a row
+        // (row-per-lane stores would touch 32 different lines per instruction). Rotary
+        // embedding and the addend are applied after the transpose on 8-column groups.
+        uint8_t* ebuf = epi_smem + (warp - 2) * 4096;
+        const int rrow = lane >> 3;
+        const int rch = lane & 7;
+        const bool has_math = (p.epi_mode == EPI_ADD) || (p.rope_cos != nullptr);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64) {
+          const int col0 = n0 + c;
+          if (col0 >= p.N) break;
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32(t_row + c, va);
+          tmem_ld_32x32(t_row + c + 32, vb);
+          tmem_ld_wait();
+          uint8_t* myrow = ebuf + lane * 128;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col0 + 8 * j + 8 <= p.N) {
+          for (int j = 0; j < 4; ++j) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(va[8 * j + 0]), __uint_as_float(va[8 * j + 1]));
+            w.y = pack_bf16x2(__uint_as_float(va[8 * j + 2]), __uint_as_float(va[8 * j + 3]));
+            w.z = pack_bf16x2(__uint_as_float(va[8 * j + 4]), __uint_as_float(va[8 * j + 5]));
+            w.w = pack_bf16x2(__uint_as_float(va[8 * j + 6]), __uint_as_float(va[8 * j + 7]));
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) = w;
+            w.x = pack_bf16x2(__uint_as_float(vb[8 * j + 0]), __uint_as_float(vb[8 * j + 1]));
+            w.y = pack_bf16x2(__uint_as_float(vb[8 * j + 2]), __uint_as_float(vb[8 * j + 3]));
+            w.z = pack_bf16x2(__uint_as_float(vb[8 * j + 4]), __uint_as_float(vb[8 * j + 5]));
+            w.w = pack_bf16x2(__uint_as_float(vb[8 * j + 6]), __uint_as_float(vb[8 * j + 7]));
+            *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = w;
+          }
+          __syncwarp();
+          const int gcol = col0 + rch * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + rrow;
+            const int grow = m0 + q * 32 + r;
+            uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
+            if (grow < p.M && gcol + 8 <= p.N) {
+              if (has_math) {
                 float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * j + e]);
-                if (p.rope_cos != nullptr && col0 + 8 * j < p.rope_cols) {
+                const float2 x0 = unpack_bf16x2(w.x), x1 = unpack_bf16x2(w.y), x2 = unpack_bf16x2(w.z),
+                             x3 = unpack_bf16x2(w.w);
+                f[0] = x0.x; f[1] = x0.y; f[2] = x1.x; f[3] = x1.y; f[4] = x2.x; f[5] = x2.y; f[6] = x3.x; f[7] = x3.y;
+                if (p.rope_cos != nullptr && gcol < p.rope_cols) {
                   const int half = p.rope_d >> 1;
-                  const size_t ti = static_cast<size_t>(row / p.rope_b) * half + (((col0 + 8 * j) % p.rope_d) >> 1);
+                  const size_t ti = static_cast<size_t>(grow / p.rope_b) * half + ((gcol % p.rope_d) >> 1);
                   const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
                   const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
                   const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
@@ -306,21 +339,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   f[6] = a6 * cs.w - a7 * sn.w; f[7] = a6 * sn.w + a7 * cs.w;
                 }
                 if (p.epi_mode == EPI_ADD) {
-                  const uint4 rr = *reinterpret_cast<const uint4*>(res + 8 * j);
+                  const uint4 rr = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(grow) * p.ldr + gcol);
                   const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
                                r3 = unpack_bf16x2(rr.w);
                   f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
                   f[4] += r2.x; f[5] += r2.y; f[6] += r3.x; f[7] += r3.y;
                 }
-                uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]);
-                o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]);
-                o.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+                w.x = pack_bf16x2(f[0], f[1]);
+                w.y = pack_bf16x2(f[2], f[3]);
+                w.z = pack_bf16x2(f[4], f[5]);
+                w.w = pack_bf16x2(f[6], f[7]);
               }
+              __nv_bfloat16* dst;
+              if (COMM == COMM_REDUCE_SCATTER) {
+                // partial rows go to their owner's staging area, slot of this (source) rank
+                dst = p.comm.peer_buf[chunk] +
+                      (static_cast<size_t>(p.comm.rank) * p.comm.rows_per_rank +
+                       (grow - chunk * p.comm.rows_per_rank)) * p.N + gcol;
+              } else {
+                dst = p.C + static_cast<size_t>(grow) * p.ldc + gcol;
+              }
+              *reinterpret_cast<uint4*>(dst) = w;
             }
           }
+          __syncwarp();
         }
       }
       tc_fence_before();
