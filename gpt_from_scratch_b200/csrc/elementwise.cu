@@ -95,6 +95,106 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // ---------------------------------------------------------------------------
 constexpr int NB_WARPS = 8;
 
+// Register path (H <= 256 * NV): every lane keeps the row values it needs for the second
+// pass and its dw partial sums in registers; shared memory is only used once at the end.
+template <int NV>
+__global__ void __launch_bounds__(NB_WARPS * 32)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int rows, int H, int rows_per_cta) {
+  extern __shared__ float red[];  // [warps][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int nvec = H >> 3;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  float wv[NV][8];
+  float dwacc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dwacc[i][e] = 0.f;
+      wv[i][e] = 0.f;
+    }
+    if (v < nvec) load8(w + 8 * v, wv[i]);
+  }
+  for (int row = r0 + warp; row < r1; row += nwarps) {
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    const float rs = rstd[row];
+    uint4 cdy[NV], cx[NV], cres[NV];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        cdy[i] = *reinterpret_cast<const uint4*>(dyr + 8 * v);
+        cx[i] = *reinterpret_cast<const uint4*>(xr + 8 * v);
+        if (dres != nullptr) cres[i] = *reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * H + 8 * v);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        const float2 a0 = unpack_bf16x2(cdy[i].x), a1 = unpack_bf16x2(cdy[i].y), a2 = unpack_bf16x2(cdy[i].z),
+                     a3 = unpack_bf16x2(cdy[i].w);
+        const float2 b0 = unpack_bf16x2(cx[i].x), b1 = unpack_bf16x2(cx[i].y), b2 = unpack_bf16x2(cx[i].z),
+                     b3 = unpack_bf16x2(cx[i].w);
+        dot += a0.x * wv[i][0] * b0.x + a0.y * wv[i][1] * b0.y + a1.x * wv[i][2] * b1.x + a1.y * wv[i][3] * b1.y +
+               a2.x * wv[i][4] * b2.x + a2.y * wv[i][5] * b2.y + a3.x * wv[i][6] * b3.x + a3.y * wv[i][7] * b3.y;
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rs * rs * rs / static_cast<float>(H);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float a[8], b[8], o[8];
+        const float2 a0 = unpack_bf16x2(cdy[i].x), a1 = unpack_bf16x2(cdy[i].y), a2 = unpack_bf16x2(cdy[i].z),
+                     a3 = unpack_bf16x2(cdy[i].w);
+        const float2 b0 = unpack_bf16x2(cx[i].x), b1 = unpack_bf16x2(cx[i].y), b2 = unpack_bf16x2(cx[i].z),
+                     b3 = unpack_bf16x2(cx[i].w);
+        a[0] = a0.x; a[1] = a0.y; a[2] = a1.x; a[3] = a1.y; a[4] = a2.x; a[5] = a2.y; a[6] = a3.x; a[7] = a3.y;
+        b[0] = b0.x; b[1] = b0.y; b[2] = b1.x; b[3] = b1.y; b[4] = b2.x; b[5] = b2.y; b[6] = b3.x; b[7] = b3.y;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          o[e] = rs * a[e] * wv[i][e] - b[e] * coef;
+          dwacc[i][e] += a[e] * round_bf16(b[e] * rs);
+        }
+        if (dres != nullptr) {
+          const float2 d0 = unpack_bf16x2(cres[i].x), d1 = unpack_bf16x2(cres[i].y), d2 = unpack_bf16x2(cres[i].z),
+                       d3 = unpack_bf16x2(cres[i].w);
+          o[0] += d0.x; o[1] += d0.y; o[2] += d1.x; o[3] += d1.y; o[4] += d2.x; o[5] += d2.y; o[6] += d3.x; o[7] += d3.y;
+        }
+        store8(dx + static_cast<size_t>(row) * H + 8 * v, o);
+      }
+    }
+  }
+  float* my_red = red + static_cast<size_t>(warp) * H;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) my_red[8 * v + e] = dwacc[i][e];
+    }
+  }
+  __syncthreads();
+  float* outp = dw_partial + static_cast<size_t>(blockIdx.x) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float s = 0.f;
+    for (int wv2 = 0; wv2 < nwarps; ++wv2) s += red[static_cast<size_t>(wv2) * H + i];
+    outp[i] = s;
+  }
+}
+
+// Generic path (any H that is a multiple of 8): partial sums live in shared memory.
 __global__ void __launch_bounds__(NB_WARPS * 32)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -332,7 +432,7 @@ int gfs_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows,
 // Number of fp32 elements the backward needs in `partial`: parts * H with parts from this call.
 int gfs_rmsnorm_bwd_parts(int rows) {
   const int sms = gfs_host::sm_count();
-  const int want = sms * 2;
+  const int want = sms * 4;
   const int rows_per_cta = std::max(NB_WARPS, (rows + want - 1) / want);
   return (rows + rows_per_cta - 1) / rows_per_cta;
 }
@@ -349,18 +449,35 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
   while (warps > 1 && static_cast<size_t>(warps) * H * sizeof(float) > 200 * 1024) warps >>= 1;
   const size_t smem = static_cast<size_t>(warps) * H * sizeof(float);
   if (smem > 200 * 1024) return -1;
-  static int smem_set = 0;
-  if (smem > 48 * 1024 && smem_set < static_cast<int>(smem)) {
-    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
-        cudaSuccess)
-      return -10;
-    smem_set = 200 * 1024;
+  const __nv_bfloat16* a_dy = static_cast<const __nv_bfloat16*>(dy);
+  const __nv_bfloat16* a_x = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* a_w = static_cast<const __nv_bfloat16*>(w);
+  const float* a_rstd = static_cast<const float*>(rstd);
+  const __nv_bfloat16* a_res = static_cast<const __nv_bfloat16*>(dres);
+  __nv_bfloat16* a_dx = static_cast<__nv_bfloat16*>(dx);
+  float* a_part = static_cast<float*>(partial);
+  auto ensure_smem = [&](auto kern, int& done) -> int {
+    if (smem > 48 * 1024 && done < static_cast<int>(smem)) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return -10;
+      done = 200 * 1024;
+    }
+    return 0;
+  };
+  static int set_gen = 0, set_r4 = 0, set_r8 = 0;
+  if (H <= 1024) {
+    if (ensure_smem(rmsnorm_bwd_reg_kernel<4>, set_r4)) return -10;
+    rmsnorm_bwd_reg_kernel<4><<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows,
+                                                                   H, rows_per_cta);
+  } else if (H <= 2048) {
+    if (ensure_smem(rmsnorm_bwd_reg_kernel<8>, set_r8)) return -10;
+    rmsnorm_bwd_reg_kernel<8><<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows,
+                                                                   H, rows_per_cta);
+  } else {
+    if (ensure_smem(rmsnorm_bwd_kernel, set_gen)) return -10;
+    rmsnorm_bwd_kernel<<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows, H,
+                                                            rows_per_cta);
   }
-  rmsnorm_bwd_kernel<<<parts, warps * 32, smem, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
-      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), static_cast<float*>(partial), rows, H,
-      rows_per_cta);
   if (cudaGetLastError() != cudaSuccess) return -11;
   rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(static_cast<const float*>(partial),
                                                               static_cast<__nv_bfloat16*>(dw), parts, H,

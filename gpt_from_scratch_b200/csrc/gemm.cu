@@ -75,8 +75,18 @@ struct GemmParams {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols, rope_d, rope_b;
+  // SwiGLU fusion. mode 1 (forward, B = [gate rows | up rows] of a [2I, K] weight): each tile
+  // pairs 128 gate columns with the matching 128 up columns; the epilogue writes both halves
+  // of the projection (C, pitch ldc) and act = silu(gate) * up (swi_act, pitch swi_ld).
+  // mode 2 (backward, the product is d_act [M, I]): the epilogue reads gate/up from swi_gu
+  // (pitch swi_ld) and writes d_gate | d_up into C ([M, 2I], pitch ldc) instead of d_act.
+  int swi_mode, swi_I, swi_ld;
+  __nv_bfloat16* swi_act;
+  const __nv_bfloat16* swi_gu;
   CommParams comm;
 };
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
 // Tile order. Plain: n fastest. Fused collectives walk the row chunks of the ranks in a
 // rotated order: all-gather starts with the local chunk (already in place), reduce-scatter
@@ -192,7 +202,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmap_a, &full_bar[stage], m0 + 64 * i, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            if (p.swi_mode == 1) {  // 128 gate rows + the matching 128 up rows (tensor map box = 128 rows)
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0 >> 1);
+              tma_load_2d(sb + (BN / 2) * 128, &tmap_b, &full_bar[stage], k0, p.swi_I + (n0 >> 1));
+            } else {
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmap_b, &full_bar[stage], n0 + 64 * i, k0);
@@ -282,6 +297,67 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+      } else if (p.swi_mode == 1) {
+        // SwiGLU forward: accumulator columns [0,128) are gate, [128,256) the matching up columns
+        uint8_t* ebuf = epi_smem + (warp - 2) * 4096;
+        const int g0 = n0 >> 1;  // first gate column of the tile
+        const int rrow = lane >> 3;
+        const int rch = lane & 7;
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          if (g0 + c >= p.swi_I) break;
+          uint32_t vg[32], vu[32];
+          tmem_ld_32x32(t_row + c, vg);
+          tmem_ld_32x32(t_row + BN / 2 + c, vu);
+          tmem_ld_wait();
+          uint32_t pa[16];
+          uint8_t* myrow = ebuf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 wg, wu;
+            uint32_t* wgp = &wg.x;
+            uint32_t* wup = &wu.x;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              wgp[e] = pack_bf16x2(__uint_as_float(vg[8 * j + 2 * e]), __uint_as_float(vg[8 * j + 2 * e + 1]));
+              wup[e] = pack_bf16x2(__uint_as_float(vu[8 * j + 2 * e]), __uint_as_float(vu[8 * j + 2 * e + 1]));
+              // act from the bf16-rounded projections, silu rounded to bf16 before the product
+              const float2 g2 = unpack_bf16x2(wgp[e]), u2 = unpack_bf16x2(wup[e]);
+              const float s0 = __bfloat162float(__float2bfloat16_rn(g2.x * sigmoid_f(g2.x)));
+              const float s1 = __bfloat162float(__float2bfloat16_rn(g2.y * sigmoid_f(g2.y)));
+              pa[4 * j + e] = pack_bf16x2(s0 * u2.x, s1 * u2.y);
+            }
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) = wg;
+            *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = wu;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {  // gate | up halves of the projection
+            const int r = i * 4 + rrow;
+            const int grow = m0 + q * 32 + r;
+            const int lc = g0 + c + (rch & 3) * 8;  // column inside [0, I)
+            const uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
+            if (grow < p.M && lc + 8 <= p.swi_I)
+              *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(grow) * p.ldc + (rch >= 4 ? p.swi_I : 0) + lc) = w;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(pa[4 * j], pa[4 * j + 1], pa[4 * j + 2], pa[4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {  // act: 32 columns per row, 4 lanes per row
+            const int r = i * 8 + (lane >> 2);
+            const int ch = lane & 3;
+            const int grow = m0 + q * 32 + r;
+            const int lc = g0 + c + ch * 8;
+            const uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((ch ^ (r & 7)) << 4));
+            if (grow < p.M && lc + 8 <= p.swi_I)
+              *reinterpret_cast<uint4*>(p.swi_act + static_cast<size_t>(grow) * p.swi_ld + lc) = w;
+          }
+          __syncwarp();
+        }
       } else {
         // bf16 output. Each lane owns one accumulator row; a per-warp shared-memory transpose
         // turns that into stores where 8 lanes write one full 128-byte line of a row
@@ -291,10 +367,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int rrow = lane >> 3;
         const int rch = lane & 7;
         const bool has_math = (p.epi_mode == EPI_ADD) || (p.rope_cos != nullptr);
+        const bool swi_bwd = (p.swi_mode == 2);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 64) {
           const int col0 = n0 + c;
           if (col0 >= p.N) break;
+          const int gcol = col0 + rch * 8;
+          // the addend (and, in the SwiGLU backward, gate/up) are fetched up front: issued
+          // after the stores below they would be serialised behind them (the addend may alias C)
+          uint4 pre0[8], pre1[8];
+          if (p.epi_mode == EPI_ADD || swi_bwd) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int grow = m0 + q * 32 + i * 4 + rrow;
+              pre0[i] = make_uint4(0, 0, 0, 0);
+              pre1[i] = make_uint4(0, 0, 0, 0);
+              if (grow < p.M && gcol + 8 <= p.N) {
+                if (swi_bwd) {
+                  const __nv_bfloat16* gp = p.swi_gu + static_cast<size_t>(grow) * p.swi_ld + gcol;
+                  pre0[i] = *reinterpret_cast<const uint4*>(gp);
+                  pre1[i] = *reinterpret_cast<const uint4*>(gp + p.swi_I);
+                } else {
+                  pre0[i] = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(grow) * p.ldr + gcol);
+                }
+              }
+            }
+          }
           uint32_t va[32], vb[32];
           tmem_ld_32x32(t_row + c, va);
           tmem_ld_32x32(t_row + c + 32, vb);
@@ -315,13 +413,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = w;
           }
           __syncwarp();
-          const int gcol = col0 + rch * 8;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = i * 4 + rrow;
             const int grow = m0 + q * 32 + r;
             uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
-            if (grow < p.M && gcol + 8 <= p.N) {
+            if (swi_bwd) {
+              // w holds 8 values of d_act; turn them into d_gate and d_up
+              if (grow < p.M && gcol + 8 <= p.N) {
+                const uint4 gq = pre0[i];
+                const uint4 uq = pre1[i];
+                const uint32_t* dw = &w.x;
+                const uint32_t* gw = &gq.x;
+                const uint32_t* uw = &uq.x;
+                uint4 og, ou;
+                uint32_t* ogp = &og.x;
+                uint32_t* oup = &ou.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 d2 = unpack_bf16x2(dw[e]), g2 = unpack_bf16x2(gw[e]), u2 = unpack_bf16x2(uw[e]);
+                  const float sg0 = sigmoid_f(g2.x), sg1 = sigmoid_f(g2.y);
+                  ogp[e] = pack_bf16x2(d2.x * u2.x * sg0 * (1.f + g2.x * (1.f - sg0)),
+                                       d2.y * u2.y * sg1 * (1.f + g2.y * (1.f - sg1)));
+                  oup[e] = pack_bf16x2(d2.x * g2.x * sg0, d2.y * g2.y * sg1);
+                }
+                __nv_bfloat16* dst = p.C + static_cast<size_t>(grow) * p.ldc + gcol;
+                *reinterpret_cast<uint4*>(dst) = og;
+                *reinterpret_cast<uint4*>(dst + p.swi_I) = ou;
+              }
+            } else if (grow < p.M && gcol + 8 <= p.N) {
               if (has_math) {
                 float f[8];
                 const float2 x0 = unpack_bf16x2(w.x), x1 = unpack_bf16x2(w.y), x2 = unpack_bf16x2(w.z),
@@ -339,7 +459,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   f[6] = a6 * cs.w - a7 * sn.w; f[7] = a6 * sn.w + a7 * cs.w;
                 }
                 if (p.epi_mode == EPI_ADD) {
-                  const uint4 rr = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(grow) * p.ldr + gcol);
+                  const uint4 rr = pre0[i];
                   const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
                                r3 = unpack_bf16x2(rr.w);
                   f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
@@ -622,6 +742,48 @@ int gfs_gemm_bf16_rope(const void* A, const void* B, void* C, const void* R, int
     if (cudaGetLastError() != cudaSuccess) return -12;
   }
   return 0;
+}
+
+// SwiGLU-fused products of the MLP (see GemmParams::swi_mode).
+//   mode 1: gu[M, 2I] = x[M, K] @ w_gu[2I, K]^T and act[M, I] = silu(gu[:, :I]) * gu[:, I:]
+//           (a = x, b = w_gu, c = gu with pitch ldc, extra = act with pitch ld_extra)
+//   mode 2: d_gu[M, 2I] = swiglu_backward(d_act = dy[M, K] @ w_down[K, I], gu)
+//           (a = dy, b = w_down stored [K, I], c = d_gu with pitch ldc, extra = gu with pitch ld_extra)
+int gfs_gemm_bf16_swiglu(int mode, const void* a, const void* b, void* c, void* extra, int M, int I, int K, int lda,
+                         int ldb, int ldc, int ld_extra, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (mode != 1 && mode != 2) return -1;
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if ((I & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || (ld_extra & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+       reinterpret_cast<uintptr_t>(extra)) & 15)
+    return -2;
+  constexpr int BN = 256;
+  GemmParams p{};
+  p.M = M; p.K = K;
+  p.N = (mode == 1) ? 2 * I : I;
+  p.C = static_cast<__nv_bfloat16*>(c);
+  p.ldc = ldc;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (mode == 1) ? (I + BN / 2 - 1) / (BN / 2) : (I + BN - 1) / BN;
+  p.kblocks_total = (K + BK - 1) / BK;
+  p.kblocks_per_split = p.kblocks_total;
+  p.split_k = 1;
+  p.epi_mode = EPI_STORE;
+  p.status = gfs_host::status_words();
+  p.rope_b = 1;
+  p.swi_mode = mode;
+  p.swi_I = I;
+  p.swi_ld = ld_extra;
+  if (mode == 1) p.swi_act = static_cast<__nv_bfloat16*>(extra);
+  else p.swi_gu = static_cast<const __nv_bfloat16*>(extra);
+  const CUtensorMap* ta = gfs_host::tmap_2d_cached(a, M, K, lda, BM, 64);
+  const CUtensorMap* tb = (mode == 1) ? gfs_host::tmap_2d_cached(b, 2 * I, K, ldb, BN / 2, 64)
+                                      : gfs_host::tmap_2d_cached(b, K, I, ldb, 64, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+  const int grid = std::min(p.tiles_m * p.tiles_n, gfs_host::sm_count());
+  return (mode == 1) ? launch_variant<false, false, 256, 4>(ta, tb, p, grid, stream)
+                     : launch_variant<false, true, 256, 4>(ta, tb, p, grid, stream);
 }
 
 // Fused collective + GEMM over peer memory (one kernel, no NCCL):

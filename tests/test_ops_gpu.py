@@ -134,3 +134,26 @@ def test_swiglu_fwd_bwd(cuda_device):
     af.backward(da.float())
     _close(a, af, 2e-2, 1e-2, what="swiglu")
     _close(gu.grad, gf.grad, 2e-2, 1e-2, what="swiglu grad")
+
+
+@pytest.mark.parametrize("M,H,I", [(256, 256, 384), (1000, 768, 704), (2048, 768, 3072)])
+def test_fused_mlp_matches_unfused(cuda_device, M, H, I):
+    """SwiGLU folded into the GEMM epilogues == separate GEMM / activation kernels."""
+    from gpt_from_scratch_b200.ops.mlp_fused import _FusedMLP
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    x = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
+    w_gu = (torch.randn(2 * I, H, device=cuda_device, generator=g) * 0.05).bfloat16()
+    w_dn = (torch.randn(H, I, device=cuda_device, generator=g) * 0.05).bfloat16()
+    res = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
+    dout = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
+    xa, wa, wb = x.clone().requires_grad_(), w_gu.clone().requires_grad_(), w_dn.clone().requires_grad_()
+    ya = _FusedMLP.apply(xa, wa, wb, res, None, None)
+    ya.backward(dout)
+    xf, wf, wg = x.float().requires_grad_(), w_gu.float().requires_grad_(), w_dn.float().requires_grad_()
+    gu = xf @ wf.t()
+    act = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    yf = act @ wg.t() + res.float()
+    yf.backward(dout.float())
+    for name, a, b in (("y", ya, yf), ("dx", xa.grad, xf.grad), ("dW_gu", wa.grad, wf.grad), ("dW_down", wb.grad, wg.grad)):
+        rel = (a.float() - b).norm() / (b.norm() + 1e-9)
+        assert rel < 1.5e-2, f"{name}: relative error {rel:.4g}"
