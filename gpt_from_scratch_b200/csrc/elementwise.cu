@@ -255,22 +255,22 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// blockDim = (32, 8): 32 columns per block, the partial rows are split over 8 thread rows and
+// blockDim = (32, 32): 32 columns per block, the partial rows are split over 32 thread rows and
 // combined through shared memory in a fixed order (deterministic).
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int parts,
                                          int H, int accumulate) {
-  __shared__ float sm[8][33];
+  __shared__ float sm[32][33];
   const int i = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
   if (i < H) {
-    for (int p = threadIdx.y; p < parts; p += 8) s += partial[static_cast<size_t>(p) * H + i];
+    for (int p = threadIdx.y; p < parts; p += 32) s += partial[static_cast<size_t>(p) * H + i];
   }
   sm[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
   if (threadIdx.y == 0 && i < H) {
     float t = 0.f;
 #pragma unroll
-    for (int y = 0; y < 8; ++y) t += sm[y][threadIdx.x];
+    for (int y = 0; y < 32; ++y) t += sm[y][threadIdx.x];
     if (accumulate) t += __bfloat162float(dw[i]);
     dw[i] = __float2bfloat16_rn(t);
   }
@@ -479,7 +479,7 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
                                                             rows_per_cta);
   }
   if (cudaGetLastError() != cudaSuccess) return -11;
-  rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(static_cast<const float*>(partial),
+  rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(static_cast<const float*>(partial),
                                                               static_cast<__nv_bfloat16*>(dw), parts, H,
                                                               accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : -12;

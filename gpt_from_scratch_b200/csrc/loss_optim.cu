@@ -170,12 +170,22 @@ sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long n, float* __res
     is_last = (prev == gridDim.x - 1);
   }
   __syncthreads();
-  if (is_last && threadIdx.x == 0) {
+  if (is_last) {
+    // fixed-order parallel sum of the per-block partials (same result on every run)
     __threadfence();
-    float total = 0.f;
-    for (unsigned int i = 0; i < gridDim.x; ++i) total += reinterpret_cast<volatile float*>(scratch)[i];
-    out[0] = total;
-    *ticket = 0u;
+    float t = 0.f;
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += SUMSQ_THREADS)
+      t += reinterpret_cast<volatile float*>(scratch)[i];
+    t = warp_sum(t);
+    __syncthreads();
+    if (lane == 0) sm[warp] = t;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int i = 0; i < SUMSQ_THREADS / 32; ++i) total += sm[i];
+      out[0] = total;
+      *ticket = 0u;
+    }
   }
 }
 
