@@ -417,8 +417,13 @@ struct BwdParams {
   const float* rope_sin;
 };
 
-template <int D, int MODE, int NBUF>
-__global__ void __launch_bounds__(ATT_THREADS, NBUF == 1 ? 2 : 1)
+// CW = number of compute warps (4 or 8). With 8, every accumulator row is shared by two
+// threads that each take half of the 64 streamed columns (no exchange is needed: the
+// row/column statistics are inputs), which doubles the warps available to hide latency.
+// TS = stages of the streamed-tile ring (a stage is only released when the gradient MMAs that
+// read it have finished, so two stages would put the TMA latency on the critical path).
+template <int D, int MODE, int NBUF, int CW, int TS>
+__global__ void __launch_bounds__(64 + 32 * CW, NBUF == 1 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
                  const __grid_constant__ CUtensorMap tt1, const __grid_constant__ CUtensorMap tt2,
                  const BwdParams p) {
@@ -434,20 +439,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   uint8_t* R1 = smem;
   uint8_t* R2 = R1 + R_BYTES;
   uint8_t* T1 = R2 + R_BYTES;        // 2 stages
-  uint8_t* T2 = T1 + 2 * T_BYTES;    // 2 stages
-  uint8_t* M1 = T2 + 2 * T_BYTES;    // 2 buffers
+  uint8_t* T2 = T1 + TS * T_BYTES;
+  uint8_t* M1 = T2 + TS * T_BYTES;
   uint8_t* M2 = M1 + NBUF * M_BYTES;
-  float* stats = reinterpret_cast<float*>(M2 + NBUF * M_BYTES);  // mode 0: [2 stages][lse 64 | dvec 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + 1024);
+  float* stats = reinterpret_cast<float*>(M2 + NBUF * M_BYTES);  // mode 0: [TS stages][lse 64 | dvec 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + TS * 512);
   uint64_t* r_full = bars;
-  uint64_t* t_full = bars + 1;
-  uint64_t* t_empty = bars + 3;
-  uint64_t* xy_full = bars + 5;
-  uint64_t* xy_empty = bars + 7;
-  uint64_t* m_full = bars + 9;
-  uint64_t* m_empty = bars + 11;
-  uint64_t* acc_full = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* t_full = bars + 1;             // [TS]
+  uint64_t* t_empty = t_full + TS;         // [TS]
+  uint64_t* xy_full = t_empty + TS;
+  uint64_t* xy_empty = xy_full + 2;
+  uint64_t* m_full = xy_empty + 2;
+  uint64_t* m_empty = m_full + 2;
+  uint64_t* acc_full = m_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -471,12 +476,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < TS; ++i) {
       mbar_init(&t_full[i], 1);
       mbar_init(&t_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&xy_full[i], 1);
-      mbar_init(&xy_empty[i], 4);
-      mbar_init(&m_full[i], 4);
+      mbar_init(&xy_empty[i], CW);
+      mbar_init(&m_full[i], CW);
       mbar_init(&m_empty[i], 1);
     }
     mbar_init(acc_full, 1);
@@ -506,9 +513,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         tma_load_4d(R2 + db * 16384, &tr2, r_full, db * 64, rt * 128, h, b);
       }
       for (int t = 0; t < n_t; ++t) {
-        const int st = t & 1;
+        const int st = t % TS;
         const int ti = t_begin + t;
-        mbar_wait(&t_empty[st], ((t >> 1) & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+        mbar_wait(&t_empty[st], ((t / TS) & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
         mbar_arrive_expect_tx(&t_full[st], 2 * T_BYTES + (MODE == 0 ? 512 : 0));
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
@@ -532,8 +539,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
       mbar_wait(r_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
       auto issue_xy = [&](int t) {
-        const int st = t & 1;                       // streamed-tile stage
-        const uint32_t par = (t >> 1) & 1;
+        const int st = t % TS;                      // streamed-tile stage
+        const uint32_t par = (t / TS) & 1;
         const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
         const uint32_t spar = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
         mbar_wait(&t_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
@@ -546,7 +553,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       if (n_t > 0) issue_xy(0);
       for (int t = 0; t < n_t; ++t) {
         if (t + 1 < n_t) issue_xy(t + 1);
-        const int st = t & 1;
+        const int st = t % TS;
         const int sb = (NBUF == 2) ? (t & 1) : 0;
         mbar_wait(&m_full[sb], (NBUF == 2) ? ((t >> 1) & 1) : (t & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
@@ -568,6 +575,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     }
   } else {
     const int quarter = warp & 3;
+    constexpr int COLS = 64 / (CW / 4);          // streamed columns handled by this thread
+    const int chalf = (CW == 8) ? ((warp - 2) >> 2) : 0;
+    const int cbase = chalf * COLS;
     const int r = quarter * 32 + lane;
     const int row_g = rt * 128 + r;  // mode 0: key position, mode 1: query position
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
@@ -578,7 +588,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       row_dvec = p.dvec[static_cast<size_t>(bh) * p.S_pad + row_g];
     }
     for (int t = 0; t < n_t; ++t) {
-      const int st = t & 1;                       // streamed-tile stage (for the column statistics)
+      const int st = t % TS;                      // streamed-tile stage (for the column statistics)
       const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
       const uint32_t par = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
       const int ti = t_begin + t;
@@ -642,16 +652,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       };
       const uint32_t x_addr = tmem_base + lane_base + sb * 64;
       const uint32_t y_addr = tmem_base + lane_base + Y_COL + sb * 64;
-      tmem_ld_32x32(x_addr, xa);
-      tmem_ld_32x32(y_addr, ya);
+      tmem_ld_32x32(x_addr + cbase, xa);
+      tmem_ld_32x32(y_addr + cbase, ya);
       tmem_ld_wait_for(xa);
       tmem_ld_wait_for(ya);
-      tmem_ld_32x32(x_addr + 32, xb);
-      tmem_ld_32x32(y_addr + 32, yb);
-      grad_chunk(xa, ya, 0);
-      tmem_ld_wait_for(xb);
-      tmem_ld_wait_for(yb);
-      grad_chunk(xb, yb, 32);
+      if (COLS == 64) {
+        tmem_ld_32x32(x_addr + 32, xb);
+        tmem_ld_32x32(y_addr + 32, yb);
+      }
+      grad_chunk(xa, ya, cbase);
+      if (COLS == 64) {
+        tmem_ld_wait_for(xb);
+        tmem_ld_wait_for(yb);
+        grad_chunk(xb, yb, 32);
+      }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
@@ -667,7 +681,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     __nv_bfloat16* d1 = p.out1 + row_g * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
     __nv_bfloat16* d2 = (MODE == 0) ? p.out2 + row_g * p.o2_ss + b * p.o2_bs + h * p.o2_hs : nullptr;
 #pragma unroll 1
-    for (int c = 0; c < D; c += 32) {
+    for (int c = chalf * (D / (CW / 4)); c < (chalf + 1) * (D / (CW / 4)); c += 32) {
       uint32_t v[32];
       // mode 0: ACC2 holds dK (scaled), ACC1 holds dV; mode 1: ACC1 holds dQ (scaled)
       tmem_ld_32x32(tmem_base + lane_base + (MODE == 0 ? ACC2 : ACC1) + c, v);
@@ -826,8 +840,10 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p.rope_cos = static_cast<const float*>(rope_cos);
   p.rope_sin = static_cast<const float*>(rope_sin);
   const dim3 grid((S + 127) / 128, B * nh);
-  const int nbuf = (D == 64) ? 1 : 2;
-  const int smem = 2 * (D / 64) * 16384 + 4 * (D / 64) * 8192 + 2 * nbuf * 16384 + 1024 + 256 + 1024;
+  const int nbuf = 2;
+  const int bwd_threads = 64 + 32 * 8;
+  const int ts = (D == 64) ? 4 : 3;
+  const int smem = 2 * (D / 64) * 16384 + 2 * ts * (D / 64) * 8192 + 2 * nbuf * 16384 + ts * 512 + 256 + 1024;
   static bool set_done[4] = {false, false, false, false};
   // mode 0: dK, dV
   BwdParams p0 = p;
@@ -837,17 +853,17 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p1.out1 = static_cast<__nv_bfloat16*>(dq); p1.o1_ss = sdq[0]; p1.o1_bs = sdq[1]; p1.o1_hs = sdq[2];
   p1.out2 = nullptr; p1.o2_ss = p1.o2_bs = p1.o2_hs = 0;
   if (D == 64) {
-    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 1>, smem)) return -10; set_done[0] = true; }
-    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 1>, smem)) return -10; set_done[1] = true; }
-    flash_bwd_kernel<64, 0, 1><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 4>, smem)) return -10; set_done[0] = true; }
+    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 4>, smem)) return -10; set_done[1] = true; }
+    flash_bwd_kernel<64, 0, 2, 8, 4><<<grid, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<64, 1, 1><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<64, 1, 2, 8, 4><<<grid, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
   } else {
-    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2>, smem)) return -10; set_done[2] = true; }
-    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2>, smem)) return -10; set_done[3] = true; }
-    flash_bwd_kernel<128, 0, 2><<<grid, ATT_THREADS, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3>, smem)) return -10; set_done[2] = true; }
+    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3>, smem)) return -10; set_done[3] = true; }
+    flash_bwd_kernel<128, 0, 2, 8, 3><<<grid, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<128, 1, 2><<<grid, ATT_THREADS, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<128, 1, 2, 8, 3><<<grid, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
