@@ -64,6 +64,17 @@ __device__ __forceinline__ void mma_kmn(uint32_t d, uint32_t a, uint32_t a_blk, 
   }
 }
 
+// A in tensor memory (8 columns per 16-wide K step); B MN-major as in mma_kmn.
+template <int KSTEPS>
+__device__ __forceinline__ void mma_tmn(uint32_t d, uint32_t a_tmem, uint32_t b, uint32_t b_blk, uint32_t idesc,
+                                        bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint64_t bd = umma_desc_sw128(b + ks * 2048, b_blk, 1024);
+    umma_ts(d, a_tmem + ks * 8, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
@@ -434,6 +445,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   constexpr uint32_t TMEM_COLS = (NBUF == 1 && D == 64) ? 256 : 512;
   constexpr uint32_t Y_COL = 64 * NBUF;  // X tiles at [0, 64*NBUF), Y tiles after them
   constexpr uint32_t ACC1 = 128 * NBUF, ACC2 = 128 * NBUF + D;
+  // head_dim 64 leaves 128 TMEM columns free: P^T / dS^T (bf16, two per column) are handed to the
+  // gradient MMAs through tensor memory instead of shared memory, which halves the shared-memory
+  // traffic of this kernel (its 64-wide MMAs are otherwise bound by operand reads from shared memory)
+  constexpr bool PT = (D == 64 && NBUF == 2);
+  constexpr uint32_t PT_COL = 384;  // [buffer][P 32 cols | dS 32 cols]
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* R1 = smem;
@@ -557,7 +573,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         const int sb = (NBUF == 2) ? (t & 1) : 0;
         mbar_wait(&m_full[sb], (NBUF == 2) ? ((t >> 1) & 1) : (t & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
-        if (MODE == 0) {
+        if (PT) {
+          const uint32_t pt = tmem_base + PT_COL + sb * 64;
+          if (MODE == 0) {
+            mma_tmn<4>(tmem_base + ACC1, pt, smem_u32(T2 + st * T_BYTES), 8192, idesc_acc, t > 0);        // dV += P^T dO
+            mma_tmn<4>(tmem_base + ACC2, pt + 32, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc, t > 0);   // dK += dS^T Q
+          } else {
+            mma_tmn<4>(tmem_base + ACC1, pt + 32, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc, t > 0);   // dQ += dS K
+          }
+        } else if (MODE == 0) {
           // dV += P^T dO ; dK += dS^T Q
           mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + sb * M_BYTES), 0, smem_u32(T2 + st * T_BYTES), 8192, idesc_acc,
                      t > 0);
@@ -634,6 +658,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
           pp[e >> 1] = pack_bf16x2(pe[0], pe[1]);
           dd[e >> 1] = pack_bf16x2(de[0], de[1]);
         }
+        if (PT) {
+          // columns c .. c+31 of this row -> 16 packed columns of the P / dS tensor-memory tiles
+          const uint32_t pt = tmem_base + lane_base + PT_COL + sb * 64 + (c >> 1);
+          if (MODE == 0) tmem_st_32x16(pt, pp);
+          tmem_st_32x16(pt + 32, dd);
+          return;
+        }
         const int chunk0 = c >> 3;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -666,8 +697,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         tmem_ld_wait_for(yb);
         grad_chunk(xb, yb, 32);
       }
+      if (PT) tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
+      if (!PT) fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&xy_empty[sb]);
