@@ -13,7 +13,6 @@ using namespace gfs;
 namespace {
 
 constexpr int NORM_WARPS = 4;
-constexpr int NORM_MAXV = 16;  // vectors of 8 bf16 cached per lane: covers H <= 4096
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   const uint4 u = *reinterpret_cast<const uint4*>(p);
@@ -33,6 +32,9 @@ __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(_
 // ---------------------------------------------------------------------------
 // RMSNorm forward: y = bf16(x * rstd) * w, rstd = rsqrt(mean(x^2) + eps). One warp per row.
 // ---------------------------------------------------------------------------
+// NORM_MAXV = vectors of 8 bf16 cached per lane (covers H <= 256 * NORM_MAXV without a second
+// read); a template parameter so that small hidden sizes do not pay for 64 cache registers.
+template <int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int H, float eps) {
@@ -98,7 +100,7 @@ constexpr int NB_WARPS = 8;
 // Register path (H <= 256 * NV): every lane keeps the row values it needs for the second
 // pass and its dw partial sums in registers; shared memory is only used once at the end.
 template <int NV>
-__global__ void __launch_bounds__(NB_WARPS * 32)
+__global__ void __launch_bounds__(NB_WARPS * 32, NV <= 4 ? 2 : 1)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
@@ -312,47 +314,48 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 // ---------------------------------------------------------------------------
 // SwiGLU on a [M, 2I] buffer whose first I columns are the gate and last I the up half.
 // ---------------------------------------------------------------------------
+// Grid: x covers the 8-column vectors of a row, y strides over rows (no integer divisions).
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int M, int I) {
   const int vec_per_row = I >> 3;
-  const size_t total = static_cast<size_t>(M) * vec_per_row;
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = v / vec_per_row;
-    const int c = static_cast<int>(v % vec_per_row) << 3;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= vec_per_row) return;
+  const int c = v << 3;
+  for (int row = blockIdx.y; row < M; row += gridDim.y) {
+    const __nv_bfloat16* base = gu + static_cast<size_t>(row) * 2 * I;
     float g[8], u[8], o[8];
-    load8(gu + row * 2 * I + c, g);
-    load8(gu + row * 2 * I + I + c, u);
+    load8(base + c, g);
+    load8(base + I + c, u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float sg = 1.f / (1.f + __expf(-g[e]));
+      const float sg = __fdividef(1.f, 1.f + __expf(-g[e]));
       // silu rounded to bf16 before the product, as two separate bf16 ops would do
       o[e] = round_bf16(g[e] * sg) * u[e];
     }
-    store8(act + row * I + c, o);
+    store8(act + static_cast<size_t>(row) * I + c, o);
   }
 }
 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
                                   __nv_bfloat16* __restrict__ dgu, int M, int I) {
   const int vec_per_row = I >> 3;
-  const size_t total = static_cast<size_t>(M) * vec_per_row;
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = v / vec_per_row;
-    const int c = static_cast<int>(v % vec_per_row) << 3;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= vec_per_row) return;
+  const int c = v << 3;
+  for (int row = blockIdx.y; row < M; row += gridDim.y) {
+    const size_t rb = static_cast<size_t>(row) * 2 * I;
     float g[8], u[8], d[8], dg[8], du[8];
-    load8(gu + row * 2 * I + c, g);
-    load8(gu + row * 2 * I + I + c, u);
-    load8(dact + row * I + c, d);
+    load8(gu + rb + c, g);
+    load8(gu + rb + I + c, u);
+    load8(dact + static_cast<size_t>(row) * I + c, d);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float sg = 1.f / (1.f + __expf(-g[e]));
+      const float sg = __fdividef(1.f, 1.f + __expf(-g[e]));
       const float silu = g[e] * sg;
       dg[e] = d[e] * u[e] * sg * (1.f + g[e] * (1.f - sg));
       du[e] = d[e] * silu;
     }
-    store8(dgu + row * 2 * I + c, dg);
-    store8(dgu + row * 2 * I + I + c, du);
+    store8(dgu + rb + c, dg);
+    store8(dgu + rb + I + c, du);
   }
 }
 
@@ -423,9 +426,14 @@ int gfs_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows,
   if (H & 7) return -1;
   if (rows == 0) return 0;
   const int blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
-  rmsnorm_fwd_kernel<<<blocks, NORM_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
-      static_cast<float*>(rstd), rows, H, eps);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+  float* rp = static_cast<float*>(rstd);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (H <= 1024) rmsnorm_fwd_kernel<4><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
+  else if (H <= 2048) rmsnorm_fwd_kernel<8><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
+  else rmsnorm_fwd_kernel<16><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -498,18 +506,18 @@ int gfs_rope(void* x, const void* cosb, const void* sinb, int S, int B, int nh, 
 
 int gfs_swiglu_fwd(const void* gu, void* act, int M, int I, void* stream) {
   if (I & 7) return -1;
-  const size_t total = static_cast<size_t>(M) * (I >> 3);
-  if (total == 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (M == 0 || I == 0) return 0;
+  const dim3 grid(((I >> 3) + 127) / 128, std::min(M, 32768));
+  swiglu_fwd_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(act), M, I);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 int gfs_swiglu_bwd(const void* dact, const void* gu, void* dgu, int M, int I, void* stream) {
   if (I & 7) return -1;
-  const size_t total = static_cast<size_t>(M) * (I >> 3);
-  if (total == 0) return 0;
-  swiglu_bwd_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (M == 0 || I == 0) return 0;
+  const dim3 grid(((I >> 3) + 127) / 128, std::min(M, 32768));
+  swiglu_bwd_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(gu),
       static_cast<__nv_bfloat16*>(dgu), M, I);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

@@ -86,7 +86,7 @@ struct GemmParams {
   CommParams comm;
 };
 
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 // Tile order. Plain: n fastest. Fused collectives walk the row chunks of the ranks in a
 // rotated order: all-gather starts with the local chunk (already in place), reduce-scatter

@@ -100,16 +100,16 @@ __global__ void ce_combine_kernel(const float* __restrict__ stats_all, float* __
   loss[row] = l - tz;
 }
 
-// In place: z <- (exp(z - lse) - [col == target - v0]) * g[row].
+// In place: z <- (exp(z - lse) - [col == target - v0]) * g[row]. Grid: x covers the vectors of
+// a row, y strides over rows.
 __global__ void ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, const float* __restrict__ lse,
                               const long long* __restrict__ target, const float* __restrict__ grad_rows, int M, int Vp,
                               long ld, int v0) {
   const int nvec = Vp >> 3;
-  const size_t total = static_cast<size_t>(M) * nvec;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int row = static_cast<int>(i / nvec);
-    const int c = static_cast<int>(i % nvec) << 3;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= nvec) return;
+  const int c = v << 3;
+  for (int row = blockIdx.y; row < M; row += gridDim.y) {
     __nv_bfloat16* p = logits + static_cast<size_t>(row) * ld + c;
     float f[8];
     load8(p, f);
@@ -287,10 +287,9 @@ int gfs_ce_combine(const void* stats_all, void* lse, void* loss, int M, int worl
 int gfs_ce_bwd(void* logits, const void* lse, const void* target, const void* grad_rows, int M, int Vp, long ld,
                int v0, void* stream) {
   if ((Vp & 7) || (ld & 7)) return -1;
-  const size_t total = static_cast<size_t>(M) * (Vp >> 3);
-  if (total == 0) return 0;
-  const size_t blocks = std::min<size_t>((total + 255) / 256, static_cast<size_t>(gfs_host::sm_count()) * 16);
-  ce_bwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (M == 0 || Vp == 0) return 0;
+  const dim3 grid(((Vp >> 3) + 255) / 256, std::min(M, 32768));
+  ce_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(logits), static_cast<const float*>(lse), static_cast<const long long*>(target),
       static_cast<const float*>(grad_rows), M, Vp, ld, v0);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
