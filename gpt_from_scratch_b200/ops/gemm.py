@@ -13,7 +13,12 @@ import torch
 
 from . import _lib
 
+import os
+
 _WS_BYTES = 96 << 20
+# CTA-pair kernel (csrc/gemm2.cu): used when the problem has at least this many 256 x 256 tiles
+_PAIR_MIN_TILES = int(os.environ.get("GFS_GEMM_PAIR_MIN_TILES", "60"))
+_PAIR_ENABLED = os.environ.get("GFS_GEMM_PAIR", "1") != "0"
 _workspaces: dict[int, torch.Tensor] = {}
 
 
@@ -40,7 +45,7 @@ def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
               out: torch.Tensor | None = None, addend: torch.Tensor | None = None,
-              force_split: int = 0, rope: tuple | None = None) -> torch.Tensor:
+              force_split: int = 0, rope: tuple | None = None, pair: bool | None = None) -> torch.Tensor:
     """``out[M,N] = op(a) @ op(b) (+ addend)`` with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (K-major) or ``[K,M]`` (``a_mn_major``); ``b`` is ``[N,K]``
@@ -63,6 +68,21 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_m
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     assert out.shape == (M, N) and out.stride(1) == 1
+    if pair is None:
+        pair = (_PAIR_ENABLED and force_split == 0 and K >= 256 and
+                ((M + 255) // 256) * ((N + 255) // 256) >= _PAIR_MIN_TILES)
+    if pair:
+        if rope is not None:
+            cos, sin, rope_cols, head_dim, batch = rope
+            rargs = (cos.data_ptr(), sin.data_ptr(), rope_cols, head_dim, batch)
+        else:
+            rargs = (0, 0, 0, 0, 1)
+        rc = _lib.lib().gfs_gemm2_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(addend), M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), addend.stride(0) if addend is not None else 0,
+            1 if a_mn_major else 0, 1 if b_mn_major else 0, *rargs, _lib.stream_ptr())
+        _lib.check(rc, "gfs_gemm2_bf16")
+        return out
     ws = _workspace(a.device)
     if rope is None:
         rc = _lib.lib().gfs_gemm_bf16(

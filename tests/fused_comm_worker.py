@@ -37,7 +37,7 @@ def main():
     log = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
 
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    S, B, K, N = 512, 2, 256, 384
+    S, B, K, N = 128 * world * 2, 2, 256, 384
     Ss = S // world
     # ---- all-gather -> GEMM (column parallel) ----
     x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
@@ -115,14 +115,16 @@ def main():
     log("ce_exchange_combine ok")
 
     # ---- whole model, TP = world: fused vs NCCL composition ----
-    cfg = GPTConfig(vocab_size=2048, hidden_size=256, num_layers=2, num_attention_heads=4,
-                    max_position_embeddings=512, intermediate_size=512, init_method="normal")
-    data = [torch.randint(0, 2048, (2, 513), generator=torch.Generator().manual_seed(50 + i)) for i in range(4)]
+    heads = 4 if world <= 4 else 8
+    cfg = GPTConfig(vocab_size=2048, hidden_size=64 * heads, num_layers=2, num_attention_heads=heads,
+                    max_position_embeddings=512, intermediate_size=128 * max(4, world), init_method="normal")
+    data = [torch.randint(0, 2048, (max(2, world), 513), generator=torch.Generator().manual_seed(50 + i))
+            for i in range(4)]
     traj = {}
     for impl in ("nccl", "fused"):
         ps.set_comm_impl(impl)
         eng = TrainEngine(cfg, lr=1e-3, seed=3)
-        traj[impl] = [float(eng.train_step(t[:, :-1].contiguous().to(dev), t[:, 1:].contiguous().to(dev)))
+        traj[impl] = [float(eng.train_step(t[:2, :-1].contiguous().to(dev), t[:2, 1:].contiguous().to(dev)))
                       for t in data]
         torch.cuda.synchronize()
         _lib.raise_on_status()
@@ -142,7 +144,7 @@ def main():
         eng = TrainEngine(cfg, lr=1e-3, seed=3)
         losses = []
         for t in data:
-            tt = t[rank::world] if t.shape[0] >= world else t
+            tt = t[rank::world]
             losses.append(float(eng.train_step(tt[:, :-1].contiguous().to(dev), tt[:, 1:].contiguous().to(dev))))
         traj[impl] = losses
         finals[impl] = eng.optimizer.param_buffer.float().clone()

@@ -86,3 +86,20 @@ def test_gemm_rope_epilogue(cuda_device):
     q, k, v = ref.unbind(2)
     ref = torch.stack((rope_reference(q, cos, sin), rope_reference(k, cos, sin), v), dim=2).view(S * B, -1)
     _check(out, ref, K)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (1024, 1280, 328), (2000, 520, 1024),
+                                   (4096, 2304, 768)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_cta_pair_kernel(cuda_device, M, N, K, a_mn, b_mn):
+    """The cta_group::2 kernel (one 256x256 tile per CTA pair) against the fp32 reference."""
+    from gpt_from_scratch_b200.ops.gemm import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device=cuda_device, generator=g).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=cuda_device, generator=g).bfloat16()
+    r = torch.randn((M, N), device=cuda_device, generator=g).bfloat16()
+    out = gemm_bf16(a, b, a_mn_major=a_mn, b_mn_major=b_mn, pair=True)
+    _check(out, _ref(a, b, a_mn, b_mn, None), K)
+    out2 = r.clone()
+    gemm_bf16(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out2, addend=out2, pair=True)
+    _check(out2, _ref(a, b, a_mn, b_mn, r), K)
