@@ -381,6 +381,342 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------
+// Forward, head_dim 64: two 128-row query tiles per CTA.
+//
+// One CTA per SM; warps 2-5 run the softmax of tile A and warps 6-9 that of tile B (one thread
+// per query row, so no cross-thread reductions), which gives every scheduler two independent
+// softmax warps while K/V tiles are fetched once for 256 query rows. S, P V and P each live
+// in tensor memory (S_A S_B | PV_A PV_B | P_A P_B = 512 columns): the probabilities are
+// handed to the P V MMA as its TMEM A operand, nothing of the softmax goes through shared
+// memory. K/V use a 3-stage ring.
+// ---------------------------------------------------------------------------
+constexpr int FWD64_THREADS = 64 + 256;
+constexpr int FWD64_KS = 3;
+constexpr int FWD64_SMEM = 2 * 16384 + FWD64_KS * 32768 + 256;
+
+// Persistent: each CTA walks work items (pair of query tiles, batch*head), heaviest pairs
+// first, so barrier set-up, the TMEM allocation and the CTA launch gap are paid once per SM
+// instead of once per item (at sequence length 1024 they were ~45 % of the kernel's time).
+// All barrier parities therefore run on counters that continue across items.
+__global__ void __launch_bounds__(FWD64_THREADS, 1)
+flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const FwdParams p, int n_pairs, int n_items) {
+  constexpr int D = 64;
+  constexpr int KS = FWD64_KS;
+  constexpr uint32_t S_COL = 0, OP_COL = 256, P_COL = 384;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* Qs = smem_raw;                    // [2][128 x 64]
+  uint8_t* Ks = Qs + 2 * 16384;              // [KS][128 x 64]
+  uint8_t* Vs = Ks + KS * 16384;             // [KS][128 x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + KS * 16384);
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* k_full = bars + 2;               // [KS]
+  uint64_t* k_empty = k_full + KS;
+  uint64_t* v_full = k_empty + KS;
+  uint64_t* v_empty = v_full + KS;
+  uint64_t* s_full = v_empty + KS;           // [2] per query tile
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 2;
+  uint64_t* o_empty = o_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0) record_status(p.status, STATUS_BAD_ARGUMENT, 0x5a12u);
+    return;
+  }
+  const int nb = (p.S + 127) >> 7;
+  const int BH = p.B * p.nh;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int i = 0; i < KS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
+
+  // Work items are dealt to the CTAs in a snake (left to right, then right to left), which
+  // evens out the per-CTA totals of the descending item weights; an item past the end can
+  // only occur in a CTA's last round.
+  const int G = static_cast<int>(gridDim.x);
+  auto snake = [&](int rnd) {
+    return rnd * G + ((rnd & 1) ? G - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x));
+  };
+  // decode of work item w: pairs in descending order (most key blocks first), then batch*head
+  auto decode = [&](int w, int& qp, int& bh, int& na, int& nbk) {
+    qp = n_pairs - 1 - w / BH;
+    bh = w % BH;
+    const int qa = 2 * qp, qb = 2 * qp + 1;
+    na = p.causal ? min(qa + 1, nb) : nb;
+    nbk = (qb < nb) ? (p.causal ? min(qb + 1, nb) : nb) : 0;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int g = 0;      // key blocks loaded so far (ring position)
+      for (int rnd = 0; rnd * G < n_items; ++rnd) {
+        const int w = snake(rnd);
+        if (w >= n_items) break;
+        const int item = rnd;
+        int qp, bh, na, nbk;
+        decode(w, qp, bh, na, nbk);
+        const int b = bh / p.nh, h = bh % p.nh;
+        const int n_kv = max(na, nbk);
+        mbar_wait(q_empty, (item & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);  // previous item's S MMAs done
+        mbar_arrive_expect_tx(q_full, 2 * 16384);
+        tma_load_4d(Qs, &tq, q_full, 0, (2 * qp) * 128, h, b);
+        tma_load_4d(Qs + 16384, &tq, q_full, 0, (2 * qp + 1) * 128, h, b);   // rows past S are zero-filled
+        for (int j = 0; j < n_kv; ++j, ++g) {
+          const int st = g % KS;
+          const uint32_t par = ((g / KS) & 1) ^ 1u;
+          mbar_wait(&k_empty[st], par, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+          mbar_arrive_expect_tx(&k_full[st], 16384);
+          tma_load_4d(Ks + st * 16384, &tk, &k_full[st], 0, j * 128, h, b);
+          mbar_wait(&v_empty[st], par, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+          mbar_arrive_expect_tx(&v_full[st], 16384);
+          tma_load_4d(Vs + st * 16384, &tv, &v_full[st], 0, j * 128, h, b);
+        }
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
+      int g0 = 0;            // ring position of this item's first key block
+      int cx[2] = {0, 0};    // blocks processed so far per query tile (barrier phase counters)
+      for (int rnd = 0; rnd * G < n_items; ++rnd) {
+        const int w = snake(rnd);
+        if (w >= n_items) break;
+        const int item = rnd;
+        int qp, bh, n_x[2];
+        decode(w, qp, bh, n_x[0], n_x[1]);
+        const int n_kv = max(n_x[0], n_x[1]);
+        mbar_wait(q_full, item & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
+        auto issue_s = [&](int x, int j) {
+          const int g = g0 + j;
+          mbar_wait(&k_full[g % KS], (g / KS) & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
+          tc_fence_after();
+          mma_kk<D / 16>(tmem_base + S_COL + x * 128, smem_u32(Qs + x * 16384), 0, smem_u32(Ks + (g % KS) * 16384),
+                         0, idesc_s, false);
+          umma_commit(&s_full[x]);
+        };
+        // S(0) of this item may only overwrite S once the softmax has consumed the previous
+        // item's last block of that tile; that is guaranteed because the previous item's last
+        // P V of the tile was issued after its p_full, and we issue in program order.
+        if (n_x[0] > 0) issue_s(0, 0);
+        if (n_x[1] > 0) issue_s(1, 0);
+        if (n_kv > 0) umma_commit(&k_empty[g0 % KS]);
+        if (n_kv == 1) umma_commit(q_empty);
+        for (int j = 0; j < n_kv; ++j) {
+          const int g = g0 + j;
+          for (int x = 0; x < 2; ++x) {
+            if (j >= n_x[x]) continue;
+            const int c = cx[x] + j;
+            mbar_wait(&p_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);   // S_x(j) consumed, P_x(j) in TMEM
+            if (j + 1 < n_x[x]) issue_s(x, j + 1);
+            mbar_wait(&v_full[g % KS], (g / KS) & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
+            mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+            tc_fence_after();
+            mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384), 0,
+                       idesc_o, false);
+            umma_commit(&o_full[x]);
+          }
+          if (j + 1 < n_kv) umma_commit(&k_empty[(g + 1) % KS]);  // both tiles' S(j+1) have been issued
+          if (j + 2 == n_kv) umma_commit(q_empty);                // the item's last S MMAs are issued
+          umma_commit(&v_empty[g % KS]);
+        }
+        g0 += n_kv;
+        cx[0] += n_x[0];
+        cx[1] += n_x[1];
+      }
+    }
+  } else {
+    const int x = (warp - 2) >> 2;           // query tile of this warp
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + S_COL + x * 128;
+    const uint32_t o_addr = tmem_base + lane_base + OP_COL + x * 64;
+    const uint32_t p_addr = tmem_base + lane_base + P_COL + x * 64;
+    const float sl2 = p.scale * LOG2E_F;
+    int cdone = 0;  // blocks of this tile processed in earlier items
+    for (int rnd = 0; rnd * G < n_items; ++rnd) {
+      const int w = snake(rnd);
+      if (w >= n_items) break;
+      int qp, bh, na, nbk;
+      decode(w, qp, bh, na, nbk);
+      const int b = bh / p.nh, h = bh % p.nh;
+      const int qtx = 2 * qp + x;
+      const int row_g = qtx * 128 + r;
+      const int n_mine = x == 0 ? na : nbk;
+      float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+      float o[D];
+#pragma unroll
+      for (int i = 0; i < D; ++i) o[i] = 0.f;
+
+      auto fold_pv = [&](int c, float alpha) {
+        mbar_wait(&o_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        uint32_t wa[32], wb[32];
+        tmem_ld_32x32(o_addr, wa);
+        tmem_ld_32x32(o_addr + 32, wb);
+        tmem_ld_wait_for(wa);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = fmaf(o[e], alpha, __uint_as_float(wa[e]));
+        tmem_ld_wait_for(wb);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[32 + e] = fmaf(o[32 + e], alpha, __uint_as_float(wb[e]));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[x]);
+      };
+
+      for (int j = 0; j < n_mine; ++j) {
+        const int c = cdone + j;
+        const bool need_mask = (p.causal && j == qtx) || ((j + 1) * 128 > p.S);
+        mbar_wait(&s_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+        tc_fence_after();
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        uint32_t va[32], vb[32];
+        auto max_chunk = [&](const uint32_t (&v)[32], int cc) {
+          if (need_mask) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int col_g = j * 128 + cc + e;
+              const bool dead = (p.causal && col_g > row_g) || col_g >= p.S;
+              mx0 = fmaxf(mx0, dead ? -INFINITY : __uint_as_float(v[e]));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              mx0 = fmaxf(mx0, __uint_as_float(v[e]));
+              mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
+            }
+          }
+        };
+        tmem_ld_32x32(s_addr + 0, va);
+        tmem_ld_wait_for(va);
+        tmem_ld_32x32(s_addr + 32, vb);
+        max_chunk(va, 0);
+        tmem_ld_wait_for(vb);
+        tmem_ld_32x32(s_addr + 64, va);
+        max_chunk(vb, 32);
+        tmem_ld_wait_for(va);
+        tmem_ld_32x32(s_addr + 96, vb);
+        max_chunk(va, 64);
+        tmem_ld_wait_for(vb);
+        tmem_ld_32x32(s_addr + 0, va);  // first chunk of pass 2
+        max_chunk(vb, 96);
+        const float m_new = fmaxf(m, fmaxf(mx0, mx1));
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = fast_exp2((m - m_use) * sl2);
+        const float moff = m_use * sl2;
+        // the previous block's P V must have finished before P is overwritten; fold it in now
+        if (j > 0) fold_pv(c - 1, alpha_prev);
+        float rs0 = 0.f, rs1 = 0.f;
+        auto prob_chunk_impl = [&](auto mask_tag, const uint32_t (&v)[32], int cc) {
+          constexpr bool MASKED = decltype(mask_tag)::value;
+          uint32_t packed[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
+            float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
+            if constexpr (MASKED) {
+              const int col_g = j * 128 + cc + e;
+              const bool dead0 = (p.causal && col_g > row_g) || col_g >= p.S;
+              const bool dead1 = (p.causal && col_g + 1 > row_g) || col_g + 1 >= p.S;
+              x0 = dead0 ? 0.f : x0;
+              x1 = dead1 ? 0.f : x1;
+            }
+            rs0 += x0;
+            rs1 += x1;
+            packed[e >> 1] = pack_bf16x2(x0, x1);
+          }
+          tmem_st_32x16(p_addr + (cc >> 1), packed);
+        };
+        auto prob_chunk = [&](const uint32_t (&v)[32], int cc) {
+          if (need_mask) prob_chunk_impl(std::true_type{}, v, cc);
+          else prob_chunk_impl(std::false_type{}, v, cc);
+        };
+        tmem_ld_wait_for(va);
+        tmem_ld_32x32(s_addr + 32, vb);
+        prob_chunk(va, 0);
+        tmem_ld_wait_for(vb);
+        tmem_ld_32x32(s_addr + 64, va);
+        prob_chunk(vb, 32);
+        tmem_ld_wait_for(va);
+        tmem_ld_32x32(s_addr + 96, vb);
+        prob_chunk(va, 64);
+        tmem_ld_wait_for(vb);
+        prob_chunk(vb, 96);
+        l = l * alpha + (rs0 + rs1);
+        m = m_new;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x]);
+        alpha_prev = alpha;
+      }
+      if (n_mine > 0) fold_pv(cdone + n_mine - 1, alpha_prev);
+      cdone += n_mine;
+
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      if (row_g < p.S && n_mine > 0) {
+        __nv_bfloat16* dst = p.O + row_g * p.o_ss + b * p.o_bs + h * p.o_hs;
+#pragma unroll
+        for (int cc = 0; cc < D; cc += 8) {
+          uint4 wv;
+          wv.x = pack_bf16x2(o[cc + 0] * inv_l, o[cc + 1] * inv_l);
+          wv.y = pack_bf16x2(o[cc + 2] * inv_l, o[cc + 3] * inv_l);
+          wv.z = pack_bf16x2(o[cc + 4] * inv_l, o[cc + 5] * inv_l);
+          wv.w = pack_bf16x2(o[cc + 6] * inv_l, o[cc + 7] * inv_l);
+          *reinterpret_cast<uint4*>(dst + cc) = wv;
+        }
+      }
+      if (row_g < p.S_pad && n_mine > 0) {
+        const float mm = (m == -INFINITY) ? 0.f : m;
+        p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] = mm * p.scale + logf(fmaxf(l, 1e-37f));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Backward pre-pass: dvec[b,h,s] = sum_d dO[s,b,h,d] * O[s,b,h,d]; one warp per row.
 // ---------------------------------------------------------------------------
 __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
@@ -437,7 +773,7 @@ template <int D, int MODE, int NBUF, int CW, int TS>
 __global__ void __launch_bounds__(64 + 32 * CW, NBUF == 1 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
                  const __grid_constant__ CUtensorMap tt1, const __grid_constant__ CUtensorMap tt2,
-                 const BwdParams p) {
+                 const BwdParams p, int n_rt, int n_items) {
   constexpr int DB = D / 64;
   constexpr int R_BYTES = DB * 16384;  // resident [128 x D]
   constexpr int T_BYTES = DB * 8192;   // streamed [64 x D]
@@ -468,27 +804,39 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   uint64_t* m_full = xy_empty + 2;
   uint64_t* m_empty = m_full + 2;
   uint64_t* acc_full = m_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_empty = acc_full + 1;
+  uint64_t* r_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 3);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
-  const int b = bh / p.nh;
-  const int h = bh % p.nh;
   const int n_small = (p.S + 63) >> 6;  // number of 64-row streamed tiles in the sequence
-  // resident tile index and range of streamed tiles
-  int rt, t_begin, t_end;
-  if (MODE == 0) {
-    rt = blockIdx.x;  // key tile; the first ones have the most query tiles
-    t_begin = p.causal ? 2 * rt : 0;
-    t_end = n_small;
-  } else {
-    rt = gridDim.x - 1 - blockIdx.x;  // query tile; the last ones have the most key tiles
-    t_begin = 0;
-    t_end = p.causal ? min(n_small, 2 * rt + 2) : n_small;
-  }
-  const int n_t = t_end - t_begin;
+  const int BH = p.B * p.nh;
+  // Persistent: a CTA walks work items (resident tile, batch*head), heaviest resident tiles
+  // first, dealt in a snake over the CTAs; barrier phases run on counters that continue
+  // across items, so set-up and the TMEM allocation are paid once and the next item's loads
+  // and first score MMAs overlap the current item's epilogue.
+  const int G = static_cast<int>(gridDim.x);
+  auto snake = [&](int rnd) {
+    return rnd * G + ((rnd & 1) ? G - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x));
+  };
+  // resident tile index and range of streamed tiles of work item w
+  auto decode = [&](int w, int& rt, int& bh, int& t_begin, int& n_t) {
+    const int level = w / BH;
+    bh = w % BH;
+    int t_end;
+    if (MODE == 0) {
+      rt = level;  // key tile; the first ones have the most query tiles
+      t_begin = p.causal ? 2 * rt : 0;
+      t_end = n_small;
+    } else {
+      rt = n_rt - 1 - level;  // query tile; the last ones have the most key tiles
+      t_begin = 0;
+      t_end = p.causal ? min(n_small, 2 * rt + 2) : n_small;
+    }
+    n_t = max(t_end - t_begin, 0);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
@@ -503,6 +851,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       mbar_init(&m_empty[i], 1);
     }
     mbar_init(acc_full, 1);
+    mbar_init(acc_empty, CW);
+    mbar_init(r_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tr1);
@@ -522,16 +872,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
+      int g = 0;  // streamed tiles loaded so far (ring position)
+      for (int it = 0; it * G < n_items; ++it) {
+        const int w = snake(it);
+        if (w >= n_items) break;
+        int rt, bh, t_begin, n_t;
+        decode(w, rt, bh, t_begin, n_t);
+        const int b = bh / p.nh, h = bh % p.nh;
+        mbar_wait(r_empty, (it & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);  // previous item's score MMAs done
       mbar_arrive_expect_tx(r_full, 2 * R_BYTES);
 #pragma unroll
       for (int db = 0; db < DB; ++db) {
         tma_load_4d(R1 + db * 16384, &tr1, r_full, db * 64, rt * 128, h, b);
         tma_load_4d(R2 + db * 16384, &tr2, r_full, db * 64, rt * 128, h, b);
       }
-      for (int t = 0; t < n_t; ++t) {
-        const int st = t % TS;
+      for (int t = 0; t < n_t; ++t, ++g) {
+        const int st = g % TS;
         const int ti = t_begin + t;
-        mbar_wait(&t_empty[st], ((t / TS) & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+        mbar_wait(&t_empty[st], ((g / TS) & 1) ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
         mbar_arrive_expect_tx(&t_full[st], 2 * T_BYTES + (MODE == 0 ? 512 : 0));
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
@@ -544,6 +902,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
           bulk_load_1d(stats + st * 128 + 64, p.dvec + off, 256, &t_full[st]);
         }
       }
+      }
       if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
@@ -553,12 +912,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       constexpr uint32_t idesc_xy = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, 0, 1);
       const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
-      mbar_wait(r_full, 0, wctx, STATUS_TIMEOUT_PIPE_FULL);
+      int g0 = 0;  // ring position of the item's first streamed tile
+      for (int it = 0; it * G < n_items; ++it) {
+        const int w = snake(it);
+        if (w >= n_items) break;
+        int rt, bh, t_begin, n_t;
+        decode(w, rt, bh, t_begin, n_t);
+      mbar_wait(r_full, it & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
       auto issue_xy = [&](int t) {
-        const int st = t % TS;                      // streamed-tile stage
-        const uint32_t par = (t / TS) & 1;
-        const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
-        const uint32_t spar = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
+        const int g = g0 + t;
+        const int st = g % TS;                      // streamed-tile stage
+        const uint32_t par = (g / TS) & 1;
+        const int sb = (NBUF == 2) ? (g & 1) : 0;   // X / Y / P / dS buffer
+        const uint32_t spar = (NBUF == 2) ? ((g >> 1) & 1) : (g & 1);
         mbar_wait(&t_full[st], par, wctx, STATUS_TIMEOUT_PIPE_FULL);
         mbar_wait(&xy_empty[sb], spar ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
@@ -567,11 +933,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         umma_commit(&xy_full[sb]);
       };
       if (n_t > 0) issue_xy(0);
+      if (n_t <= 1) umma_commit(r_empty);
       for (int t = 0; t < n_t; ++t) {
-        if (t + 1 < n_t) issue_xy(t + 1);
-        const int st = t % TS;
-        const int sb = (NBUF == 2) ? (t & 1) : 0;
-        mbar_wait(&m_full[sb], (NBUF == 2) ? ((t >> 1) & 1) : (t & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
+        if (t + 1 < n_t) {
+          issue_xy(t + 1);
+          if (t + 2 == n_t) umma_commit(r_empty);  // the item's last score MMAs are issued
+        }
+        const int g = g0 + t;
+        const int st = g % TS;
+        const int sb = (NBUF == 2) ? (g & 1) : 0;
+        mbar_wait(&m_full[sb], (NBUF == 2) ? ((g >> 1) & 1) : (g & 1), wctx, STATUS_TIMEOUT_SOFTMAX);
+        if (t == 0) mbar_wait(acc_empty, (it & 1) ^ 1u, wctx, STATUS_TIMEOUT_TMEM_EMPTY);  // previous epilogue done
         tc_fence_after();
         if (PT) {
           const uint32_t pt = tmem_base + PT_COL + sb * 64;
@@ -596,6 +968,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         umma_commit(&m_empty[sb]);
       }
       umma_commit(acc_full);
+      g0 += n_t;
+      }
     }
   } else {
     const int quarter = warp & 3;
@@ -603,18 +977,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     const int chalf = (CW == 8) ? ((warp - 2) >> 2) : 0;
     const int cbase = chalf * COLS;
     const int r = quarter * 32 + lane;
-    const int row_g = rt * 128 + r;  // mode 0: key position, mode 1: query position
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = p.scale * LOG2E_F;
+    int g0 = 0;
+    for (int it = 0; it * G < n_items; ++it) {
+    const int w = snake(it);
+    if (w >= n_items) break;
+    int rt, bh, t_begin, n_t;
+    decode(w, rt, bh, t_begin, n_t);
+    const int b = bh / p.nh, h = bh % p.nh;
+    const int row_g = rt * 128 + r;  // mode 0: key position, mode 1: query position
     float row_lse = 0.f, row_dvec = 0.f;
     if (MODE == 1 && row_g < p.S_pad) {
       row_lse = p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] * LOG2E_F;
       row_dvec = p.dvec[static_cast<size_t>(bh) * p.S_pad + row_g];
     }
     for (int t = 0; t < n_t; ++t) {
-      const int st = t % TS;                      // streamed-tile stage (for the column statistics)
-      const int sb = (NBUF == 2) ? (t & 1) : 0;   // X / Y / P / dS buffer
-      const uint32_t par = (NBUF == 2) ? ((t >> 1) & 1) : (t & 1);
+      const int g = g0 + t;
+      const int st = g % TS;                      // streamed-tile stage (for the column statistics)
+      const int sb = (NBUF == 2) ? (g & 1) : 0;   // X / Y / P / dS buffer
+      const uint32_t par = (NBUF == 2) ? ((g >> 1) & 1) : (g & 1);
       const int ti = t_begin + t;
       bool need_mask;
       if (MODE == 0) need_mask = (p.causal && ti < 2 * rt + 2) || ((ti + 1) * 64 > p.S);
@@ -707,7 +1089,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       }
     }
     // epilogue: accumulators -> global
-    mbar_wait(acc_full, 0, wctx, STATUS_TIMEOUT_TMEM_FULL);
+    g0 += n_t;
+    mbar_wait(acc_full, it & 1, wctx, STATUS_TIMEOUT_TMEM_FULL);
     tc_fence_after();
     const bool live = row_g < p.S;
     __nv_bfloat16* d1 = p.out1 + row_g * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
@@ -757,6 +1140,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
           }
         }
       }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(acc_empty);  // the accumulators may be overwritten by the next item
     }
   }
 
@@ -817,8 +1204,12 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   static bool set64 = false, set128 = false;
   if (D == 64) {
     const int smem = 16384 * 5 + 1 * 32768 + 256;   // single-buffered: two CTAs per SM
-    if (!set64) { if (set_smem(flash_fwd_kernel<64, 1>, smem)) return -10; set64 = true; }
-    flash_fwd_kernel<64, 1><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+    (void)smem;
+    if (!set64) { if (set_smem(flash_fwd64_kernel, FWD64_SMEM)) return -10; set64 = true; }
+    const int n_pairs = (static_cast<int>(grid.x) + 1) / 2;
+    const int n_items = n_pairs * B * nh;
+    const int ctas = std::min(n_items, gfs_host::sm_count());
+    flash_fwd64_kernel<<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
   } else {
     const int smem = 32768 * 5 + 2 * 32768 + 256;
     if (!set128) { if (set_smem(flash_fwd_kernel<128, 2>, smem)) return -10; set128 = true; }
@@ -871,7 +1262,9 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p.status = gfs_host::status_words();
   p.rope_cos = static_cast<const float*>(rope_cos);
   p.rope_sin = static_cast<const float*>(rope_sin);
-  const dim3 grid((S + 127) / 128, B * nh);
+  const int n_rt = (S + 127) / 128;
+  const int n_items = n_rt * B * nh;
+  const int ctas = std::min(n_items, gfs_host::sm_count());
   const int nbuf = 2;
   const int bwd_threads = 64 + 32 * 8;
   const int ts = (D == 64) ? 4 : 3;
@@ -887,15 +1280,15 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   if (D == 64) {
     if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 4>, smem)) return -10; set_done[0] = true; }
     if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 4>, smem)) return -10; set_done[1] = true; }
-    flash_bwd_kernel<64, 0, 2, 8, 4><<<grid, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    flash_bwd_kernel<64, 0, 2, 8, 4><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<64, 1, 2, 8, 4><<<grid, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<64, 1, 2, 8, 4><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
   } else {
     if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3>, smem)) return -10; set_done[2] = true; }
     if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3>, smem)) return -10; set_done[3] = true; }
-    flash_bwd_kernel<128, 0, 2, 8, 3><<<grid, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0);
+    flash_bwd_kernel<128, 0, 2, 8, 3><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<128, 1, 2, 8, 3><<<grid, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1);
+    flash_bwd_kernel<128, 1, 2, 8, 3><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
