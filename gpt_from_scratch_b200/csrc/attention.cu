@@ -41,6 +41,26 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 }
 
 // A K-major [rows x K] (64-column blocks a_blk bytes apart), B K-major [N x K] (blocks b_blk apart).
+// Classifies a (32-row warp slice) x (column chunk) block of the score matrix against the
+// causal / sequence-end mask: 0 = every element alive, 1 = mixed, 2 = every element dead.
+// KEY_ROWS: rows are key positions and columns are query positions (dead when col < row);
+// otherwise rows are queries and columns are keys (dead when col > row). Warp-uniform.
+template <bool KEY_ROWS>
+__device__ __forceinline__ int mask_class(int row_min, int row_max, int col_min, int col_max, bool causal, int S) {
+  if (col_min >= S) return 2;
+  bool all_alive = col_max < S, all_dead = false;
+  if (causal) {
+    if (KEY_ROWS) {
+      all_alive = all_alive && col_min >= row_max;
+      all_dead = col_max < row_min;
+    } else {
+      all_alive = all_alive && col_max <= row_min;
+      all_dead = col_min > row_max;
+    }
+  }
+  return all_dead ? 2 : (all_alive ? 0 : 1);
+}
+
 template <int KSTEPS>
 __device__ __forceinline__ void mma_kk(uint32_t d, uint32_t a, uint32_t a_blk, uint32_t b, uint32_t b_blk,
                                        uint32_t idesc, bool accumulate) {
@@ -608,8 +628,17 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         tc_fence_after();
         float mx0 = -INFINITY, mx1 = -INFINITY;
         uint32_t va[32], vb[32];
+        // per 32-column chunk: alive / mixed / dead for this warp's 32 rows (dead chunks cost no
+        // exponentials: on the diagonal block that is 3/8 of the work)
+        const int row_lo = qtx * 128 + quarter * 32;
+        auto kind_of = [&](int cc) {
+          return need_mask ? mask_class<false>(row_lo, row_lo + 31, j * 128 + cc, j * 128 + cc + 31, p.causal != 0, p.S)
+                           : 0;
+        };
         auto max_chunk = [&](const uint32_t (&v)[32], int cc) {
-          if (need_mask) {
+          const int kind = kind_of(cc);
+          if (kind == 2) return;
+          if (kind == 1) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const int col_g = j * 128 + cc + e;
@@ -665,8 +694,17 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           tmem_st_32x16(p_addr + (cc >> 1), packed);
         };
         auto prob_chunk = [&](const uint32_t (&v)[32], int cc) {
-          if (need_mask) prob_chunk_impl(std::true_type{}, v, cc);
-          else prob_chunk_impl(std::false_type{}, v, cc);
+          const int kind = kind_of(cc);
+          if (kind == 2) {
+            uint32_t zeros[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) zeros[e] = 0u;
+            tmem_st_32x16(p_addr + (cc >> 1), zeros);
+          } else if (kind == 1) {
+            prob_chunk_impl(std::true_type{}, v, cc);
+          } else {
+            prob_chunk_impl(std::false_type{}, v, cc);
+          }
         };
         tmem_ld_wait_for(va);
         tmem_ld_32x32(s_addr + 32, vb);
@@ -1060,8 +1098,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         }
       };
       auto grad_chunk = [&](const uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
-        if (need_mask) grad_chunk_impl(std::true_type{}, xv, yv, c);
-        else grad_chunk_impl(std::false_type{}, xv, yv, c);
+        // alive / mixed / dead for this warp's 32 rows x 32 columns; a dead chunk costs no math
+        const int row_lo = rt * 128 + quarter * 32;
+        const int kind = need_mask ? mask_class<MODE == 0>(row_lo, row_lo + 31, ti * 64 + c, ti * 64 + c + 31,
+                                                           p.causal != 0, p.S)
+                                   : 0;
+        if (kind == 2 && PT) {
+          uint32_t zeros[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) zeros[e] = 0u;
+          const uint32_t pt = tmem_base + lane_base + PT_COL + sb * 64 + (c >> 1);
+          if (MODE == 0) tmem_st_32x16(pt, zeros);
+          tmem_st_32x16(pt + 32, zeros);
+        } else if (kind != 0) {
+          grad_chunk_impl(std::true_type{}, xv, yv, c);
+        } else {
+          grad_chunk_impl(std::false_type{}, xv, yv, c);
+        }
       };
       const uint32_t x_addr = tmem_base + lane_base + sb * 64;
       const uint32_t y_addr = tmem_base + lane_base + Y_COL + sb * 64;

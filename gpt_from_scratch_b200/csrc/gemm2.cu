@@ -11,8 +11,12 @@
 // by both CTAs are signalled twice (own address and the peer's address obtained with
 // mapa), so no multicast form of any instruction is used. TMA loads are plain per-CTA loads.
 //
-// Same operand layouts, addend and rotary epilogues as gemm.cu; no split-K and no fused
-// collectives here (those stay on the single-CTA kernel).
+// Same operand layouts, addend and rotary epilogues as gemm.cu; no split-K. The fused
+// collectives of gemm.cu exist here too (template parameter COMM, two extra warps per CTA):
+// all-gather of A's row shards before the product (each CTA pushes a slice of the local shard
+// to every peer; the producers wait per row chunk for its arrival) and reduce-scatter of the
+// product's rows after it (the epilogue stores partial tiles into the owner's staging area,
+// the extra warps sum what the peers delivered). Peer traffic is plain loads/stores.
 #include <algorithm>
 #include <cstdio>
 
@@ -28,6 +32,23 @@ constexpr int BN = 256;        // output columns per tile
 constexpr int BK = 64;
 constexpr int STAGES = 6;
 constexpr int THREADS = 192;
+constexpr int COMM_THREADS = 64;
+constexpr int MAX_PEERS = 8;
+enum CommMode : int { COMM_NONE = 0, COMM_ALLGATHER = 1, COMM_REDUCE_SCATTER = 2 };
+
+struct CommParams {
+  int world, rank;
+  int rows_per_rank;                    // rows of the sharded dimension per rank (multiple of 256)
+  const __nv_bfloat16* ag_src;          // all-gather: local shard [rows_per_rank, ag_cols], pitch ag_ld
+  int ag_ld, ag_cols;
+  __nv_bfloat16* peer_buf[MAX_PEERS];   // AG: gathered [world*rows_per_rank, ag_cols]; RS: staging [world][rows_per_rank][N]
+  __nv_bfloat16* rs_out;                // reduce-scatter: out[rows_per_rank, N] = sum of partial rows (+ residual)
+  const __nv_bfloat16* rs_res;
+  int rs_ld_out, rs_ld_res;
+  uint32_t* peer_flags[MAX_PEERS];      // flags[p][src]: progress of rank src's writes into rank p
+  uint32_t target;                      // value flags[rank][src] must reach in this call
+  unsigned long long wait_ns;
+};
 constexpr int A_BYTES = BM * BK * 2;     // 16 KB
 constexpr int B_BYTES = BNH * BK * 2;    // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -44,7 +65,27 @@ struct Params2 {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols, rope_d, rope_b;
+  CommParams comm;
 };
+
+// Tile t -> first row of the pair tile, first column, and (fused collectives) the row chunk.
+// The collectives walk the ranks' row chunks in a rotated order: all-gather starts with the
+// local chunk (already in place), reduce-scatter ends with it.
+template <int COMM>
+__device__ __forceinline__ void decode_tile2(const Params2& p, int t, int& m0, int& n0, int& chunk) {
+  if (COMM == COMM_NONE) {
+    m0 = (t / p.tiles_n) * 256;
+    n0 = (t % p.tiles_n) * BN;
+    chunk = 0;
+  } else {
+    const int tiles_per_chunk = (p.comm.rows_per_rank / 256) * p.tiles_n;
+    const int ci = t / tiles_per_chunk;
+    const int rem = t - ci * tiles_per_chunk;
+    chunk = (p.comm.rank + ci + (COMM == COMM_REDUCE_SCATTER ? 1 : 0)) % p.comm.world;
+    m0 = chunk * p.comm.rows_per_rank + (rem / p.tiles_n) * 256;
+    n0 = (rem % p.tiles_n) * BN;
+  }
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -99,8 +140,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
                : "memory");
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+template <bool A_MN, bool B_MN, int COMM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
              const Params2 p) {
   extern __shared__ uint8_t smem_raw[];
@@ -154,9 +195,21 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t chunk_ready = 0;  // all-gather: chunks whose arrival has been observed
       for (int t = pair; t < total_tiles; t += num_pairs) {
-        const int m0 = (t / p.tiles_n) * 256 + static_cast<int>(rank) * BM;
-        const int n0 = (t % p.tiles_n) * BN + static_cast<int>(rank) * BNH;
+        int m0, n0, chunk;
+        decode_tile2<COMM>(p, t, m0, n0, chunk);
+        m0 += static_cast<int>(rank) * BM;
+        n0 += static_cast<int>(rank) * BNH;
+        if (COMM == COMM_ALLGATHER && !((chunk_ready >> chunk) & 1u)) {
+          // rows of this chunk are written into our gathered buffer by rank `chunk`
+          if (!*abort_flag &&
+              !wait_flag_reached(p.comm.peer_flags[p.comm.rank] + chunk, p.comm.target, p.comm.wait_ns, p.status,
+                                 0xA7000000u | (chunk << 8) | p.comm.rank))
+            *abort_flag = 1u;
+          fence_proxy_async_global();  // peer's generic-proxy stores -> our TMA (async proxy) loads
+          chunk_ready |= 1u << chunk;
+        }
         for (int kb = 0; kb < p.kblocks; ++kb) {
           mbar_wait(&empty_bar[stage], phase ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
           uint8_t* sa = tiles + stage * STAGE_BYTES;
@@ -228,7 +281,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue (both CTAs, own accumulator half) ------------------------------
     const int q = warp & 3;
     int acc = 0;
@@ -237,9 +290,28 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     const int rrow = lane >> 3;
     const int rch = lane & 7;
     const bool has_add = (p.R != nullptr);
+    // The addend of a 64-column chunk is fetched one chunk ahead (across tile boundaries too), so
+    // its global-memory latency is covered by the previous chunk's work instead of stalling this one.
+    uint4 pre[8];
+    auto load_addend = [&](uint4 (&dst)[8], int mm0, int col0) {
+      const int gc = col0 + rch * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int grow = mm0 + q * 32 + i * 4 + rrow;
+        dst[i] = make_uint4(0, 0, 0, 0);
+        if (grow < p.M && gc + 8 <= p.N)
+          dst[i] = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(grow) * p.ldr + gc);
+      }
+    };
+    if (has_add && pair < total_tiles) {
+      int fm0, fn0, fchunk;
+      decode_tile2<COMM>(p, pair, fm0, fn0, fchunk);
+      load_addend(pre, fm0 + static_cast<int>(rank) * BM, fn0);
+    }
     for (int t = pair; t < total_tiles; t += num_pairs) {
-      const int m0 = (t / p.tiles_n) * 256 + static_cast<int>(rank) * BM;
-      const int n0 = (t % p.tiles_n) * BN;
+      int m0, n0, chunk;
+      decode_tile2<COMM>(p, t, m0, n0, chunk);
+      m0 += static_cast<int>(rank) * BM;
       mbar_wait(&tmem_full[acc], acc_phase, wctx, STATUS_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
@@ -248,14 +320,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         const int col0 = n0 + c;
         if (col0 >= p.N) break;
         const int gcol = col0 + rch * 8;
-        uint4 pre[8];
+        uint4 cur[8];
         if (has_add) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int grow = m0 + q * 32 + i * 4 + rrow;
-            pre[i] = make_uint4(0, 0, 0, 0);
-            if (grow < p.M && gcol + 8 <= p.N)
-              pre[i] = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(grow) * p.ldr + gcol);
+          for (int i = 0; i < 8; ++i) cur[i] = pre[i];
+          if (c + 64 < BN && col0 + 64 < p.N) {
+            load_addend(pre, m0, col0 + 64);
+          } else if (t + num_pairs < total_tiles) {
+            int nm0, nn0, nchunk;
+            decode_tile2<COMM>(p, t + num_pairs, nm0, nn0, nchunk);
+            load_addend(pre, nm0 + static_cast<int>(rank) * BM, nn0);
           }
         }
         uint32_t va[32], vb[32];
@@ -301,7 +375,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
                 f[6] = a6 * cs.w - a7 * sn.w; f[7] = a6 * sn.w + a7 * cs.w;
               }
               if (has_add) {
-                const uint4 rr = pre[i];
+                const uint4 rr = cur[i];
                 const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
                              r3 = unpack_bf16x2(rr.w);
                 f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
@@ -312,7 +386,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
               w.z = pack_bf16x2(f[4], f[5]);
               w.w = pack_bf16x2(f[6], f[7]);
             }
-            *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(grow) * p.ldc + gcol) = w;
+            __nv_bfloat16* dst;
+            if (COMM == COMM_REDUCE_SCATTER) {
+              // partial rows go to their owner's staging area, slot of this (source) rank
+              dst = p.comm.peer_buf[chunk] +
+                    (static_cast<size_t>(p.comm.rank) * p.comm.rows_per_rank +
+                     (grow - chunk * p.comm.rows_per_rank)) * p.N + gcol;
+            } else {
+              dst = p.C + static_cast<size_t>(grow) * p.ldc + gcol;
+            }
+            *reinterpret_cast<uint4*>(dst) = w;
           }
         }
         __syncwarp();
@@ -320,11 +403,90 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       // the accumulator buffer may be overwritten once all 8 epilogue warps of the pair are done
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+      if (lane == 0) {
+        mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+        if (COMM == COMM_REDUCE_SCATTER) red_release_sys_add_u32(p.comm.peer_flags[chunk] + p.comm.rank, 1u);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
       }
+    }
+  } else if (COMM == COMM_ALLGATHER) {
+    // ------------------------------ all-gather push (warps 6-7) ------------------------------
+    // Every CTA pushes its slice of the local shard into every rank's gathered buffer
+    // (own rank first), then bumps that rank's counter for this source.
+    const CommParams& c = p.comm;
+    const int ct = threadIdx.x - THREADS;
+    const int rpc = (c.rows_per_rank + gridDim.x - 1) / gridDim.x;
+    const int r0 = min(c.rows_per_rank, static_cast<int>(blockIdx.x) * rpc);
+    const int r1 = min(c.rows_per_rank, r0 + rpc);
+    const int vpr = c.ag_cols >> 3;
+    const int nvec = (r1 - r0) * vpr;
+    for (int i = 0; i < c.world; ++i) {
+      const int peer = (c.rank + i) % c.world;
+      __nv_bfloat16* dst = c.peer_buf[peer] + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
+      for (int v = ct; v < nvec; v += COMM_THREADS * 4) {
+        uint4 tmp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int vv = v + u * COMM_THREADS;
+          if (vv < nvec) {
+            const int row = r0 + vv / vpr;
+            tmp[u] = *reinterpret_cast<const uint4*>(c.ag_src + static_cast<size_t>(row) * c.ag_ld + (vv % vpr) * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int vv = v + u * COMM_THREADS;
+          if (vv < nvec) {
+            const int row = r0 + vv / vpr;
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * c.ag_cols + (vv % vpr) * 8) = tmp[u];
+          }
+        }
+      }
+      __threadfence_system();
+      named_barrier_sync(1, COMM_THREADS);
+      if (ct == 0) red_release_sys_add_u32(c.peer_flags[peer] + c.rank, 1u);
+    }
+  } else if (COMM == COMM_REDUCE_SCATTER) {
+    // ------------------------------ reduce (warps 6-7) ------------------------------
+    // Wait until every rank (this one included) has delivered all partial tiles of our row
+    // chunk, then sum the staged partials in rank order, add the residual, round once.
+    const CommParams& c = p.comm;
+    const int ct = threadIdx.x - THREADS;
+    bool ok = true;
+    for (int src = 0; src < c.world; ++src)
+      ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
+                             0xB7000000u | (src << 8) | c.rank) && ok;
+    if (!ok) *abort_flag = 1u;
+    const __nv_bfloat16* stage = c.peer_buf[c.rank];
+    const int vpr = p.N >> 3;
+    const size_t total = static_cast<size_t>(c.rows_per_rank) * vpr;
+    const size_t chunk_elems = static_cast<size_t>(c.rows_per_rank) * p.N;
+    for (size_t v = static_cast<size_t>(blockIdx.x) * COMM_THREADS + ct; v < total;
+         v += static_cast<size_t>(gridDim.x) * COMM_THREADS) {
+      const int row = static_cast<int>(v / vpr);
+      const int col = static_cast<int>(v % vpr) << 3;
+      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int src = 0; src < c.world; ++src) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + src * chunk_elems + static_cast<size_t>(row) * p.N + col);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
+      }
+      if (c.rs_res != nullptr) {
+        const uint4 u = *reinterpret_cast<const uint4*>(c.rs_res + static_cast<size_t>(row) * c.rs_ld_res + col);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
+        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc8[0], acc8[1]);
+      o.y = pack_bf16x2(acc8[2], acc8[3]);
+      o.z = pack_bf16x2(acc8[4], acc8[5]);
+      o.w = pack_bf16x2(acc8[6], acc8[7]);
+      *reinterpret_cast<uint4*>(c.rs_out + static_cast<size_t>(row) * c.rs_ld_out + col) = o;
     }
   }
 
@@ -336,16 +498,20 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int COMM = COMM_NONE>
 int launch2(const CUtensorMap* ta, const CUtensorMap* tb, const Params2& p, int grid, cudaStream_t stream) {
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+  auto kern = gemm2_kernel<A_MN, B_MN, COMM>;
   static bool attr_set = false;
-  if (!attr_set) {
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set || attr_dev != dev) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess)
       return -10;
     attr_set = true;
+    attr_dev = dev;
   }
-  kern<<<grid, THREADS, SMEM_TOTAL, stream>>>(*ta, *tb, p);
+  kern<<<grid, THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), SMEM_TOTAL, stream>>>(*ta, *tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -388,6 +554,76 @@ int gfs_gemm2_bf16(const void* A, const void* B, void* C, const void* R, int M, 
   if (!a_mn_major && b_mn_major) return launch2<false, true>(ta, tb, p, grid, stream);
   if (a_mn_major && b_mn_major) return launch2<true, true>(ta, tb, p, grid, stream);
   return launch2<true, false>(ta, tb, p, grid, stream);
+}
+
+// Fused collective + GEMM on CTA pairs; same contract as gfs_gemm_bf16_comm (gemm.cu) with the
+// extra requirement that M/world is a multiple of 256. Returns -20 when the problem does not
+// qualify, in which case the caller uses the single-CTA kernel (nothing has been launched and
+// *target_inout is unchanged).
+int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
+                        const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
+                        const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
+                        unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
+                        int rope_d, int rope_b, long long wait_ns, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (mode != COMM_ALLGATHER && mode != COMM_REDUCE_SCATTER) return -1;
+  if (world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return -1;
+  if (M <= 0 || N <= 0 || K <= 0 || (M % world) != 0) return -1;
+  if (((M / world) % 256) != 0 || N < 256 || K < 256) return -20;
+  if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
+  const int rows_per_rank = M / world;
+  Params2 p{};
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / 256;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.kblocks = (K + BK - 1) / BK;
+  p.status = gfs_host::status_words();
+  p.rope_cos = static_cast<const float*>(rope_cos);
+  p.rope_sin = static_cast<const float*>(rope_sin);
+  p.rope_cols = rope_cols; p.rope_d = rope_d; p.rope_b = rope_b > 0 ? rope_b : 1;
+  CommParams& c = p.comm;
+  c.world = world; c.rank = rank; c.rows_per_rank = rows_per_rank;
+  c.wait_ns = wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : 20000000000ull;
+  for (int i = 0; i < world; ++i) {
+    c.peer_buf[i] = reinterpret_cast<__nv_bfloat16*>(peer_bufs[i]);
+    c.peer_flags[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+  }
+  const int pairs = std::min(p.tiles_m * p.tiles_n, gfs_host::sm_count() / 2);
+  const int grid = 2 * pairs;
+  const void* a_base;
+  int a_ld;
+  unsigned int increment;
+  if (mode == COMM_ALLGATHER) {
+    c.ag_src = static_cast<const __nv_bfloat16*>(a);
+    c.ag_ld = lda;
+    c.ag_cols = K;
+    a_base = c.peer_buf[rank];   // the GEMM reads the local gathered buffer
+    a_ld = K;
+    p.C = static_cast<__nv_bfloat16*>(out);
+    p.ldc = ldo;
+    increment = static_cast<unsigned int>(grid);   // every CTA of a source signals once per destination
+  } else {
+    a_base = a;
+    a_ld = lda;
+    c.rs_out = static_cast<__nv_bfloat16*>(out);
+    c.rs_ld_out = ldo;
+    c.rs_res = static_cast<const __nv_bfloat16*>(residual);
+    c.rs_ld_res = ldr;
+    increment = static_cast<unsigned int>((rows_per_rank / 256) * p.tiles_n * 8);  // 8 epilogue warps per pair tile
+  }
+  if ((reinterpret_cast<uintptr_t>(a_base) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return -2;
+  const CUtensorMap* ta = gfs_host::tmap_2d_cached(a_base, M, K, a_ld, BM, 64);
+  const CUtensorMap* tb = b_mn_major ? gfs_host::tmap_2d_cached(B, K, N, ldb, 64, 64)
+                                     : gfs_host::tmap_2d_cached(B, N, K, ldb, BNH, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+  *target_inout += increment;
+  c.target = *target_inout;
+  if (mode == COMM_ALLGATHER)
+    return b_mn_major ? launch2<false, true, COMM_ALLGATHER>(ta, tb, p, grid, stream)
+                      : launch2<false, false, COMM_ALLGATHER>(ta, tb, p, grid, stream);
+  return b_mn_major ? launch2<false, true, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream)
+                    : launch2<false, false, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream);
 }
 
 }  // extern "C"

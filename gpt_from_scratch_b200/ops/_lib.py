@@ -79,6 +79,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
         "gfs_gemm_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
                                 ctypes.c_longlong, vp], i),
+        "gfs_gemm2_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
+                                 ctypes.c_longlong, vp], i),
         "gfs_symm_barrier": ([ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_allgather": ([vp, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_embedding_scatter": ([vp, vp, i, i, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),

@@ -7,6 +7,7 @@ reference with ONE of our kernels that moves the data over peer memory while it 
                                 row-parallel dgrad)            csrc/gemm.cu, mode 1
 * :func:`linear_reduce_scatter` GEMM -> reduce-scatter (+ residual)    (row-parallel forward,
                                 column-parallel dgrad)         csrc/gemm.cu, mode 2
+                                (both also on CTA pairs for large problems: csrc/gemm2.cu)
 * :func:`embedding_reduce_scatter` embedding lookup written straight into the owner's
                                 sequence shard                 csrc/comm.cu
 * :func:`ce_exchange_combine`   cross-entropy statistics exchange + combine   csrc/comm.cu
@@ -52,11 +53,18 @@ def _gemm_comm(mode: int, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, r
         rc_args = (cos.data_ptr(), sin.data_ptr(), rope_cols, head_dim, batch)
     else:
         rc_args = (0, 0, 0, 0, 1)
-    rc = _lib.lib().gfs_gemm_bf16_comm(
-        mode, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
-        _lib.ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, 1 if b_mn_major else 0,
-        grp.world, grp.rank, buf.ptrs, _site_flag_ptrs(grp, site), ctypes.byref(site.target), *rc_args, WAIT_NS,
-        _lib.stream_ptr())
+    args = (mode, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
+            _lib.ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, 1 if b_mn_major else 0,
+            grp.world, grp.rank, buf.ptrs, _site_flag_ptrs(grp, site), ctypes.byref(site.target), *rc_args, WAIT_NS,
+            _lib.stream_ptr())
+    # CTA-pair kernel when the problem has enough 256 x 256 tiles (every rank takes the same
+    # decision: it depends on the global shape only); -20 = not eligible, nothing launched
+    if gemm_ops._PAIR_ENABLED and (M // 256) * ((N + 255) // 256) >= gemm_ops._PAIR_MIN_TILES:
+        rc = _lib.lib().gfs_gemm2_bf16_comm(*args)
+        if rc != -20:
+            _lib.check(rc, "gfs_gemm2_bf16_comm")
+            return
+    rc = _lib.lib().gfs_gemm_bf16_comm(*args)
     _lib.check(rc, "gfs_gemm_bf16_comm")
 
 

@@ -37,47 +37,58 @@ def main():
     log = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
 
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    S, B, K, N = 128 * world * 2, 2, 256, 384
-    Ss = S // world
-    # ---- all-gather -> GEMM (column parallel) ----
-    x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
-    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
-    dy = torch.randn(S, B, N, device=dev, generator=g).bfloat16()
-    dist.broadcast(dy, 0)   # the gradient w.r.t. a column-parallel output differs per rank in general; any value works
-    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
-    ya = fused_comm.allgather_linear(xa, wa)
-    ya.backward(dy)
-    xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
-    yb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
-    yb.backward(dy)
-    torch.cuda.synchronize()
-    assert torch.equal(ya, yb), "AG->GEMM forward differs from NCCL all-gather + GEMM"
-    close(xa.grad, xb.grad, "AG->GEMM dX (GEMM->RS)")
-    close(wa.grad, wb.grad, "AG->GEMM dW", 1e-3)
-    log("allgather_linear ok")
-
-    # ---- GEMM -> reduce-scatter (row parallel) ----
-    xr = torch.randn(S, B, K, device=dev, generator=g).bfloat16()
-    wr = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
-    res = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
-    dout = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
-    for use_res in (False, True):
-        xa, wa = xr.clone().requires_grad_(), wr.clone().requires_grad_()
-        ra = res.clone().requires_grad_() if use_res else None
-        ya = fused_comm.linear_reduce_scatter(xa, wa, ra)
-        ya.backward(dout)
-        xb, wb = xr.clone().requires_grad_(), wr.clone().requires_grad_()
-        yb = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(xb, wb))
-        if use_res:
-            yb = yb + res
-        yb.backward(dout)
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    # second pass: shapes that qualify for the CTA-pair kernel (rows per rank a multiple of 256),
+    # with its tile-count threshold lowered so that these small problems take it
+    for S, B, K, N, pair_min in ((128 * world * 2, 2, 256, 384, None), (256 * world, 2, 256, 512, 1)):
+        saved_min = gemm_ops._PAIR_MIN_TILES
+        if pair_min is not None:
+            gemm_ops._PAIR_MIN_TILES = pair_min
+        log(f"shapes S={S} B={B} K={K} N={N} pair_min_tiles={gemm_ops._PAIR_MIN_TILES}")
+        Ss = S // world
+        # ---- all-gather -> GEMM (column parallel) ----
+        x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+        dy = torch.randn(S, B, N, device=dev, generator=g).bfloat16()
+        dist.broadcast(dy, 0)   # the gradient w.r.t. a column-parallel output differs per rank in general; any value works
+        xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+        ya = fused_comm.allgather_linear(xa, wa)
+        ya.backward(dy)
+        xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+        yb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
+        yb.backward(dy)
         torch.cuda.synchronize()
-        close(ya, yb, f"GEMM->RS forward (residual={use_res})")
-        close(xa.grad, xb.grad, "GEMM->RS dX (AG->GEMM)", 1e-3)
-        close(wa.grad, wb.grad, "GEMM->RS dW", 1e-3)
-        if use_res:
-            assert torch.equal(ra.grad, dout)
-    log("linear_reduce_scatter ok")
+        assert torch.equal(ya, yb), "AG->GEMM forward differs from NCCL all-gather + GEMM"
+        close(xa.grad, xb.grad, "AG->GEMM dX (GEMM->RS)")
+        close(wa.grad, wb.grad, "AG->GEMM dW", 1e-3)
+        log("allgather_linear ok")
+
+        # ---- GEMM -> reduce-scatter (row parallel) ----
+        xr = torch.randn(S, B, K, device=dev, generator=g).bfloat16()
+        wr = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+        res = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+        dout = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+        for use_res in (False, True):
+            xa, wa = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+            ra = res.clone().requires_grad_() if use_res else None
+            ya = fused_comm.linear_reduce_scatter(xa, wa, ra)
+            ya.backward(dout)
+            xb, wb = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+            yb = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(xb, wb))
+            if use_res:
+                yb = yb + res
+            yb.backward(dout)
+            torch.cuda.synchronize()
+            close(ya, yb, f"GEMM->RS forward (residual={use_res})")
+            close(xa.grad, xb.grad, "GEMM->RS dX (AG->GEMM)", 1e-3)
+            close(wa.grad, wb.grad, "GEMM->RS dW", 1e-3)
+            if use_res:
+                assert torch.equal(ra.grad, dout)
+        log("linear_reduce_scatter ok")
+
+        gemm_ops._PAIR_MIN_TILES = saved_min
+    S, B = 128 * world * 2, 2
+    Ss = S // world
 
     # ---- embedding -> reduce-scatter ----
     V, H = 1024, 256
