@@ -498,6 +498,247 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------
+// Grouped weight-gradient GEMM: up to MAX_GROUP independent problems C_g[M_g, N_g] (+)= A_g^T B_g
+// (A_g = [K, M_g], B_g = [K, N_g], both row-major, i.e. MN-major operands) in ONE launch. The
+// weight gradients of a transformer layer are many-K, few-tile problems (hidden x hidden
+// outputs, K = tokens); one by one they fill a fraction of the SMs, together they fill a wave.
+// ---------------------------------------------------------------------------
+constexpr int MAX_GROUP = 4;
+
+struct GroupMaps {
+  CUtensorMap a[MAX_GROUP];
+  CUtensorMap b[MAX_GROUP];
+};
+
+struct GroupProblem {
+  int M, N, ldc;
+  int tiles_n, tile_begin, kblocks;
+  int accumulate;        // add the product to C instead of overwriting it
+  __nv_bfloat16* C;
+};
+
+struct GroupParams {
+  int ngroups, total_tiles;
+  GroupProblem g[MAX_GROUP];
+  uint32_t* status;
+};
+
+__device__ __forceinline__ int group_of_tile(const GroupParams& p, int t) {
+  int gi = 0;
+#pragma unroll
+  for (int i = 1; i < MAX_GROUP; ++i)
+    if (i < p.ngroups && t >= p.g[i].tile_begin) gi = i;
+  return gi;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm2_grouped_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant__ GroupParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + EPI_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full = bars + 2 * STAGES;
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = (rank == 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    for (int i = 0; i < p.ngroups; ++i) {
+      tma_prefetch_desc(&maps.a[i]);
+      tma_prefetch_desc(&maps.b[i]);
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
+
+  const int num_pairs = gridDim.x >> 1;
+  const int pair = blockIdx.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < p.total_tiles; t += num_pairs) {
+        const int gi = group_of_tile(p, t);
+        const GroupProblem& g = p.g[gi];
+        const int lt = t - g.tile_begin;
+        const int m0 = (lt / g.tiles_n) * 256 + static_cast<int>(rank) * BM;
+        const int n0 = (lt % g.tiles_n) * BN + static_cast<int>(rank) * BNH;
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, wctx, STATUS_TIMEOUT_PIPE_EMPTY);
+          uint8_t* sa = tiles + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * 8192, &maps.a[gi], bar, m0 + 64 * i, k0);
+#pragma unroll
+          for (int i = 0; i < BNH / 64; ++i) tma_load_2d_pair(sb + i * 8192, &maps.b[gi], bar, n0 + 64 * i, k0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = pair; t < p.total_tiles; t += num_pairs) {
+        const int kblocks = p.g[group_of_tile(p, t)].kblocks;
+        mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, wctx, STATUS_TIMEOUT_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          mbar_wait(&full_bar[stage], phase, wctx, STATUS_TIMEOUT_PIPE_FULL);
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = umma_desc_sw128(sa + k * 2048, 8192, 1024);
+            const uint64_t bdesc = umma_desc_sw128(sb + k * 2048, 8192, 1024);
+            umma_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(mapa_u32(smem_u32(&empty_bar[stage]), 0));
+          umma_commit_pair(mapa_u32(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit_pair(mapa_u32(smem_u32(&tmem_full[acc]), 0));
+        umma_commit_pair(mapa_u32(smem_u32(&tmem_full[acc]), 1));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint8_t* ebuf = epi_smem + (warp - 2) * 4096;
+    const int rrow = lane >> 3;
+    const int rch = lane & 7;
+    for (int t = pair; t < p.total_tiles; t += num_pairs) {
+      const GroupProblem& g = p.g[group_of_tile(p, t)];
+      const int lt = t - g.tile_begin;
+      const int m0 = (lt / g.tiles_n) * 256 + static_cast<int>(rank) * BM;
+      const int n0 = (lt % g.tiles_n) * BN;
+      mbar_wait(&tmem_full[acc], acc_phase, wctx, STATUS_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 64) {
+        const int col0 = n0 + c;
+        if (col0 >= g.N) break;
+        const int gcol = col0 + rch * 8;
+        uint4 pre[8];
+        if (g.accumulate) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int grow = m0 + q * 32 + i * 4 + rrow;
+            pre[i] = make_uint4(0, 0, 0, 0);
+            if (grow < g.M && gcol + 8 <= g.N)
+              pre[i] = *reinterpret_cast<const uint4*>(g.C + static_cast<size_t>(grow) * g.ldc + gcol);
+          }
+        }
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(t_row + c, va);
+        tmem_ld_32x32(t_row + c + 32, vb);
+        tmem_ld_wait();
+        uint8_t* myrow = ebuf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(va[8 * j + 0]), __uint_as_float(va[8 * j + 1]));
+          w.y = pack_bf16x2(__uint_as_float(va[8 * j + 2]), __uint_as_float(va[8 * j + 3]));
+          w.z = pack_bf16x2(__uint_as_float(va[8 * j + 4]), __uint_as_float(va[8 * j + 5]));
+          w.w = pack_bf16x2(__uint_as_float(va[8 * j + 6]), __uint_as_float(va[8 * j + 7]));
+          *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) = w;
+          w.x = pack_bf16x2(__uint_as_float(vb[8 * j + 0]), __uint_as_float(vb[8 * j + 1]));
+          w.y = pack_bf16x2(__uint_as_float(vb[8 * j + 2]), __uint_as_float(vb[8 * j + 3]));
+          w.z = pack_bf16x2(__uint_as_float(vb[8 * j + 4]), __uint_as_float(vb[8 * j + 5]));
+          w.w = pack_bf16x2(__uint_as_float(vb[8 * j + 6]), __uint_as_float(vb[8 * j + 7]));
+          *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = w;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + rrow;
+          const int grow = m0 + q * 32 + r;
+          uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
+          if (grow < g.M && gcol + 8 <= g.N) {
+            if (g.accumulate) {
+              const uint4 rr = pre[i];
+              const float2 x0 = unpack_bf16x2(w.x), x1 = unpack_bf16x2(w.y), x2 = unpack_bf16x2(w.z),
+                           x3 = unpack_bf16x2(w.w);
+              const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
+                           r3 = unpack_bf16x2(rr.w);
+              w.x = pack_bf16x2(x0.x + r0.x, x0.y + r0.y);
+              w.y = pack_bf16x2(x1.x + r1.x, x1.y + r1.y);
+              w.z = pack_bf16x2(x2.x + r2.x, x2.y + r2.y);
+              w.w = pack_bf16x2(x3.x + r3.x, x3.y + r3.y);
+            }
+            *reinterpret_cast<uint4*>(g.C + static_cast<size_t>(grow) * g.ldc + gcol) = w;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
 template <bool A_MN, bool B_MN, int COMM = COMM_NONE>
 int launch2(const CUtensorMap* ta, const CUtensorMap* tb, const Params2& p, int grid, cudaStream_t stream) {
   auto kern = gemm2_kernel<A_MN, B_MN, COMM>;
@@ -624,6 +865,61 @@ int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb
                       : launch2<false, false, COMM_ALLGATHER>(ta, tb, p, grid, stream);
   return b_mn_major ? launch2<false, true, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream)
                     : launch2<false, false, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream);
+}
+
+// Grouped weight gradients: for g < n, C_g[M_g, N_g] (+)= A_g^T B_g with A_g = [K_g, M_g] (pitch lda_g),
+// B_g = [K_g, N_g] (pitch ldb_g), all bf16 row-major, fp32 accumulation, one launch. n <= 4.
+// accumulate_g != 0 adds the product to the existing C_g (rounded once).
+int gfs_gemm2_wgrad_grouped(int n, const unsigned long long* A, const unsigned long long* B,
+                            const unsigned long long* C, const int* M, const int* N, const int* K, const int* lda,
+                            const int* ldb, const int* ldc, const int* accumulate, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (n <= 0) return 0;
+  if (n > MAX_GROUP) return -1;
+  GroupMaps maps;
+  GroupParams p{};
+  p.ngroups = n;
+  p.status = gfs_host::status_words();
+  int total = 0;
+  for (int i = 0; i < n; ++i) {
+    if (M[i] <= 0 || N[i] <= 0 || K[i] <= 0) return -1;
+    if ((N[i] & 7) || (M[i] & 7) || (lda[i] & 7) || (ldb[i] & 7) || (ldc[i] & 7)) return -1;
+    if ((A[i] | B[i] | C[i]) & 15) return -2;
+    const CUtensorMap* ta = gfs_host::tmap_2d_cached(reinterpret_cast<const void*>(A[i]), K[i], M[i], lda[i], 64, 64);
+    const CUtensorMap* tb = gfs_host::tmap_2d_cached(reinterpret_cast<const void*>(B[i]), K[i], N[i], ldb[i], 64, 64);
+    if (ta == nullptr || tb == nullptr) return -3;
+    maps.a[i] = *ta;
+    maps.b[i] = *tb;
+    GroupProblem& g = p.g[i];
+    g.M = M[i]; g.N = N[i]; g.ldc = ldc[i];
+    g.tiles_n = (N[i] + BN - 1) / BN;
+    g.tile_begin = total;
+    g.kblocks = (K[i] + BK - 1) / BK;
+    g.accumulate = accumulate[i];
+    g.C = reinterpret_cast<__nv_bfloat16*>(C[i]);
+    total += ((M[i] + 255) / 256) * g.tiles_n;
+  }
+  for (int i = n; i < MAX_GROUP; ++i) {
+    maps.a[i] = maps.a[0];
+    maps.b[i] = maps.b[0];
+    p.g[i] = p.g[0];
+    p.g[i].tile_begin = 0x7fffffff;
+  }
+  p.total_tiles = total;
+  static bool attr_set = false;
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set || attr_dev != dev) {
+    if (cudaFuncSetAttribute(gemm2_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) !=
+        cudaSuccess)
+      return -10;
+    attr_set = true;
+    attr_dev = dev;
+  }
+  const int pairs = std::min(total, gfs_host::sm_count() / 2);
+  gemm2_grouped_kernel<<<2 * pairs, THREADS, SMEM_TOTAL, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 }  // extern "C"

@@ -53,6 +53,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lp = POINTER(ctypes.c_longlong)
     ulp = POINTER(ctypes.c_ulonglong)
     uip = POINTER(ctypes.c_uint)
+    ip = POINTER(ctypes.c_int)
     cl = ctypes.c_long
     sigs = {
         "gfs_read_status": ([POINTER(c_uint32), i], i),
@@ -79,6 +80,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
         "gfs_gemm_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
                                 ctypes.c_longlong, vp], i),
+        "gfs_gemm2_wgrad_grouped": ([i, ulp, ulp, ulp, ip, ip, ip, ip, ip, ip, ip, vp], i),
         "gfs_gemm2_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
                                  ctypes.c_longlong, vp], i),
         "gfs_symm_barrier": ([ulp, i, i, i, uip, ctypes.c_longlong, vp], i),

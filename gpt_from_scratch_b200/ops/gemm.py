@@ -9,11 +9,12 @@ core/tensor_parallel/layers.py:47,82.
 """
 from __future__ import annotations
 
+import ctypes
+import os
+
 import torch
 
 from . import _lib
-
-import os
 
 _WS_BYTES = 96 << 20
 # CTA-pair kernel (csrc/gemm2.cu): used when the problem has at least this many 256 x 256 tiles
@@ -133,6 +134,77 @@ def linear_dgrad(dy2d: torch.Tensor, w: torch.Tensor, addend: torch.Tensor | Non
         out.copy_(dx)
         return out
     return dx
+
+
+class _WgradQueue:
+    """Weight-gradient GEMMs waiting to be launched together.
+
+    A layer's weight gradients are ``[out, in] = dY^T X`` with K = tokens: few output tiles,
+    very deep. One at a time they occupy a fraction of the SMs (or need split-K and a
+    reduction pass); several of them in ONE grouped launch (``gfs_gemm2_wgrad_grouped``) fill
+    a wave of CTA pairs. A weight gradient is only needed at the optimizer step, so problems
+    that write into a gradient sink are parked here (holding references to their operands)
+    and launched when enough tiles have accumulated or when :func:`flush_wgrad` is called
+    (the engine does so after ``backward``).
+    """
+
+    MAX_GROUP = 4
+
+    def __init__(self):
+        self.items: list[tuple] = []
+        self.tiles = 0
+
+    @staticmethod
+    def tiles_of(M: int, N: int) -> int:
+        return ((M + 255) // 256) * ((N + 255) // 256)
+
+    def push(self, dy2d, x2d, out, accumulate, done_cb) -> None:
+        self.items.append((dy2d, x2d, out, accumulate, done_cb))
+        self.tiles += self.tiles_of(dy2d.shape[1], x2d.shape[1])
+        if len(self.items) == self.MAX_GROUP or self.tiles >= _PAIR_MIN_TILES:
+            self.flush()
+
+    def flush(self) -> None:
+        items, self.items, self.tiles = self.items, [], 0
+        if not items:
+            return
+        n = len(items)
+        U, I = ctypes.c_ulonglong * n, ctypes.c_int * n
+        rc = _lib.lib().gfs_gemm2_wgrad_grouped(
+            n, U(*[it[0].data_ptr() for it in items]), U(*[it[1].data_ptr() for it in items]),
+            U(*[it[2].data_ptr() for it in items]), I(*[it[0].shape[1] for it in items]),
+            I(*[it[1].shape[1] for it in items]), I(*[it[0].shape[0] for it in items]),
+            I(*[it[0].stride(0) for it in items]), I(*[it[1].stride(0) for it in items]),
+            I(*[it[2].stride(0) for it in items]), I(*[1 if it[3] else 0 for it in items]), _lib.stream_ptr())
+        _lib.check(rc, "gfs_gemm2_wgrad_grouped")
+        for it in items:
+            if it[4] is not None:
+                it[4]()
+
+
+_wgrad_queue = _WgradQueue()
+_WGRAD_GROUPING = os.environ.get("GFS_WGRAD_GROUPING", "1") != "0"
+
+
+def flush_wgrad() -> None:
+    """Launch every parked weight-gradient GEMM (no-op when nothing is parked)."""
+    _wgrad_queue.flush()
+
+
+def linear_wgrad_to_sink(dy2d: torch.Tensor, x2d: torch.Tensor, sink) -> None:
+    """Weight gradient ``dy2d^T @ x2d`` written (or accumulated) into ``sink``'s slice of the
+    gradient buffer. Small problems are grouped (see :class:`_WgradQueue`); the operands must
+    not be modified before :func:`flush_wgrad`."""
+    out = sink.target()
+    accumulate = sink.consume_accumulate()
+    N_out, N_in = dy2d.shape[1], x2d.shape[1]
+    if (_WGRAD_GROUPING and _PAIR_ENABLED and use_native(dy2d, x2d, out)
+            and _WgradQueue.tiles_of(N_out, N_in) < _PAIR_MIN_TILES and dy2d.shape[0] >= 256
+            and N_out % 8 == 0 and N_in % 8 == 0 and out.stride(1) == 1 and out.stride(0) % 8 == 0):
+        _wgrad_queue.push(_rowmajor_2d(dy2d), _rowmajor_2d(x2d), out, accumulate, sink.done)
+        return
+    linear_wgrad(dy2d, x2d, out=out, accumulate=accumulate)
+    sink.done()
 
 
 def linear_wgrad(dy2d: torch.Tensor, x2d: torch.Tensor, out: torch.Tensor | None = None,

@@ -76,14 +76,12 @@ class _FusedMLP(torch.autograd.Function):
             _lib.check(rc, "gfs_swiglu_bwd")
         dw_down = dw_gu = None
         if sink_down is not None:
-            gemm_ops.linear_wgrad(d2, act, out=sink_down.target(), accumulate=sink_down.consume_accumulate())
-            sink_down.done()
+            gemm_ops.linear_wgrad_to_sink(d2, act, sink_down)
         else:
             dw_down = gemm_ops.linear_wgrad(d2, act)
         dx = gemm_ops.linear_dgrad(dgu, w_gu).view(ctx.in_shape)
         if sink_gu is not None:
-            gemm_ops.linear_wgrad(dgu, x2, out=sink_gu.target(), accumulate=sink_gu.consume_accumulate())
-            sink_gu.done()
+            gemm_ops.linear_wgrad_to_sink(dgu, x2, sink_gu)
         else:
             dw_gu = gemm_ops.linear_wgrad(dgu, x2)
         return dx, dw_gu, dw_down, (dout if ctx.has_res else None), None, None

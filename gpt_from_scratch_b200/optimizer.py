@@ -35,6 +35,7 @@ import torch
 import torch.distributed as dist
 
 from .ops import adam as adam_ops
+from .ops import gemm as gemm_ops
 from .parallel import mappings
 from .parallel import parallel_state as ps
 
@@ -126,6 +127,7 @@ class DistributedOptimizer:
     def zero_grad(self, set_to_zero: bool = False):
         """Prepare the gradient buffer for a new step. Never sets ``.grad`` to None (the
         views into the flat buffer must survive)."""
+        gemm_ops.flush_wgrad()   # nothing parked may land in the buffer after this point
         if self.use_fused_kernels and not set_to_zero:
             for p in self.params:
                 p._grad_fresh = True
@@ -149,6 +151,7 @@ class DistributedOptimizer:
 
     # ------------------------------------------------------------------ step
     def step(self):
+        gemm_ops.flush_wgrad()   # weight-gradient GEMMs parked for a grouped launch
         self._materialise_unwritten()
         self._sum_replicated_grads_over_tp()
         if self.use_fused_comm:

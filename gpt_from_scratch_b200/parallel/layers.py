@@ -86,8 +86,7 @@ class _LinearFn(torch.autograd.Function):
         dw = None
         sink = ctx.sink
         if sink is not None:
-            gemm_ops.linear_wgrad(dy2, x2, out=sink.target(), accumulate=sink.consume_accumulate())
-            sink.done()
+            gemm_ops.linear_wgrad_to_sink(dy2, x2, sink)
         elif ctx.needs_input_grad[1]:
             dw = gemm_ops.linear_wgrad(dy2, x2)
         dres = dy if ctx.has_res else None

@@ -103,3 +103,54 @@ def test_gemm_cta_pair_kernel(cuda_device, M, N, K, a_mn, b_mn):
     out2 = r.clone()
     gemm_bf16(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out2, addend=out2, pair=True)
     _check(out2, _ref(a, b, a_mn, b_mn, r), K)
+
+
+def test_grouped_weight_gradients(cuda_device):
+    """Several weight-gradient problems in one grouped launch (parked, then flushed) against
+    the fp32 reference; one of them accumulates into an existing gradient."""
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+
+    class Sink:  # the two methods of GradSink the GEMM layer uses, on a plain tensor
+        def __init__(self, t, accumulate):
+            self.t, self.acc, self.finished = t, accumulate, False
+
+        def target(self):
+            return self.t
+
+        def consume_accumulate(self):
+            return self.acc
+
+        def done(self):
+            self.finished = True
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    T = 1536  # tokens (the contraction)
+    shapes = [(768, 768), (2304, 768), (768, 3072), (384, 264)]
+    flat = torch.randn(sum(o * i for o, i in shapes), device=cuda_device, generator=g).bfloat16()
+    before = flat.clone()
+    sinks, operands, off = [], [], 0
+    for n, (o, i) in enumerate(shapes):
+        dy = torch.randn(T, o, device=cuda_device, generator=g).bfloat16()
+        x = torch.randn(T, i, device=cuda_device, generator=g).bfloat16()
+        sinks.append(Sink(flat[off:off + o * i].view(o, i), accumulate=(n == 1)))
+        operands.append((dy, x))
+        off += o * i
+    saved = gemm_ops._PAIR_MIN_TILES
+    gemm_ops._PAIR_MIN_TILES = 10 ** 6   # park everything until the explicit flush
+    try:
+        for n, ((dy, x), sk) in enumerate(zip(operands, sinks)):
+            gemm_ops.linear_wgrad_to_sink(dy, x, sk)
+            if n == 2:
+                assert not any(s_.finished for s_ in sinks)   # parked, nothing launched yet
+        gemm_ops.flush_wgrad()   # (the fourth problem filled the group and launched it already)
+    finally:
+        gemm_ops._PAIR_MIN_TILES = saved
+    torch.cuda.synchronize()
+    off = 0
+    for n, ((dy, x), sk, (o, i)) in enumerate(zip(operands, sinks, shapes)):
+        assert sk.finished
+        ref = dy.float().t() @ x.float()
+        if n == 1:
+            ref = ref + before[off:off + o * i].view(o, i).float()
+        _check(sk.t, ref, T)
+        off += o * i
