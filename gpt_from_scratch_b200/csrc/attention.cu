@@ -61,14 +61,20 @@ __device__ __forceinline__ int mask_class(int row_min, int row_max, int col_min,
   return all_dead ? 2 : (all_alive ? 0 : 1);
 }
 
+// The shared-memory descriptors are built once per call and advanced by adding the byte offset
+// (in 16-byte units) to their start-address field: the tiles are 1024-byte aligned and the
+// offsets small, so the 14-bit field never carries. The issuing thread competes with the
+// compute warps for issue slots, so every instruction saved per MMA shortens the chain.
 template <int KSTEPS>
 __device__ __forceinline__ void mma_kk(uint32_t d, uint32_t a, uint32_t a_blk, uint32_t b, uint32_t b_blk,
                                        uint32_t idesc, bool accumulate) {
+  const uint64_t ad0 = umma_desc_sw128(a, 16, 1024);
+  const uint64_t bd0 = umma_desc_sw128(b, 16, 1024);
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint64_t ad = umma_desc_sw128(a + (ks >> 2) * a_blk + (ks & 3) * 32, 16, 1024);
-    const uint64_t bd = umma_desc_sw128(b + (ks >> 2) * b_blk + (ks & 3) * 32, 16, 1024);
-    umma_ss(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    const uint64_t ad = ad0 + (((ks >> 2) * a_blk + (ks & 3) * 32) >> 4);
+    const uint64_t bd = bd0 + (((ks >> 2) * b_blk + (ks & 3) * 32) >> 4);
+    umma_ss_e(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 // A K-major; B MN-major: stored as [K rows x N] in 64-column blocks b_blk bytes apart
@@ -76,11 +82,13 @@ __device__ __forceinline__ void mma_kk(uint32_t d, uint32_t a, uint32_t a_blk, u
 template <int KSTEPS>
 __device__ __forceinline__ void mma_kmn(uint32_t d, uint32_t a, uint32_t a_blk, uint32_t b, uint32_t b_blk,
                                         uint32_t idesc, bool accumulate) {
+  const uint64_t ad0 = umma_desc_sw128(a, 16, 1024);
+  const uint64_t bd0 = umma_desc_sw128(b, b_blk, 1024);
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint64_t ad = umma_desc_sw128(a + (ks >> 2) * a_blk + (ks & 3) * 32, 16, 1024);
-    const uint64_t bd = umma_desc_sw128(b + ks * 2048, b_blk, 1024);
-    umma_ss(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    const uint64_t ad = ad0 + (((ks >> 2) * a_blk + (ks & 3) * 32) >> 4);
+    const uint64_t bd = bd0 + ((ks * 2048) >> 4);
+    umma_ss_e(d, ad, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -88,10 +96,11 @@ __device__ __forceinline__ void mma_kmn(uint32_t d, uint32_t a, uint32_t a_blk, 
 template <int KSTEPS>
 __device__ __forceinline__ void mma_tmn(uint32_t d, uint32_t a_tmem, uint32_t b, uint32_t b_blk, uint32_t idesc,
                                         bool accumulate) {
+  const uint64_t bd0 = umma_desc_sw128(b, b_blk, 1024);
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint64_t bd = umma_desc_sw128(b + ks * 2048, b_blk, 1024);
-    umma_ts(d, a_tmem + ks * 8, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    const uint64_t bd = bd0 + ((ks * 2048) >> 4);
+    umma_ts_e(d, a_tmem + ks * 8, bd, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -208,7 +217,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       const uint32_t q_addr = smem_u32(Qs);
@@ -222,8 +231,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         mbar_wait(&s_empty[sb], spar ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
         tc_fence_after();
         mma_kk<D / 16>(tmem_base + sb * 128, q_addr, 16384, smem_u32(Ks + st * TILE_BYTES), 16384, idesc_s, false);
-        umma_commit(&s_full[sb]);
-        umma_commit(&k_empty[st]);
+        umma_commit_e(&s_full[sb]);
+        umma_commit_e(&k_empty[st]);
       };
       issue_s(0);
       for (int j = 0; j < n_kv; ++j) {
@@ -238,9 +247,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tc_fence_after();
         mma_kmn<8>(tmem_base + OP_COL + sb * D, smem_u32(Ps + sb * P_BYTES), 16384, smem_u32(Vs + st * TILE_BYTES),
                    16384, idesc_o, false);
-        umma_commit(&o_full[sb]);
-        umma_commit(&v_empty[st]);
-        umma_commit(&p_empty[sb]);
+        umma_commit_e(&o_full[sb]);
+        umma_commit_e(&v_empty[st]);
+        umma_commit_e(&p_empty[sb]);
       }
     }
   } else {
@@ -529,7 +538,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       int g0 = 0;            // ring position of this item's first key block
@@ -548,15 +557,15 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           tc_fence_after();
           mma_kk<D / 16>(tmem_base + S_COL + x * 128, smem_u32(Qs + x * 16384), 0, smem_u32(Ks + (g % KS) * 16384),
                          0, idesc_s, false);
-          umma_commit(&s_full[x]);
+          umma_commit_e(&s_full[x]);
         };
         // S(0) of this item may only overwrite S once the softmax has consumed the previous
         // item's last block of that tile; that is guaranteed because the previous item's last
         // P V of the tile was issued after its p_full, and we issue in program order.
         if (n_x[0] > 0) issue_s(0, 0);
         if (n_x[1] > 0) issue_s(1, 0);
-        if (n_kv > 0) umma_commit(&k_empty[g0 % KS]);
-        if (n_kv == 1) umma_commit(q_empty);
+        if (n_kv > 0) umma_commit_e(&k_empty[g0 % KS]);
+        if (n_kv == 1) umma_commit_e(q_empty);
         for (int j = 0; j < n_kv; ++j) {
           const int g = g0 + j;
           for (int x = 0; x < 2; ++x) {
@@ -569,11 +578,11 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             tc_fence_after();
             mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384), 0,
                        idesc_o, false);
-            umma_commit(&o_full[x]);
+            umma_commit_e(&o_full[x]);
           }
-          if (j + 1 < n_kv) umma_commit(&k_empty[(g + 1) % KS]);  // both tiles' S(j+1) have been issued
-          if (j + 2 == n_kv) umma_commit(q_empty);                // the item's last S MMAs are issued
-          umma_commit(&v_empty[g % KS]);
+          if (j + 1 < n_kv) umma_commit_e(&k_empty[(g + 1) % KS]);  // both tiles' S(j+1) have been issued
+          if (j + 2 == n_kv) umma_commit_e(q_empty);                // the item's last S MMAs are issued
+          umma_commit_e(&v_empty[g % KS]);
         }
         g0 += n_kv;
         cx[0] += n_x[0];
@@ -946,7 +955,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc_xy = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, 0, 1);
       const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
@@ -968,14 +977,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         tc_fence_after();
         mma_kk<D / 16>(tmem_base + sb * 64, r1, 16384, smem_u32(T1 + st * T_BYTES), 8192, idesc_xy, false);
         mma_kk<D / 16>(tmem_base + Y_COL + sb * 64, r2, 16384, smem_u32(T2 + st * T_BYTES), 8192, idesc_xy, false);
-        umma_commit(&xy_full[sb]);
+        umma_commit_e(&xy_full[sb]);
       };
-      if (n_t > 0) issue_xy(0);
-      if (n_t <= 1) umma_commit(r_empty);
+      // Score MMAs run LA blocks ahead of the gradient MMAs. With two X/Y buffers and a ring
+      // deep enough (LA = 2), block t+2's scores are issued as soon as the compute warps have
+      // pulled block t's X/Y into registers (xy_empty is signalled right after those loads),
+      // i.e. while they are still doing block t's math, so they never wait for scores.
+      constexpr int LA = (NBUF == 2 && TS >= 4) ? 2 : 1;
+      for (int t = 0; t < LA && t < n_t; ++t) issue_xy(t);
+      if (n_t <= LA) umma_commit_e(r_empty);
       for (int t = 0; t < n_t; ++t) {
-        if (t + 1 < n_t) {
-          issue_xy(t + 1);
-          if (t + 2 == n_t) umma_commit(r_empty);  // the item's last score MMAs are issued
+        if (t + LA < n_t) {
+          issue_xy(t + LA);
+          if (t + LA + 1 == n_t) umma_commit_e(r_empty);  // the item's last score MMAs are issued
         }
         const int g = g0 + t;
         const int st = g % TS;
@@ -1002,10 +1016,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
           mma_kmn<4>(tmem_base + ACC1, smem_u32(M1 + sb * M_BYTES), 0, smem_u32(T1 + st * T_BYTES), 8192, idesc_acc,
                      t > 0);
         }
-        umma_commit(&t_empty[st]);
-        umma_commit(&m_empty[sb]);
+        umma_commit_e(&t_empty[st]);
+        umma_commit_e(&m_empty[sb]);
       }
-      umma_commit(acc_full);
+      umma_commit_e(acc_full);
       g0 += n_t;
       }
     }
@@ -1120,26 +1134,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       const uint32_t y_addr = tmem_base + lane_base + Y_COL + sb * 64;
       tmem_ld_32x32(x_addr + cbase, xa);
       tmem_ld_32x32(y_addr + cbase, ya);
-      tmem_ld_wait_for(xa);
-      tmem_ld_wait_for(ya);
       if (COLS == 64) {
         tmem_ld_32x32(x_addr + 32, xb);
         tmem_ld_32x32(y_addr + 32, yb);
       }
-      grad_chunk(xa, ya, cbase);
+      tmem_ld_wait_for(xa);
+      tmem_ld_wait_for(ya);
       if (COLS == 64) {
         tmem_ld_wait_for(xb);
         tmem_ld_wait_for(yb);
-        grad_chunk(xb, yb, 32);
       }
+      // X / Y are in registers: hand the buffer back now so the next scores can be computed
+      // into it while this block's math runs
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xy_empty[sb]);
+      grad_chunk(xa, ya, cbase);
+      if (COLS == 64) grad_chunk(xb, yb, 32);
       if (PT) tmem_st_wait();
       tc_fence_before();
       if (!PT) fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&xy_empty[sb]);
-        mbar_arrive(&m_full[sb]);
-      }
+      if (lane == 0) mbar_arrive(&m_full[sb]);
     }
     // epilogue: accumulators -> global
     g0 += n_t;

@@ -225,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -249,15 +249,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                         : umma_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_desc_sw128(sb + k * 2048, 8192, 1024)
                                         : umma_desc_sw128(sb + k * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_ss_e(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          umma_commit_e(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        umma_commit(&tmem_full[acc]);
+        umma_commit_e(&tmem_full[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;

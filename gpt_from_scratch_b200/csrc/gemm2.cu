@@ -125,19 +125,26 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// Called by all 32 lanes of the issuing warp (converged); one elected lane issues (see
+// umma_ss_e in common.cuh for why the issuing loop runs on the whole warp).
 __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// arrive (once) on the barrier at `cluster_addr` when all MMAs issued so far by this thread are done
+// arrive (once) on the barrier at `cluster_addr` when all MMAs issued so far by the elected lane
+// are done; called by all 32 lanes of the issuing warp
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
-               : "memory");
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_addr)
+      : "memory");
 }
 
 template <bool A_MN, bool B_MN, int COMM>
@@ -242,7 +249,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader only) ------------------------------
-    if (leader && lane == 0) {
+    if (leader) {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -613,7 +620,7 @@ gemm2_grouped_kernel(const __grid_constant__ GroupMaps maps, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (leader && lane == 0) {
+    if (leader) {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
       constexpr uint32_t idesc = umma_idesc_bf16(256, BN, 1, 1);
       int stage = 0;
       uint32_t phase = 0;

@@ -14,7 +14,9 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libgfs_b200.so"
+# GFS_LIB_PATH selects another build of the library (e.g. an experimental variant) explicitly.
+_LIB_PATH = Path(os.environ.get("GFS_LIB_PATH") or
+                 Path(__file__).resolve().parent.parent / "lib" / "libgfs_b200.so")
 _lib = None
 _lock = threading.Lock()
 
