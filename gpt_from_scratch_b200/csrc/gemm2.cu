@@ -52,7 +52,12 @@ struct CommParams {
 constexpr int A_BYTES = BM * BK * 2;     // 16 KB
 constexpr int B_BYTES = BNH * BK * 2;    // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_BYTES = 4 * 4096;
+constexpr int EPI_BYTES = 8 * 4096;     // one [32 rows x 128 B] transpose buffer per epilogue warp
+// Epilogue warps per CTA: 8 in the plain kernel (two per TMEM lane quarter, each taking half of the
+// tile's columns, so epilogues with real work per element still hide behind the next tile's
+// MMAs); 4 in the fused-collective variants, whose two extra warps need the registers.
+__host__ __device__ constexpr int epi_warps(int comm) { return comm == 0 ? 8 : 4; }
+__host__ __device__ constexpr int threads2(int comm) { return 64 + 32 * epi_warps(comm) + (comm != 0 ? 64 : 0); }
 constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 256 + 1024;
 
 struct Params2 {
@@ -65,8 +70,19 @@ struct Params2 {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols, rope_d, rope_b;
+  // SwiGLU fusion (template parameter SWI). 1 (forward, B = [gate rows | up rows] of a [2I, K]
+  // weight): a tile pairs 128 gate columns (leader CTA's B rows) with the matching 128 up columns
+  // (the other CTA's); the epilogue writes both halves of the projection (C, pitch ldc) and
+  // act = silu(gate) * up (swi_act, pitch swi_ld). 2 (backward, the product is d_act [M, I]):
+  // the epilogue reads gate/up from swi_gu (pitch swi_ld) and writes d_gate | d_up into C
+  // ([M, 2I], pitch ldc) instead of d_act.
+  int swi_I, swi_ld;
+  __nv_bfloat16* swi_act;
+  const __nv_bfloat16* swi_gu;
   CommParams comm;
 };
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 // Tile t -> first row of the pair tile, first column, and (fused collectives) the row chunk.
 // The collectives walk the ranks' row chunks in a rotated order: all-gather starts with the
@@ -147,8 +163,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
       : "memory");
 }
 
-template <bool A_MN, bool B_MN, int COMM>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), 1)
+template <bool A_MN, bool B_MN, int COMM, int SWI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads2(COMM), 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
              const Params2 p) {
   extern __shared__ uint8_t smem_raw[];
@@ -175,7 +191,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 8);
+      mbar_init(&tmem_empty[b], 2 * epi_warps(COMM));
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -231,7 +247,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * 8192, &tmap_a, bar, m0 + 64 * i, k0);
           }
-          if (!B_MN) {
+          if (SWI == 1) {
+            // n0 counts interleaved tile columns: gate rows [g0, g0 + 128) for the leader, the
+            // matching up rows [I + g0, ...) for the other CTA
+            const int g0 = (n0 - static_cast<int>(rank) * BNH) >> 1;
+            tma_load_2d_pair(sb, &tmap_b, bar, k0, (rank == 0 ? 0 : p.swi_I) + g0);
+          } else if (!B_MN) {
             tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
           } else {
 #pragma unroll
@@ -288,9 +309,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + epi_warps(COMM)) {
     // ------------------------------ epilogue (both CTAs, own accumulator half) ------------------------------
-    const int q = warp & 3;
+    constexpr int EW = epi_warps(COMM);
+    const int q = warp & 3;                               // TMEM lane quarter this warp may access
+    const int c_begin = (EW == 8) ? ((warp - 2) >> 2) * (BN / 2) : 0;   // this warp's column range of the tile
+    const int c_end = (EW == 8) ? c_begin + BN / 2 : BN;
     int acc = 0;
     uint32_t acc_phase = 0;
     uint8_t* ebuf = epi_smem + (warp - 2) * 4096;
@@ -313,7 +337,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (has_add && pair < total_tiles) {
       int fm0, fn0, fchunk;
       decode_tile2<COMM>(p, pair, fm0, fn0, fchunk);
-      load_addend(pre, fm0 + static_cast<int>(rank) * BM, fn0);
+      load_addend(pre, fm0 + static_cast<int>(rank) * BM, fn0 + c_begin);
     }
     for (int t = pair; t < total_tiles; t += num_pairs) {
       int m0, n0, chunk;
@@ -322,21 +346,96 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       mbar_wait(&tmem_full[acc], acc_phase, wctx, STATUS_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (SWI == 1) {
+        // accumulator columns [0,128) are gate, [128,256) the matching up columns
+        const int g0 = n0 >> 1;  // first gate column of the tile
+        const int sc_begin = (EW == 8) ? ((warp - 2) >> 2) * 64 : 0;
+        const int sc_end = (EW == 8) ? sc_begin + 64 : 128;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
+        for (int c = sc_begin; c < sc_end; c += 32) {
+          if (g0 + c >= p.swi_I) break;
+          uint32_t vg[32], vu[32];
+          tmem_ld_32x32(t_row + c, vg);
+          tmem_ld_32x32(t_row + BN / 2 + c, vu);
+          tmem_ld_wait();
+          uint32_t pa[16];
+          uint8_t* myrow = ebuf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 wg, wu;
+            uint32_t* wgp = &wg.x;
+            uint32_t* wup = &wu.x;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              wgp[e] = pack_bf16x2(__uint_as_float(vg[8 * j + 2 * e]), __uint_as_float(vg[8 * j + 2 * e + 1]));
+              wup[e] = pack_bf16x2(__uint_as_float(vu[8 * j + 2 * e]), __uint_as_float(vu[8 * j + 2 * e + 1]));
+              // act from the bf16-rounded projections, silu rounded to bf16 before the product
+              const float2 g2 = unpack_bf16x2(wgp[e]), u2 = unpack_bf16x2(wup[e]);
+              const float s0 = __bfloat162float(__float2bfloat16_rn(g2.x * sigmoid_f(g2.x)));
+              const float s1 = __bfloat162float(__float2bfloat16_rn(g2.y * sigmoid_f(g2.y)));
+              pa[4 * j + e] = pack_bf16x2(s0 * u2.x, s1 * u2.y);
+            }
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) = wg;
+            *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = wu;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {  // gate | up halves of the projection
+            const int r = i * 4 + rrow;
+            const int grow = m0 + q * 32 + r;
+            const int lc = g0 + c + (rch & 3) * 8;  // column inside [0, I)
+            const uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
+            if (grow < p.M && lc + 8 <= p.swi_I)
+              *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(grow) * p.ldc + (rch >= 4 ? p.swi_I : 0) + lc) = w;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(pa[4 * j], pa[4 * j + 1], pa[4 * j + 2], pa[4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {  // act: 32 columns per row, 4 lanes per row
+            const int r = i * 8 + (lane >> 2);
+            const int ch = lane & 3;
+            const int grow = m0 + q * 32 + r;
+            const int lc = g0 + c + ch * 8;
+            const uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((ch ^ (r & 7)) << 4));
+            if (grow < p.M && lc + 8 <= p.swi_I)
+              *reinterpret_cast<uint4*>(p.swi_act + static_cast<size_t>(grow) * p.swi_ld + lc) = w;
+          }
+          __syncwarp();
+        }
+      } else {
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; c += 64) {
         const int col0 = n0 + c;
         if (col0 >= p.N) break;
         const int gcol = col0 + rch * 8;
         uint4 cur[8];
+        uint4 gq[8], uq[8];
+        if (SWI == 2) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int grow = m0 + q * 32 + i * 4 + rrow;
+            gq[i] = make_uint4(0, 0, 0, 0);
+            uq[i] = make_uint4(0, 0, 0, 0);
+            if (grow < p.M && gcol + 8 <= p.N) {
+              const __nv_bfloat16* gp = p.swi_gu + static_cast<size_t>(grow) * p.swi_ld + gcol;
+              gq[i] = *reinterpret_cast<const uint4*>(gp);
+              uq[i] = *reinterpret_cast<const uint4*>(gp + p.swi_I);
+            }
+          }
+        }
         if (has_add) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) cur[i] = pre[i];
-          if (c + 64 < BN && col0 + 64 < p.N) {
+          if (c + 64 < c_end && col0 + 64 < p.N) {
             load_addend(pre, m0, col0 + 64);
           } else if (t + num_pairs < total_tiles) {
             int nm0, nn0, nchunk;
             decode_tile2<COMM>(p, t + num_pairs, nm0, nn0, nchunk);
-            load_addend(pre, nm0 + static_cast<int>(rank) * BM, nn0);
+            load_addend(pre, nm0 + static_cast<int>(rank) * BM, nn0 + c_begin);
           }
         }
         uint32_t va[32], vb[32];
@@ -364,7 +463,28 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           const int r = i * 4 + rrow;
           const int grow = m0 + q * 32 + r;
           uint4 w = *reinterpret_cast<const uint4*>(ebuf + r * 128 + ((rch ^ (r & 7)) << 4));
-          if (grow < p.M && gcol + 8 <= p.N) {
+          if (SWI == 2) {
+            // w holds 8 values of d_act; turn them into d_gate and d_up
+            if (grow < p.M && gcol + 8 <= p.N) {
+              const uint32_t* dw = &w.x;
+              const uint32_t* gw = &gq[i].x;
+              const uint32_t* uw = &uq[i].x;
+              uint4 og, ou;
+              uint32_t* ogp = &og.x;
+              uint32_t* oup = &ou.x;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 d2 = unpack_bf16x2(dw[e]), g2 = unpack_bf16x2(gw[e]), u2 = unpack_bf16x2(uw[e]);
+                const float sg0 = sigmoid_f(g2.x), sg1 = sigmoid_f(g2.y);
+                ogp[e] = pack_bf16x2(d2.x * u2.x * sg0 * (1.f + g2.x * (1.f - sg0)),
+                                     d2.y * u2.y * sg1 * (1.f + g2.y * (1.f - sg1)));
+                oup[e] = pack_bf16x2(d2.x * g2.x * sg0, d2.y * g2.y * sg1);
+              }
+              __nv_bfloat16* dst = p.C + static_cast<size_t>(grow) * p.ldc + gcol;
+              *reinterpret_cast<uint4*>(dst) = og;
+              *reinterpret_cast<uint4*>(dst + p.swi_I) = ou;
+            }
+          } else if (grow < p.M && gcol + 8 <= p.N) {
             if (has_add || p.rope_cos != nullptr) {
               float f[8];
               const float2 x0 = unpack_bf16x2(w.x), x1 = unpack_bf16x2(w.y), x2 = unpack_bf16x2(w.z),
@@ -407,9 +527,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
         __syncwarp();
       }
+      }
       tc_fence_before();
       __syncwarp();
-      // the accumulator buffer may be overwritten once all 8 epilogue warps of the pair are done
+      // the accumulator buffer may be overwritten once all epilogue warps of the pair are done
       if (lane == 0) {
         mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
         if (COMM == COMM_REDUCE_SCATTER) red_release_sys_add_u32(p.comm.peer_flags[chunk] + p.comm.rank, 1u);
@@ -424,7 +545,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     // Every CTA pushes its slice of the local shard into every rank's gathered buffer
     // (own rank first), then bumps that rank's counter for this source.
     const CommParams& c = p.comm;
-    const int ct = threadIdx.x - THREADS;
+    const int ct = threadIdx.x - (threads2(COMM) - COMM_THREADS);
     const int rpc = (c.rows_per_rank + gridDim.x - 1) / gridDim.x;
     const int r0 = min(c.rows_per_rank, static_cast<int>(blockIdx.x) * rpc);
     const int r1 = min(c.rows_per_rank, r0 + rpc);
@@ -461,7 +582,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     // Wait until every rank (this one included) has delivered all partial tiles of our row
     // chunk, then sum the staged partials in rank order, add the residual, round once.
     const CommParams& c = p.comm;
-    const int ct = threadIdx.x - THREADS;
+    const int ct = threadIdx.x - (threads2(COMM) - COMM_THREADS);
     bool ok = true;
     for (int src = 0; src < c.world; ++src)
       ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
@@ -746,9 +867,9 @@ gemm2_grouped_kernel(const __grid_constant__ GroupMaps maps, const __grid_consta
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
-template <bool A_MN, bool B_MN, int COMM = COMM_NONE>
+template <bool A_MN, bool B_MN, int COMM = COMM_NONE, int SWI = 0>
 int launch2(const CUtensorMap* ta, const CUtensorMap* tb, const Params2& p, int grid, cudaStream_t stream) {
-  auto kern = gemm2_kernel<A_MN, B_MN, COMM>;
+  auto kern = gemm2_kernel<A_MN, B_MN, COMM, SWI>;
   static bool attr_set = false;
   static int attr_dev = -1;
   int dev = 0;
@@ -759,7 +880,7 @@ int launch2(const CUtensorMap* ta, const CUtensorMap* tb, const Params2& p, int 
     attr_set = true;
     attr_dev = dev;
   }
-  kern<<<grid, THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), SMEM_TOTAL, stream>>>(*ta, *tb, p);
+  kern<<<grid, threads2(COMM), SMEM_TOTAL, stream>>>(*ta, *tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -802,6 +923,43 @@ int gfs_gemm2_bf16(const void* A, const void* B, void* C, const void* R, int M, 
   if (!a_mn_major && b_mn_major) return launch2<false, true>(ta, tb, p, grid, stream);
   if (a_mn_major && b_mn_major) return launch2<true, true>(ta, tb, p, grid, stream);
   return launch2<true, false>(ta, tb, p, grid, stream);
+}
+
+// SwiGLU-fused products of the MLP on CTA pairs; same contract as gfs_gemm_bf16_swiglu (gemm.cu):
+//   mode 1: gu[M, 2I] = x[M, K] @ w_gu[2I, K]^T and act[M, I] = silu(gu[:, :I]) * gu[:, I:]
+//           (a = x, b = w_gu, c = gu with pitch ldc, extra = act with pitch ld_extra)
+//   mode 2: d_gu[M, 2I] = swiglu_backward(d_act = dy[M, K] @ w_down[K, I], gu)
+//           (a = dy, b = w_down stored [K, I], c = d_gu with pitch ldc, extra = gu with pitch ld_extra)
+int gfs_gemm2_bf16_swiglu(int mode, const void* a, const void* b, void* c, void* extra, int M, int I, int K, int lda,
+                          int ldb, int ldc, int ld_extra, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (mode != 1 && mode != 2) return -1;
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if ((I & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || (ld_extra & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+       reinterpret_cast<uintptr_t>(extra)) & 15)
+    return -2;
+  Params2 p{};
+  p.M = M; p.K = K;
+  p.N = (mode == 1) ? 2 * I : I;
+  p.C = static_cast<__nv_bfloat16*>(c);
+  p.ldc = ldc;
+  p.tiles_m = (M + 255) / 256;
+  p.tiles_n = (mode == 1) ? (I + BN / 2 - 1) / (BN / 2) : (I + BN - 1) / BN;
+  p.kblocks = (K + BK - 1) / BK;
+  p.status = gfs_host::status_words();
+  p.rope_b = 1;
+  p.swi_I = I;
+  p.swi_ld = ld_extra;
+  if (mode == 1) p.swi_act = static_cast<__nv_bfloat16*>(extra);
+  else p.swi_gu = static_cast<const __nv_bfloat16*>(extra);
+  const CUtensorMap* ta = gfs_host::tmap_2d_cached(a, M, K, lda, BM, 64);
+  const CUtensorMap* tb = (mode == 1) ? gfs_host::tmap_2d_cached(b, 2 * I, K, ldb, BNH, 64)
+                                      : gfs_host::tmap_2d_cached(b, K, I, ldb, 64, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+  const int pairs = std::min(p.tiles_m * p.tiles_n, gfs_host::sm_count() / 2);
+  return (mode == 1) ? launch2<false, false, COMM_NONE, 1>(ta, tb, p, 2 * pairs, stream)
+                     : launch2<false, true, COMM_NONE, 2>(ta, tb, p, 2 * pairs, stream);
 }
 
 // Fused collective + GEMM on CTA pairs; same contract as gfs_gemm_bf16_comm (gemm.cu) with the

@@ -95,6 +95,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i,
                                 ctypes.c_uint, i, uip, vp, vp, f, f, f, f, f, f, f, f, f, ctypes.c_longlong, vp], i),
         "gfs_gemm_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
+        "gfs_gemm2_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_gemm2_bf16": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, i, i, i, vp], i),
         "gfs_gemm_bf16_rope": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, vp, sz, i, vp, vp, i, i, i, vp], i),
     }

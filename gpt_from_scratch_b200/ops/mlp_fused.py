@@ -17,15 +17,28 @@ from . import _lib
 from . import gemm as gemm_ops
 
 
+def _pair_eligible(M: int, I: int, cols_per_tile: int) -> bool:
+    """Enough 256-row tiles for the CTA-pair kernel (``cols_per_tile``: columns of I covered by
+    one tile, 128 forward / 256 backward)."""
+    tiles = ((M + 255) // 256) * ((I + cols_per_tile - 1) // cols_per_tile)
+    return gemm_ops._PAIR_ENABLED and tiles >= gemm_ops._PAIR_MIN_TILES
+
+
+def _swiglu_entry(M: int, I: int, cols_per_tile: int):
+    if _pair_eligible(M, I, cols_per_tile):
+        return _lib.lib().gfs_gemm2_bf16_swiglu
+    return _lib.lib().gfs_gemm_bf16_swiglu
+
+
 def swiglu_gemm_fwd(x2d: torch.Tensor, w_gu: torch.Tensor):
     """Returns ``(gu [M, 2I], act [M, I])``."""
     M, K = x2d.shape
     I = w_gu.shape[0] // 2
     gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=x2d.device)
     act = torch.empty((M, I), dtype=torch.bfloat16, device=x2d.device)
-    rc = _lib.lib().gfs_gemm_bf16_swiglu(1, x2d.data_ptr(), w_gu.data_ptr(), gu.data_ptr(), act.data_ptr(), M, I, K,
-                                         x2d.stride(0), w_gu.stride(0), gu.stride(0), act.stride(0),
-                                         _lib.stream_ptr())
+    fn = _swiglu_entry(M, I, 128)
+    rc = fn(1, x2d.data_ptr(), w_gu.data_ptr(), gu.data_ptr(), act.data_ptr(), M, I, K,
+            x2d.stride(0), w_gu.stride(0), gu.stride(0), act.stride(0), _lib.stream_ptr())
     _lib.check(rc, "gfs_gemm_bf16_swiglu(fwd)")
     return gu, act
 
@@ -35,9 +48,9 @@ def swiglu_gemm_bwd(dy2d: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor) 
     M, H = dy2d.shape
     I = w_down.shape[1]
     dgu = torch.empty_like(gu)
-    rc = _lib.lib().gfs_gemm_bf16_swiglu(2, dy2d.data_ptr(), w_down.data_ptr(), dgu.data_ptr(), gu.data_ptr(), M, I,
-                                         H, dy2d.stride(0), w_down.stride(0), dgu.stride(0), gu.stride(0),
-                                         _lib.stream_ptr())
+    fn = _swiglu_entry(M, I, 256)
+    rc = fn(2, dy2d.data_ptr(), w_down.data_ptr(), dgu.data_ptr(), gu.data_ptr(), M, I,
+            H, dy2d.stride(0), w_down.stride(0), dgu.stride(0), gu.stride(0), _lib.stream_ptr())
     _lib.check(rc, "gfs_gemm_bf16_swiglu(bwd)")
     return dgu
 
@@ -65,7 +78,7 @@ class _FusedMLP(torch.autograd.Function):
         d2 = dout.reshape(-1, w_down.shape[0])
         if not d2.is_contiguous():
             d2 = d2.contiguous()
-        if x2.shape[-1] >= MIN_HIDDEN_FOR_BWD_FUSION:
+        if x2.shape[-1] >= MIN_HIDDEN_FOR_BWD_FUSION or _pair_eligible(d2.shape[0], gu.shape[1] // 2, 256):
             dgu = swiglu_gemm_bwd(d2, w_down, gu)
         else:
             # short contraction: the plain dgrad GEMM + the SwiGLU backward kernel are faster
@@ -87,10 +100,10 @@ class _FusedMLP(torch.autograd.Function):
         return dx, dw_gu, dw_down, (dout if ctx.has_res else None), None, None
 
 
-# The forward fusion pays at every size (hidden 768: 149 us fused vs 114 + 50 us unfused). In
-# the backward the epilogue has to fetch gate/up and do twice the math; with a short
-# contraction (K = hidden) that is slower than the separate kernels (175 us vs 67 + 80 us at
-# hidden 768), so it is only used from this hidden size up.
+# The forward fusion pays at every size (hidden 768, 16384 rows: 132 us on CTA pairs vs 106 + 50 us
+# unfused). In the backward the epilogue has to fetch gate/up and do twice the math: on CTA pairs
+# (8 epilogue warps) it still wins (126 us vs 61 + 80 us); on the single-CTA kernel with a short
+# contraction (K = hidden) it does not (155 us), so there it is only used from this hidden size up.
 MIN_HIDDEN_FOR_BWD_FUSION = 2048
 
 

@@ -157,3 +157,32 @@ def test_fused_mlp_matches_unfused(cuda_device, M, H, I):
     for name, a, b in (("y", ya, yf), ("dx", xa.grad, xf.grad), ("dW_gu", wa.grad, wf.grad), ("dW_down", wb.grad, wg.grad)):
         rel = (a.float() - b).norm() / (b.norm() + 1e-9)
         assert rel < 1.5e-2, f"{name}: relative error {rel:.4g}"
+
+
+@pytest.mark.parametrize("M,H,I", [(512, 256, 384), (1000, 768, 704), (2048, 320, 1536)])
+@pytest.mark.parametrize("pair", [False, True])
+def test_swiglu_gemm_epilogues(cuda_device, M, H, I, pair):
+    """SwiGLU forward / backward folded into the GEMM epilogue (single-CTA and CTA-pair kernels)
+    against an fp32 reference of the same two steps."""
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    from gpt_from_scratch_b200.ops.mlp_fused import swiglu_gemm_bwd, swiglu_gemm_fwd
+    g = torch.Generator(device="cuda").manual_seed(M + I + int(pair))
+    x = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
+    w_gu = (torch.randn(2 * I, H, device=cuda_device, generator=g) * 0.05).bfloat16()
+    w_dn = (torch.randn(H, I, device=cuda_device, generator=g) * 0.05).bfloat16()
+    dy = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
+    saved = gemm_ops._PAIR_MIN_TILES
+    gemm_ops._PAIR_MIN_TILES = 1 if pair else 10 ** 9
+    try:
+        gu, act = swiglu_gemm_fwd(x, w_gu)
+        dgu = swiglu_gemm_bwd(dy, w_dn, gu)
+    finally:
+        gemm_ops._PAIR_MIN_TILES = saved
+    gu_ref = x.float() @ w_gu.float().t()
+    _close(gu, gu_ref, 2e-2, 2e-2, what="gate_up projection")
+    guf = gu.float().requires_grad_()          # the kernels compute act and the gradient from the bf16 projection
+    act_ref = torch.nn.functional.silu(guf[:, :I]) * guf[:, I:]
+    _close(act, act_ref, 2e-2, 2e-2, what="act")
+    dact = (dy.float() @ w_dn.float()).bfloat16().float()
+    act_ref.backward(dact)
+    _close(dgu, guf.grad, 3e-2, 3e-2, what="d_gate_up")
