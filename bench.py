@@ -129,6 +129,8 @@ def timed_loop(step_fn, batches, steps, stage: str):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     last = None
+    step_async = getattr(step_fn, "step_async", None)
+    pending = None
     for i in range(steps):
         if stage == "device":
             x, y = staged[i]
@@ -137,7 +139,18 @@ def timed_loop(step_fn, batches, steps, stage: str):
             hx, hy = batches[i % len(batches)]
             x = hx.to(dev, non_blocking=True)
             y = hy.to(dev, non_blocking=True)
-            last = float(step_fn(x, y))     # device -> host read of this step's loss
+            if step_async is not None:
+                # every step copies its loss device -> pinned host memory (asynchronously); the
+                # host reads the value of step i while step i+1 is already queued, the last one
+                # before the closing event
+                handle = step_async(x, y)
+                if pending is not None:
+                    last = pending.value()
+                pending = handle
+            else:
+                last = float(step_fn(x, y))     # device -> host read of this step's loss (blocking)
+    if pending is not None:
+        last = pending.value()
     e1.record()
     barrier_sync()
     return max_over_ranks(e0.elapsed_time(e1)), last
@@ -164,6 +177,7 @@ def build_ours(cfgd, args, world):
 
     def step_fn(x, y):
         return engine.train_step(x, y)
+    step_fn.step_async = engine.train_step_async   # loss via asynchronous copy to pinned memory
 
     def launches():
         return _lib.launch_count()
@@ -272,7 +286,10 @@ def main():
     if not args.no_e2e:
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss}
+               "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss,
+               "loss_read": ("asynchronous copy to pinned memory every step, value read one step later "
+                             "(TrainEngine.train_step_async)" if args.impl == "ours" else
+                             "blocking read every step")}
     if rank == 0:
         par = (f"tp{tp}" if tp > 1 else "") + (f"dp{dp}" if (dp > 1 or tp == 1) else "")
         line = {

@@ -125,11 +125,18 @@ def test_training_matches_fp32_oracle(cuda_device):
     before = _lib.launch_count()
     g = torch.Generator().manual_seed(3)
     ours, ref = [], []
-    for _ in range(8):
+    handles = []
+    for i in range(8):
         t = torch.randint(0, 512, (4, 129), generator=g)
         x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
-        ours.append(float(eng.train_step(x.cuda(), y.cuda())))
+        if i % 2:   # the asynchronous loss read (pinned buffer + event) must give the same numbers
+            handles.append((i, eng.train_step_async(x.cuda(), y.cuda())))
+            ours.append(None)
+        else:
+            ours.append(float(eng.train_step(x.cuda(), y.cuda())))
         ref.append(float(naive_step(oracle, opt, x, y, 1.0)))
+    for i, h in handles:
+        ours[i] = h.value()
     assert _lib.launch_count() - before > 100, "native kernels were not used"
     for a, b in zip(ours, ref):
         assert abs(a - b) < 3e-2, (ours, ref)

@@ -59,9 +59,11 @@ class TimerGroup:
     def summary(self):
         torch.cuda.synchronize()
         out = {}
-        for name, evs in self.pending.items():
-            ms = sum(a.elapsed_time(b) for a, b in evs) / max(1, len(evs))
-            out[name] = (max_over_ranks(ms, self.device), len(evs))
+        # local means first: the reduction below is itself a (possibly wrapped and timed) collective
+        local = [(name, sum(a.elapsed_time(b) for a, b in evs) / max(1, len(evs)), len(evs))
+                 for name, evs in sorted(self.pending.items())]
+        for name, ms, n in local:
+            out[name] = (max_over_ranks(ms, self.device), n)
         return out
 
 
