@@ -79,6 +79,11 @@ struct Params2 {
   int swi_I, swi_ld;
   __nv_bfloat16* swi_act;
   const __nv_bfloat16* swi_gu;
+  // SWI == 3 (LM head): besides storing the logits, every epilogue warp writes the online-softmax
+  // statistics (max, sum exp(x - max)) of its 128 columns of each row, computed from the
+  // bf16-rounded logits: ce_partials[(tile_n * 2 + column half) * M + row]. A small kernel
+  // combines them, so the cross entropy needs no pass over the logits in the forward.
+  float2* ce_partials;
   CommParams comm;
 };
 
@@ -407,6 +412,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           __syncwarp();
         }
       } else {
+      float ce_m = -INFINITY, ce_s = 0.f;   // SWI == 3: running statistics of this lane's row
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 64) {
         const int col0 = n0 + c;
@@ -456,6 +462,43 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           w.z = pack_bf16x2(__uint_as_float(vb[8 * j + 4]), __uint_as_float(vb[8 * j + 5]));
           w.w = pack_bf16x2(__uint_as_float(vb[8 * j + 6]), __uint_as_float(vb[8 * j + 7]));
           *reinterpret_cast<uint4*>(myrow + (((4 + j) ^ (lane & 7)) << 4)) = w;
+        }
+        if (SWI == 3) {
+          // this lane still holds its own row's 64 columns: fold their bf16-rounded values (read
+          // back from the words it just wrote for the transpose) into the row's running
+          // (max, sum-exp). Columns past N only exist in the last tile (warp-uniform test).
+          constexpr float L2E = 1.4426950408889634f;
+          const int n_valid = min(64, p.N - col0);
+          uint32_t pk[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 t = *reinterpret_cast<const uint4*>(myrow + ((j ^ (lane & 7)) << 4));
+            pk[4 * j + 0] = t.x; pk[4 * j + 1] = t.y; pk[4 * j + 2] = t.z; pk[4 * j + 3] = t.w;
+          }
+          if (n_valid < 64) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const uint32_t lo = (2 * e < n_valid) ? (pk[e] & 0xffffu) : 0xff80u;          // bf16 -inf
+              const uint32_t hi = (2 * e + 1 < n_valid) ? (pk[e] & 0xffff0000u) : 0xff800000u;
+              pk[e] = lo | hi;
+            }
+          }
+          float cm0 = -INFINITY, cm1 = -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            cm0 = fmaxf(cm0, __uint_as_float(pk[e] << 16));
+            cm1 = fmaxf(cm1, __uint_as_float(pk[e] & 0xffff0000u));
+          }
+          const float nm = fmaxf(ce_m, fmaxf(cm0, cm1));
+          const float off = (nm == -INFINITY) ? 0.f : nm * L2E;
+          float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            a0 += fast_exp2(fmaf(__uint_as_float(pk[e] << 16), L2E, -off));
+            a1 += fast_exp2(fmaf(__uint_as_float(pk[e] & 0xffff0000u), L2E, -off));
+          }
+          ce_s = ce_s * fast_exp2((ce_m == -INFINITY) ? -INFINITY : (ce_m - nm) * L2E) + (a0 + a1);
+          ce_m = nm;
         }
         __syncwarp();
 #pragma unroll
@@ -526,6 +569,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
         }
         __syncwarp();
+      }
+      if (SWI == 3) {
+        const int row = m0 + q * 32 + lane;
+        const int part = (n0 / BN) * 2 + ((EW == 8) ? ((warp - 2) >> 2) : 0);
+        if (row < p.M) p.ce_partials[static_cast<size_t>(part) * p.M + row] = make_float2(ce_m, ce_s);
       }
       }
       tc_fence_before();
@@ -923,6 +971,38 @@ int gfs_gemm2_bf16(const void* A, const void* B, void* C, const void* R, int M, 
   if (!a_mn_major && b_mn_major) return launch2<false, true>(ta, tb, p, grid, stream);
   if (a_mn_major && b_mn_major) return launch2<true, true>(ta, tb, p, grid, stream);
   return launch2<true, false>(ta, tb, p, grid, stream);
+}
+
+// LM head with cross-entropy statistics: C[M, N] = A[M, K] @ B[N, K]^T (both K-major) and, per row,
+// the (max, sum exp(x - max)) of every 128-column slice of the bf16-rounded logits:
+// partials is float2 [gfs_gemm2_ce_parts(N)][M]. Returns -20 if the problem is too small for CTA
+// pairs (nothing launched).
+int gfs_gemm2_ce_parts(int N) { return 2 * ((N + BN - 1) / BN); }
+
+int gfs_gemm2_bf16_ce(const void* A, const void* B, void* C, void* partials, int M, int N, int K, int lda, int ldb,
+                      int ldc, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(partials)) & 15)
+    return -2;
+  if (K < 256) return -20;
+  const CUtensorMap* ta = gfs_host::tmap_2d_cached(A, M, K, lda, BM, 64);
+  const CUtensorMap* tb = gfs_host::tmap_2d_cached(B, N, K, ldb, BNH, 64);
+  if (ta == nullptr || tb == nullptr) return -3;
+  Params2 p{};
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.tiles_m = (M + 255) / 256;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.kblocks = (K + BK - 1) / BK;
+  p.status = gfs_host::status_words();
+  p.rope_b = 1;
+  p.ce_partials = static_cast<float2*>(partials);
+  const int pairs = std::min(p.tiles_m * p.tiles_n, gfs_host::sm_count() / 2);
+  return launch2<false, false, COMM_NONE, 3>(ta, tb, p, 2 * pairs, stream);
 }
 
 // SwiGLU-fused products of the MLP on CTA pairs; same contract as gfs_gemm_bf16_swiglu (gemm.cu):

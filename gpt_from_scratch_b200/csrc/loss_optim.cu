@@ -82,6 +82,35 @@ ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restr
   }
 }
 
+// Same outputs as ce_fwd_kernel, from per-slice statistics that the LM-head GEMM epilogue already
+// produced (partials: float2 {max, sum exp(x - max)} [parts][M]); only the target logit is read
+// from the logits. One thread per row; consecutive threads read consecutive float2.
+__global__ void ce_from_partials_kernel(const float2* __restrict__ partials, const __nv_bfloat16* __restrict__ logits,
+                                        const long long* __restrict__ target, float* __restrict__ stats,
+                                        float* __restrict__ lse, float* __restrict__ loss, int parts, int M, int Vp,
+                                        long ld, int v0, int single_rank) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float gm = -INFINITY, gs = 0.f;
+  for (int i = 0; i < parts; ++i) {
+    const float2 ms = partials[static_cast<size_t>(i) * M + row];
+    const float nm = fmaxf(gm, ms.x);
+    if (nm != -INFINITY) gs = gs * __expf(gm - nm) + ms.y * __expf(ms.x - nm);
+    gm = nm;
+  }
+  const long long t = target[row];
+  float tz = 0.f;
+  if (t >= v0 && t < v0 + Vp) tz = __bfloat162float(logits[static_cast<size_t>(row) * ld + (t - v0)]);
+  stats[3 * row + 0] = gm;
+  stats[3 * row + 1] = gs;
+  stats[3 * row + 2] = tz;
+  if (single_rank) {
+    const float l = gm + __logf(gs);
+    lse[row] = l;
+    loss[row] = l - tz;
+  }
+}
+
 // Combine the per-rank stats of `world` ranks (stats_all is [world, M, 3]).
 __global__ void ce_combine_kernel(const float* __restrict__ stats_all, float* __restrict__ lse,
                                   float* __restrict__ loss, int M, int world) {
@@ -274,6 +303,16 @@ int gfs_ce_fwd(const void* logits, const void* target, void* stats, void* lse, v
   ce_fwd_kernel<<<M, CE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(logits), static_cast<const long long*>(target), static_cast<float*>(stats),
       static_cast<float*>(lse), static_cast<float*>(loss), Vp, ld, v0, single_rank);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int gfs_ce_from_partials(const void* partials, const void* logits, const void* target, void* stats, void* lse,
+                         void* loss, int parts, int M, int Vp, long ld, int v0, int single_rank, void* stream) {
+  if (M == 0) return 0;
+  ce_from_partials_kernel<<<(M + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float2*>(partials), static_cast<const __nv_bfloat16*>(logits),
+      static_cast<const long long*>(target), static_cast<float*>(stats), static_cast<float*>(lse),
+      static_cast<float*>(loss), parts, M, Vp, ld, v0, single_rank);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

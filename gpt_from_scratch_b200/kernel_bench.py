@@ -85,6 +85,10 @@ def build_cases(dev, small: bool):
     gemm_case("gemm_fwd_gate_up", M, 2 * I, H)
     gemm_case("gemm_fwd_down_residual", M, H, I, add=True)
     gemm_case("gemm_fwd_lm_head", M, V, H)
+    from .ops.gemm import linear_fwd_ce
+    xl, wl = rnd(M, H), rnd(V, H) * 0.05
+    cases.append(("gemm_fwd_lm_head+ce_stats", lambda: linear_fwd_ce(xl, wl), 2.0 * M * V * H,
+                  2 * (M * H + V * H + M * V)))
     gemm_case("gemm_dgrad_qkv", M, H, 3 * H, b_mn=True)
     gemm_case("gemm_dgrad_gate_up", M, H, 2 * I, b_mn=True)
     gemm_case("gemm_dgrad_down", M, I, H, b_mn=True)

@@ -29,4 +29,5 @@ class GPTModel(nn.Module):
         for layer in self.layers:
             hidden = layer(hidden)
         hidden = self.final_norm(hidden)
-        return self.output(hidden)                 # [S, B, V/P]
+        # the LM head's GEMM epilogue also emits the softmax statistics the loss needs
+        return self.output(hidden, ce_stats=True)  # [S, B, V/P]

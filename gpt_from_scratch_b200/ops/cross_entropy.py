@@ -26,6 +26,22 @@ def ce_local_stats(logits2d: torch.Tensor, target: torch.Tensor, vocab_start: in
     return stats, lse, loss
 
 
+def ce_stats_from_partials(partials: torch.Tensor, logits2d: torch.Tensor, target: torch.Tensor, vocab_start: int,
+                           single_rank: bool):
+    """Same outputs as :func:`ce_local_stats`, from the per-slice statistics the LM-head GEMM epilogue
+    produced (``partials`` fp32 ``[parts, M, 2]``): no pass over the logits."""
+    M, Vp = logits2d.shape
+    dev = logits2d.device
+    stats = torch.empty((M, 3), dtype=torch.float32, device=dev)
+    lse = torch.empty(M, dtype=torch.float32, device=dev)
+    loss = torch.empty(M, dtype=torch.float32, device=dev)
+    rc = _lib.lib().gfs_ce_from_partials(partials.data_ptr(), logits2d.data_ptr(), target.data_ptr(), stats.data_ptr(),
+                                         lse.data_ptr(), loss.data_ptr(), partials.shape[0], M, Vp,
+                                         logits2d.stride(0), vocab_start, 1 if single_rank else 0, _lib.stream_ptr())
+    _lib.check(rc, "gfs_ce_from_partials")
+    return stats, lse, loss
+
+
 def ce_combine(stats_all: torch.Tensor):
     """stats_all: [world, M, 3] -> (lse [M], loss [M])."""
     world, M, _ = stats_all.shape

@@ -122,6 +122,26 @@ def linear_fwd(x2d: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None
     return y
 
 
+def linear_fwd_ce(x2d: torch.Tensor, w: torch.Tensor):
+    """LM head: ``(x2d @ w^T, partials)`` where ``partials`` (fp32 ``[parts, M, 2]``) holds the
+    online-softmax statistics of every 128-column slice of each row of the bf16 logits, produced by
+    the GEMM epilogue; ``None`` when the problem does not run on the CTA-pair kernel."""
+    M, K = x2d.shape
+    N = w.shape[0]
+    if (_CE_EPILOGUE and use_native(x2d, w) and _PAIR_ENABLED and K >= 256 and N % 8 == 0 and
+            ((M + 255) // 256) * ((N + 255) // 256) >= _PAIR_MIN_TILES):
+        a, b = _rowmajor_2d(x2d), _rowmajor_2d(w)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        parts = _lib.lib().gfs_gemm2_ce_parts(N)
+        partials = torch.empty((parts, M, 2), dtype=torch.float32, device=a.device)
+        rc = _lib.lib().gfs_gemm2_bf16_ce(a.data_ptr(), b.data_ptr(), out.data_ptr(), partials.data_ptr(), M, N, K,
+                                          a.stride(0), b.stride(0), out.stride(0), _lib.stream_ptr())
+        if rc != -20:
+            _lib.check(rc, "gfs_gemm2_bf16_ce")
+            return out, partials
+    return linear_fwd(x2d, w), None
+
+
 def linear_dgrad(dy2d: torch.Tensor, w: torch.Tensor, addend: torch.Tensor | None = None,
                  out: torch.Tensor | None = None) -> torch.Tensor:
     """``dy2d[M,N] @ w[N,K] (+ addend[M,K])``."""
@@ -182,6 +202,7 @@ class _WgradQueue:
                 it[4]()
 
 
+_CE_EPILOGUE = os.environ.get("GFS_CE_EPILOGUE", "1") != "0"
 _wgrad_queue = _WgradQueue()
 _WGRAD_GROUPING = os.environ.get("GFS_WGRAD_GROUPING", "1") != "0"
 

@@ -61,12 +61,18 @@ class _LinearFn(torch.autograd.Function):
     """``y = x @ W^T (+ residual)`` with explicit dgrad/wgrad so the weight gradient can go
     to a :class:`GradSink`."""
 
+    last_ce_partials = None   # statistics produced by the most recent forward with ce_stats=True
+
     @staticmethod
-    def forward(ctx, x, weight, residual, sink, rope=None):
+    def forward(ctx, x, weight, residual, sink, rope=None, ce_stats=False):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         res2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
-        y2 = gemm_ops.linear_fwd(x2, weight, res2, rope=rope)
+        if ce_stats and residual is None and rope is None:
+            y2, _LinearFn.last_ce_partials = gemm_ops.linear_fwd_ce(x2, weight)
+        else:
+            _LinearFn.last_ce_partials = None
+            y2 = gemm_ops.linear_fwd(x2, weight, res2, rope=rope)
         ctx.save_for_backward(x2, weight)
         ctx.sink = sink
         ctx.has_res = residual is not None
@@ -90,15 +96,24 @@ class _LinearFn(torch.autograd.Function):
         elif ctx.needs_input_grad[1]:
             dw = gemm_ops.linear_wgrad(dy2, x2)
         dres = dy if ctx.has_res else None
-        return dx, dw, dres, None, None
+        return dx, dw, dres, None, None, None
 
 
 def linear_with_sink(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
-                     rope: tuple | None = None) -> torch.Tensor:
+                     rope: tuple | None = None, ce_stats: bool = False) -> torch.Tensor:
     """``rope``: rotary epilogue of the native GEMM. Its inverse is NOT applied by this
     function's backward: the caller's next operator must return gradients w.r.t. the
-    un-rotated output (the fused attention backward does)."""
-    return _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope)
+    un-rotated output (the fused attention backward does).
+
+    ``ce_stats``: the output is the LM head's logits; when the CTA-pair GEMM serves the problem its
+    epilogue also produces the per-row softmax statistics, attached to the returned tensor as
+    ``_gfs_ce_partials`` for :func:`vocab_parallel_cross_entropy` (which then skips its pass over the
+    logits)."""
+    out = _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope, ce_stats)
+    if ce_stats and _LinearFn.last_ce_partials is not None:
+        out._gfs_ce_partials = _LinearFn.last_ce_partials
+        _LinearFn.last_ce_partials = None
+    return out
 
 
 class ColumnParallelLinear(nn.Module):
@@ -123,14 +138,14 @@ class ColumnParallelLinear(nn.Module):
         ColumnParallelLinear._salt += 1
         _init_sharded(self.weight, init_method, ColumnParallelLinear._salt)
 
-    def forward(self, input_, rope=None):
+    def forward(self, input_, rope=None, ce_stats=False):
         world = ps.get_tensor_model_parallel_world_size()
         if world > 1 and ps.get_comm_impl() == "fused" and input_.is_cuda:
             from . import fused_comm
             out = fused_comm.allgather_linear(input_, self.weight, rope=rope)
         else:
             full = mappings.gather_from_sequence_parallel_region(input_)
-            out = linear_with_sink(full, self.weight, rope=rope)
+            out = linear_with_sink(full, self.weight, rope=rope, ce_stats=ce_stats and self.bias is None)
         if self.bias is not None:
             out = out + self.bias
         return out

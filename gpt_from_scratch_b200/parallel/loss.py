@@ -33,7 +33,13 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
             tgt = target.reshape(-1).contiguous()
             if tgt.dtype != torch.int64:
                 tgt = tgt.long()
-            stats, lse, loss = ce_ops.ce_local_stats(lg2, tgt, v0, single_rank=(world == 1))
+            partials = getattr(lg, "_gfs_ce_partials", None)
+            if (partials is not None and lg2.data_ptr() == lg.data_ptr() and partials.shape[1] == lg2.shape[0]
+                    and partials.device == lg2.device):
+                # statistics already produced by the LM-head GEMM epilogue: no pass over the logits
+                stats, lse, loss = ce_ops.ce_stats_from_partials(partials, lg2, tgt, v0, single_rank=(world == 1))
+            else:
+                stats, lse, loss = ce_ops.ce_local_stats(lg2, tgt, v0, single_rank=(world == 1))
             if world > 1:
                 if ps.get_comm_impl() == "fused":
                     from . import fused_comm

@@ -168,3 +168,35 @@ def test_checkpoint_roundtrip_gpu(cuda_device, tmp_path):
     load_checkpoint(str(tmp_path), b.model, b.optimizer)
     tail_b = [step(b, t) for t in data[3:]]
     assert tail_a == tail_b, (tail_a, tail_b)
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 256, 1000), (1000, 320, 2048), (256, 768, 50304)])
+def test_lm_head_epilogue_ce_statistics(cuda_device, M, K, N):
+    """Softmax statistics produced by the LM-head GEMM epilogue == those of the separate pass
+    over the same bf16 logits, and == an fp32 log-sum-exp of those logits."""
+    from gpt_from_scratch_b200.ops import cross_entropy as ce_ops
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device=cuda_device, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=cuda_device, generator=g) * 0.2).bfloat16()
+    tgt = torch.randint(0, N, (M,), device=cuda_device, generator=g)
+    saved = gemm_ops._PAIR_MIN_TILES
+    gemm_ops._PAIR_MIN_TILES = 1
+    try:
+        logits, partials = gemm_ops.linear_fwd_ce(x, w)
+    finally:
+        gemm_ops._PAIR_MIN_TILES = saved
+    assert partials is not None
+    ref_logits = x.float() @ w.float().t()
+    assert (logits.float() - ref_logits).abs().max() <= 2e-2 * ref_logits.abs().max() + 1e-3
+    stats_a, lse_a, loss_a = ce_ops.ce_stats_from_partials(partials, logits, tgt, 0, True)
+    stats_b, lse_b, loss_b = ce_ops.ce_local_stats(logits, tgt, 0, True)
+    lse_ref = torch.logsumexp(logits.float(), dim=-1)
+    torch.cuda.synchronize()
+    assert (lse_a - lse_ref).abs().max() < 2e-3, (lse_a - lse_ref).abs().max()
+    assert (lse_a - lse_b).abs().max() < 2e-3
+    assert (loss_a - loss_b).abs().max() < 2e-3
+    assert torch.equal(stats_a[:, 2], stats_b[:, 2])      # target logits
+    # vocabulary-parallel use: targets outside the local range contribute a zero target logit
+    stats_c, _, _ = ce_ops.ce_stats_from_partials(partials, logits, tgt, N, False)
+    assert float(stats_c[:, 2].abs().max()) == 0.0
