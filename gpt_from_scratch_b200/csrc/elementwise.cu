@@ -312,6 +312,40 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 }
 
 // ---------------------------------------------------------------------------
+// Dropout fused with the residual add (the reference's `residual + dropout(x)`,
+// core/transformer_layer.py:97,103). Counter-based generator: one 64-bit mix of
+// (seed, vector index) yields the eight 8-bit thresholds of a vector of 8 elements, so
+// the keep probability is quantised to 1/256 and no mask tensor exists.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+__global__ void dropout_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                                        __nv_bfloat16* __restrict__ out, long long nvec, float p,
+                                        unsigned long long seed, int backward) {
+  const unsigned int drop_below = static_cast<unsigned int>(p * 256.f + 0.5f);  // byte < drop_below -> dropped
+  const float scale = 256.f / static_cast<float>(256u - drop_below);           // 1 / (realised keep probability)
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const unsigned long long bits = mix64(seed ^ (static_cast<unsigned long long>(v) * 0xd1342543de82ef95ull));
+    float f[8], r[8], o[8];
+    load8(x + 8 * v, f);
+    if (!backward && residual != nullptr) load8(residual + 8 * v, r);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const bool keep = ((bits >> (8 * e)) & 0xffull) >= drop_below;
+      const float d = keep ? f[e] * scale : 0.f;
+      o[e] = (!backward && residual != nullptr) ? r[e] + round_bf16(d) : d;
+    }
+    store8(out + 8 * v, o);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // SwiGLU on a [M, 2I] buffer whose first I columns are the gate and last I the up half.
 // ---------------------------------------------------------------------------
 // Grid: x covers the 8-column vectors of a row, y strides over rows (no integer divisions).
@@ -501,6 +535,22 @@ int gfs_rope(void* x, const void* cosb, const void* sinb, int S, int B, int nh, 
   rope_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(x), static_cast<const float*>(cosb), static_cast<const float*>(sinb), S, B, nh * D,
       D, parts, token_stride, backward, s_offset);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// out = residual + dropout(x, p) (forward) or dx = dy * keep / (1 - p) (backward, mode 1). The keep
+// mask is a pure function of (seed, element index), so the backward regenerates it instead of
+// storing it; n is a multiple of 8.
+int gfs_dropout_residual(const void* x, const void* residual, void* out, long long n, float p, unsigned long long seed,
+                         int backward, void* stream) {
+  if (n & 7) return -1;
+  if (n == 0) return 0;
+  if (!(p >= 0.f) || p >= 1.f) return -1;
+  const long long nvec = n >> 3;
+  const int blocks = static_cast<int>(std::min<long long>((nvec + 255) / 256, static_cast<long long>(gfs_host::sm_count()) * 16));
+  dropout_residual_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(out), nvec, p, seed, backward);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -153,7 +153,7 @@ def build_cases(dev, small: bool):
     grows = torch.full((M,), 1.0 / M, device=dev)
     cases.append(("ce_fwd", lambda: ce_ops.ce_local_stats(logits, tgt, 0, True), 0, 2 * M * V))
     cases.append(("ce_bwd_inplace", lambda: ce_ops.ce_backward_inplace(logits, lse_ce, tgt, grows, 0), 0, 4 * M * V))
-    n = 64 * 1024 * 1024 if not small else 8 * 1024 * 1024
+    n = 124_475_904 if not small else 8 * 1024 * 1024   # parameter count of the GPT-124M shape (vocab 50304)
     grad = rnd(n)
     master = torch.randn(n, device=dev)
     m1, m2 = torch.zeros_like(master), torch.zeros_like(master)

@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 
 from ..ops.attention import attention_reference, fused_rope_attention
+from ..ops.dropout import dropout_add
 from ..ops.rope import rope_reference
 from ..parallel import parallel_state as ps
 from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
@@ -85,5 +86,6 @@ class TransformerLayer(nn.Module):
             x = self.attention(h, residual=res)
             h, res = self.post_attention_norm(x, fork=True)
             return self.mlp(h, residual=res)
-        x = hidden_states + self.dropout(self.attention(self.input_norm(hidden_states)))
-        return x + self.dropout(self.mlp(self.post_attention_norm(x)))
+        # residual + dropout(x) in one kernel (regenerated mask in the backward)
+        x = dropout_add(self.attention(self.input_norm(hidden_states)), hidden_states, self.dropout_prob, True)
+        return dropout_add(self.mlp(self.post_attention_norm(x)), x, self.dropout_prob, True)

@@ -186,3 +186,29 @@ def test_swiglu_gemm_epilogues(cuda_device, M, H, I, pair):
     dact = (dy.float() @ w_dn.float()).bfloat16().float()
     act_ref.backward(dact)
     _close(dgu, guf.grad, 3e-2, 3e-2, what="d_gate_up")
+
+
+def test_dropout_residual_kernel(cuda_device):
+    """Fused residual + dropout: keep rate, scaling, regenerated mask in the backward."""
+    from gpt_from_scratch_b200.ops.dropout import dropout_add
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = (torch.rand(512, 768, device=cuda_device, generator=g) * 2 + 2).bfloat16().requires_grad_()   # in [2, 4]
+    res = (torch.randn(512, 768, device=cuda_device, generator=g) * 0.25).bfloat16().requires_grad_()
+    host_gen = torch.Generator().manual_seed(5)
+    p = 0.25
+    y = dropout_add(x, res, p, True, generator=host_gen)
+    kept = (y.float() - res.float()).abs() > 0.5            # x is bounded away from zero
+    rate = kept.float().mean().item()
+    assert abs(rate - (1 - p)) < 0.01, rate
+    expect = res.float() + torch.where(kept, x.float() / (1 - p), torch.zeros_like(x.float())).bfloat16().float()
+    assert (y.float() - expect).abs().max() < 0.07
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert torch.equal(res.grad, dy)
+    dx_expect = torch.where(kept, dy.float() / (1 - p), torch.zeros_like(dy.float()))
+    assert (x.grad.float() - dx_expect).abs().max() < 0.05
+    assert torch.equal(x.grad != 0, kept & (dy != 0))        # same mask in both directions
+    # a different call draws a different mask; evaluation mode is the plain sum
+    y2 = dropout_add(x.detach(), res.detach(), p, True, generator=host_gen)
+    assert not torch.equal(y2, y.detach())
+    assert torch.equal(dropout_add(x.detach(), res.detach(), p, False), res.detach() + x.detach())
