@@ -233,3 +233,54 @@ def test_native_library_is_required_on_request(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(_lib.NativeLibraryError):
         _lib.lib()
+
+
+def test_dropout_add_and_wgrad_queue_cpu_paths():
+    """Host-side behaviour of two helpers whose kernels only exist on the GPU: the fused
+    residual+dropout falls back to the composition off-GPU, and the weight-gradient queue
+    never parks a problem it cannot serve natively."""
+    import torch
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    from gpt_from_scratch_b200.ops.dropout import dropout_add
+    x, r = torch.randn(4, 16), torch.randn(4, 16)
+    assert torch.equal(dropout_add(x, r, 0.0, True), r + x)
+    assert torch.equal(dropout_add(x, r, 0.3, False), r + x)
+    torch.manual_seed(0)
+    y = dropout_add(x, r, 0.5, True)
+    kept = (y - r).abs() > 0
+    assert torch.allclose((y - r)[kept], (2.0 * x)[kept])
+    assert 0 < kept.float().mean() < 1
+
+    class Sink:
+        def __init__(self):
+            self.t, self.finished = torch.zeros(8, 16), False
+
+        def target(self):
+            return self.t
+
+        def consume_accumulate(self):
+            return False
+
+        def done(self):
+            self.finished = True
+
+    dy, xx, sk = torch.randn(32, 8), torch.randn(32, 16), Sink()
+    gemm_ops.linear_wgrad_to_sink(dy, xx, sk)          # fp32 on CPU: computed at once, not parked
+    assert sk.finished and torch.allclose(sk.t, dy.t() @ xx, atol=1e-5)
+    gemm_ops.flush_wgrad()                              # nothing parked: a no-op
+
+
+def test_train_step_async_cpu():
+    import torch
+    from gpt_from_scratch_b200.config import GPTConfig
+    from gpt_from_scratch_b200.engine import TrainEngine
+    from gpt_from_scratch_b200.parallel import parallel_state as ps
+    ps.set_device(torch.device("cpu"))
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_parallel_state(1)
+    cfg = GPTConfig(vocab_size=64, hidden_size=32, num_layers=1, num_attention_heads=2, max_position_embeddings=16,
+                    intermediate_size=64)
+    eng = TrainEngine(cfg, lr=1e-3, dtype=torch.float32, seed=1)
+    t = torch.randint(0, 64, (2, 17), generator=torch.Generator().manual_seed(0))
+    h = eng.train_step_async(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+    assert h.ready() and 0 < h.value() < 10
