@@ -164,8 +164,8 @@ class _WgradQueue:
     reduction pass); several of them in ONE grouped launch (``gfs_gemm2_wgrad_grouped``) fill
     a wave of CTA pairs. A weight gradient is only needed at the optimizer step, so problems
     that write into a gradient sink are parked here (holding references to their operands)
-    and launched when enough tiles have accumulated or when :func:`flush_wgrad` is called
-    (the engine does so after ``backward``).
+    and launched when enough tiles have accumulated, at the end of the backward pass that
+    parked them (an autograd-engine callback), or when :func:`flush_wgrad` is called.
     """
 
     MAX_GROUP = 4
@@ -173,6 +173,11 @@ class _WgradQueue:
     def __init__(self):
         self.items: list[tuple] = []
         self.tiles = 0
+        self._callback_pending = False
+
+    def _end_of_backward(self) -> None:
+        self._callback_pending = False
+        self.flush()
 
     @staticmethod
     def tiles_of(M: int, N: int) -> int:
@@ -181,6 +186,14 @@ class _WgradQueue:
     def push(self, dy2d, x2d, out, accumulate, done_cb) -> None:
         self.items.append((dy2d, x2d, out, accumulate, done_cb))
         self.tiles += self.tiles_of(dy2d.shape[1], x2d.shape[1])
+        if not self._callback_pending:
+            # whatever is still parked when this backward pass ends is launched then, so every
+            # ``.grad`` is complete when ``backward()`` returns
+            try:
+                torch.autograd.Variable._execution_engine.queue_callback(self._end_of_backward)
+                self._callback_pending = True
+            except RuntimeError:
+                pass   # not inside a backward pass: flush_wgrad() / optimizer.step() will launch it
         if len(self.items) == self.MAX_GROUP or self.tiles >= _PAIR_MIN_TILES:
             self.flush()
 

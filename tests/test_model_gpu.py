@@ -221,3 +221,28 @@ def test_training_with_dropout(cuda_device):
     assert all(l == l and l < 20 for l in losses), losses
     assert losses[-1] < losses[0] - 0.5, losses
     assert _lib.read_status()[0] == 0
+
+
+def test_gradients_complete_after_backward(cuda_device):
+    """Weight gradients parked for a grouped launch are launched by the end of backward():
+    every .grad is final before optimizer.step()."""
+    from gpt_from_scratch_b200.config import GPTConfig
+    from gpt_from_scratch_b200.engine import TrainEngine
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    from gpt_from_scratch_b200.parallel import parallel_state as ps
+    ps.set_device(cuda_device)
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_parallel_state(1)
+    cfg = GPTConfig(vocab_size=512, hidden_size=256, num_layers=2, num_attention_heads=4,
+                    max_position_embeddings=128, intermediate_size=512, init_method="normal")
+    eng = TrainEngine(cfg, lr=1e-3, seed=8)
+    t = torch.randint(0, 512, (4, 129), generator=torch.Generator().manual_seed(2))
+    x, y = t[:, :-1].contiguous().cuda(), t[:, 1:].contiguous().cuda()
+    eng.optimizer.zero_grad()
+    eng.forward_loss(x, y).backward()
+    assert not gemm_ops._wgrad_queue.items, "weight gradients still parked after backward()"
+    torch.cuda.synchronize()
+    for name, p in eng.model.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad.float()).all(), name
+        if name.endswith("weight") and p.dim() == 2:
+            assert float(p.grad.float().abs().max()) > 0, name
