@@ -278,6 +278,38 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, __nv
   }
 }
 
+// The same reduction for several RMSNorm layers in one launch (blockIdx.y = layer): the
+// per-layer reductions are tiny, so a backward pass parks them and runs them together.
+constexpr int DW_MULTI_MAX = 32;
+struct DwReduceBatch {
+  const float* partial[DW_MULTI_MAX];
+  __nv_bfloat16* dw[DW_MULTI_MAX];
+  int parts[DW_MULTI_MAX];
+  int accumulate[DW_MULTI_MAX];
+};
+
+__global__ void rmsnorm_dw_reduce_multi_kernel(const __grid_constant__ DwReduceBatch b, int H) {
+  __shared__ float sm[32][33];
+  const int l = blockIdx.y;
+  const float* __restrict__ partial = b.partial[l];
+  __nv_bfloat16* __restrict__ dw = b.dw[l];
+  const int parts = b.parts[l];
+  const int i = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.f;
+  if (i < H) {
+    for (int p = threadIdx.y; p < parts; p += 32) s += partial[static_cast<size_t>(p) * H + i];
+  }
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += sm[y][threadIdx.x];
+    if (b.accumulate[l]) t += __bfloat162float(dw[i]);
+    dw[i] = __float2bfloat16_rn(t);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Rotary embedding, interleaved pairs, in place on `parts` consecutive [nh*D] blocks
 // of every token (parts = 2: the q and k thirds of a [S,B,3,nh,D] buffer).
@@ -521,10 +553,28 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
                                                             rows_per_cta);
   }
   if (cudaGetLastError() != cudaSuccess) return -11;
+  if (dw == nullptr) return 0;   // the caller reduces `partial` later (gfs_rmsnorm_dw_reduce_multi)
   rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(static_cast<const float*>(partial),
                                                               static_cast<__nv_bfloat16*>(dw), parts, H,
                                                               accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+// Weight-gradient reductions of n RMSNorm layers (n <= 32) that ran gfs_rmsnorm_bwd with dw == null:
+// dw_l (bf16 [H]) = (or +=) column sums of partial_l (fp32 [parts_l, H]).
+int gfs_rmsnorm_dw_reduce_multi(int n, const unsigned long long* partial, const unsigned long long* dw,
+                                const int* parts, const int* accumulate, int H, void* stream) {
+  if (n <= 0) return 0;
+  if (n > DW_MULTI_MAX) return -1;
+  DwReduceBatch b{};
+  for (int i = 0; i < n; ++i) {
+    b.partial[i] = reinterpret_cast<const float*>(partial[i]);
+    b.dw[i] = reinterpret_cast<__nv_bfloat16*>(dw[i]);
+    b.parts[i] = parts[i];
+    b.accumulate[i] = accumulate[i];
+  }
+  rmsnorm_dw_reduce_multi_kernel<<<dim3((H + 31) / 32, n), dim3(32, 32), 0, static_cast<cudaStream_t>(stream)>>>(b, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 int gfs_rope(void* x, const void* cosb, const void* sinb, int S, int B, int nh, int D, int parts, long token_stride,

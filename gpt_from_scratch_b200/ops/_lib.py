@@ -82,6 +82,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
         "gfs_gemm_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
                                 ctypes.c_longlong, vp], i),
+        "gfs_rmsnorm_dw_reduce_multi": ([i, ulp, ulp, ip, ip, i, vp], i),
         "gfs_dropout_residual": ([vp, vp, vp, ctypes.c_longlong, f, ctypes.c_ulonglong, i, vp], i),
         "gfs_gemm2_ce_parts": ([i], i),
         "gfs_gemm2_bf16_ce": ([vp, vp, vp, vp, i, i, i, i, i, i, vp], i),

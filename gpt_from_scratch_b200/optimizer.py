@@ -36,6 +36,7 @@ import torch.distributed as dist
 
 from .ops import adam as adam_ops
 from .ops import gemm as gemm_ops
+from .ops.rmsnorm import flush_dw_reductions
 from .parallel import mappings
 from .parallel import parallel_state as ps
 
@@ -128,6 +129,7 @@ class DistributedOptimizer:
         """Prepare the gradient buffer for a new step. Never sets ``.grad`` to None (the
         views into the flat buffer must survive)."""
         gemm_ops.flush_wgrad()   # nothing parked may land in the buffer after this point
+        flush_dw_reductions()
         if self.use_fused_kernels and not set_to_zero:
             for p in self.params:
                 p._grad_fresh = True
@@ -152,6 +154,7 @@ class DistributedOptimizer:
     # ------------------------------------------------------------------ step
     def step(self):
         gemm_ops.flush_wgrad()   # weight-gradient GEMMs parked for a grouped launch
+        flush_dw_reductions()
         self._materialise_unwritten()
         self._sum_replicated_grads_over_tp()
         if self.use_fused_comm:
