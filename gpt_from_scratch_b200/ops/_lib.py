@@ -126,6 +126,39 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+class _NullRange:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _NvtxRange:
+    __slots__ = ("name",)
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+_NVTX = os.environ.get("GFS_NVTX", "0") == "1"
+_NULL_RANGE = _NullRange()
+
+
+def nvtx(name: str):
+    """``with nvtx("name"):`` marks a fused operator for timeline tools (chrome traces of
+    ``tools/profile_train.py``, ncu's NVTX filters). Enabled with GFS_NVTX=1, free otherwise."""
+    return _NvtxRange(name) if _NVTX else _NULL_RANGE
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -50,8 +50,9 @@ def flash_fwd_native(q, k, v, out, causal: bool, scale: float) -> torch.Tensor:
     S, B, nh, D = q.shape
     lse = torch.empty((B, nh, _pad128(S)), dtype=torch.float32, device=q.device)
     st = (ctypes.c_longlong * 12)(*_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out))
-    rc = _lib.lib().gfs_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                  S, B, nh, D, st, scale, 1 if causal else 0, _lib.stream_ptr())
+    with _lib.nvtx("flash_attention_fwd"):
+        rc = _lib.lib().gfs_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      S, B, nh, D, st, scale, 1 if causal else 0, _lib.stream_ptr())
     _lib.check(rc, "gfs_flash_fwd")
     return lse
 

@@ -202,17 +202,22 @@ class _WgradQueue:
         if not items:
             return
         n = len(items)
+        with _lib.nvtx("fused:grouped_wgrad"):
+            rc = self._launch(items, n)
+        _lib.check(rc, "gfs_gemm2_wgrad_grouped")
+        for it in items:
+            if it[4] is not None:
+                it[4]()
+
+    @staticmethod
+    def _launch(items, n) -> int:
         U, I = ctypes.c_ulonglong * n, ctypes.c_int * n
-        rc = _lib.lib().gfs_gemm2_wgrad_grouped(
+        return _lib.lib().gfs_gemm2_wgrad_grouped(
             n, U(*[it[0].data_ptr() for it in items]), U(*[it[1].data_ptr() for it in items]),
             U(*[it[2].data_ptr() for it in items]), I(*[it[0].shape[1] for it in items]),
             I(*[it[1].shape[1] for it in items]), I(*[it[0].shape[0] for it in items]),
             I(*[it[0].stride(0) for it in items]), I(*[it[1].stride(0) for it in items]),
             I(*[it[2].stride(0) for it in items]), I(*[1 if it[3] else 0 for it in items]), _lib.stream_ptr())
-        _lib.check(rc, "gfs_gemm2_wgrad_grouped")
-        for it in items:
-            if it[4] is not None:
-                it[4]()
 
 
 _CE_EPILOGUE = os.environ.get("GFS_CE_EPILOGUE", "1") != "0"

@@ -62,7 +62,8 @@ class _FusedMLP(torch.autograd.Function):
         x2 = x.reshape(-1, H)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        gu, act = swiglu_gemm_fwd(x2, w_gu)
+        with _lib.nvtx("fused:gemm_swiglu_fwd"):
+            gu, act = swiglu_gemm_fwd(x2, w_gu)
         res2 = residual.reshape(-1, w_down.shape[0]) if residual is not None else None
         out = gemm_ops.linear_fwd(act, w_down, res2)
         ctx.save_for_backward(x2, gu, act, w_gu, w_down)
@@ -79,7 +80,8 @@ class _FusedMLP(torch.autograd.Function):
         if not d2.is_contiguous():
             d2 = d2.contiguous()
         if x2.shape[-1] >= MIN_HIDDEN_FOR_BWD_FUSION or _pair_eligible(d2.shape[0], gu.shape[1] // 2, 256):
-            dgu = swiglu_gemm_bwd(d2, w_down, gu)
+            with _lib.nvtx("fused:gemm_swiglu_bwd"):
+                dgu = swiglu_gemm_bwd(d2, w_down, gu)
         else:
             # short contraction: the plain dgrad GEMM + the SwiGLU backward kernel are faster
             dact = gemm_ops.linear_dgrad(d2, w_down)

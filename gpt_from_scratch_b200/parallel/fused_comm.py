@@ -53,6 +53,11 @@ def _gemm_comm(mode: int, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, r
         rc_args = (cos.data_ptr(), sin.data_ptr(), rope_cols, head_dim, batch)
     else:
         rc_args = (0, 0, 0, 0, 1)
+    with _lib.nvtx("fused:allgather_gemm" if mode == MODE_AG else "fused:gemm_reduce_scatter"):
+        _gemm_comm_launch(mode, a, b, out, residual, M, N, K, b_mn_major, grp, buf, site, rc_args)
+
+
+def _gemm_comm_launch(mode, a, b, out, residual, M, N, K, b_mn_major, grp, buf, site, rc_args) -> None:
     args = (mode, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
             _lib.ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, 1 if b_mn_major else 0,
             grp.world, grp.rank, buf.ptrs, _site_flag_ptrs(grp, site), ctypes.byref(site.target), *rc_args, WAIT_NS,
@@ -237,7 +242,9 @@ def embedding_reduce_scatter(input_ids: torch.Tensor, module) -> torch.Tensor:
     if ids.dtype != torch.int64:
         ids = ids.long()
     w = module.weight
-    return _EmbeddingReduceScatter.apply(ids, w, module.vocab_start_index, module.vocab_end_index, GradSink.of(w))
+    with _lib.nvtx("fused:embedding_reduce_scatter"):
+        return _EmbeddingReduceScatter.apply(ids, w, module.vocab_start_index, module.vocab_end_index,
+                                             GradSink.of(w))
 
 
 # --------------------------------------------------------------------------- cross entropy
@@ -249,9 +256,10 @@ def ce_exchange_combine(stats: torch.Tensor):
     site = grp.site(("ce", M))
     lse = torch.empty(M, dtype=torch.float32, device=stats.device)
     loss = torch.empty(M, dtype=torch.float32, device=stats.device)
-    rc = _lib.lib().gfs_ce_exchange(stats.data_ptr(), lse.data_ptr(), loss.data_ptr(), M, buf.ptrs, grp.flag_ptrs,
-                                    grp.world, grp.rank, site.slot0, ctypes.byref(site.target), WAIT_NS,
-                                    _lib.stream_ptr())
+    with _lib.nvtx("fused:ce_exchange_combine"):
+        rc = _lib.lib().gfs_ce_exchange(stats.data_ptr(), lse.data_ptr(), loss.data_ptr(), M, buf.ptrs,
+                                        grp.flag_ptrs, grp.world, grp.rank, site.slot0, ctypes.byref(site.target),
+                                        WAIT_NS, _lib.stream_ptr())
     _lib.check(rc, "gfs_ce_exchange")
     return lse, loss
 
@@ -311,7 +319,8 @@ class DataParallelComm:
         _lib.check(rc, "gfs_dp_adam_gather")
 
     def step(self, opt, state, *, step, lr, beta1, beta2, eps, weight_decay, clip, grad_scale) -> None:
-        self.reduce_and_norm()
+        with _lib.nvtx("fused:dp_reduce_scatter_norm"):
+            self.reduce_and_norm()
         extern = None
         if opt.tp_world_size > 1 and not opt.reference_quirks and clip > 0:
             # global norm over TP x DP with replicated parameters counted once: the tiny
@@ -324,6 +333,7 @@ class DataParallelComm:
             else:
                 local[1] = 0.0
             extern = opt._global_sumsq(local)
-        self.adam_and_gather(opt.fp32_master_shard.data, state["exp_avg"], state["exp_avg_sq"], step=step, lr=lr,
-                             beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip,
-                             grad_scale=grad_scale, extern_sumsq=extern)
+        with _lib.nvtx("fused:dp_clip_adam_allgather"):
+            self.adam_and_gather(opt.fp32_master_shard.data, state["exp_avg"], state["exp_avg_sq"], step=step, lr=lr,
+                                 beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip,
+                                 grad_scale=grad_scale, extern_sumsq=extern)

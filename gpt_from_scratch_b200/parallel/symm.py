@@ -14,11 +14,18 @@ order, which holds because they run the same program.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
 
 NUM_FLAG_SLOTS = 8192
+# Debug aid (GFS_SYMM_CANARIES=1): every symmetric buffer gets a 256-byte guard region on both
+# sides, filled with a pattern; check_canaries() verifies them (the multi-GPU tests do so after
+# exercising every fused kernel). Stands in for a memory checker on peer stores.
+CANARIES = os.environ.get("GFS_SYMM_CANARIES", "0") == "1"
+GUARD_BYTES = 256
+CANARY_BYTE = 0xA5
 _groups: dict = {}
 
 
@@ -47,6 +54,7 @@ class SymmGroup:
         self.rank = rank
         self.device = device
         self._buffers: dict = {}
+        self._raw: dict = {}
         self._sites: dict = {}
         self._pools: dict = {}
         self._next_slot = 0
@@ -63,15 +71,34 @@ class SymmGroup:
         buf = self._buffers.get(key)
         if buf is not None:
             return buf
-        t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+        guard = (GUARD_BYTES // dtype.itemsize) if CANARIES else 0
+        raw = symm_mem.empty(numel + 2 * guard, dtype=dtype, device=self.device)
+        t = raw[guard:guard + numel] if guard else raw
+        if guard:
+            # guard regions in front of and behind the usable range, checked by check_canaries()
+            raw.view(torch.uint8)[:GUARD_BYTES].fill_(CANARY_BYTE)
+            raw.view(torch.uint8)[-GUARD_BYTES:].fill_(CANARY_BYTE)
         if zero:
             t.zero_()
-        handle = symm_mem.rendezvous(t, self.group)
-        ptrs = (ctypes.c_ulonglong * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        handle = symm_mem.rendezvous(raw, self.group)
+        off = guard * dtype.itemsize
+        ptrs = (ctypes.c_ulonglong * self.world)(*[int(p) + off for p in handle.buffer_ptrs])
         assert int(ptrs[self.rank]) == t.data_ptr()
         buf = SymmBuffer(t, ptrs, handle)
         self._buffers[key] = buf
+        if guard:
+            self._raw[key] = raw
         return buf
+
+    def check_canaries(self) -> None:
+        """Raise if any kernel (of any rank) wrote outside the usable range of one of this rank's
+        symmetric buffers. Only meaningful with GFS_SYMM_CANARIES=1; synchronises the device."""
+        torch.cuda.synchronize(self.device)
+        for key, raw in self._raw.items():
+            b = raw.view(torch.uint8)
+            ok = bool((b[:GUARD_BYTES] == CANARY_BYTE).all()) and bool((b[-GUARD_BYTES:] == CANARY_BYTE).all())
+            if not ok:
+                raise RuntimeError(f"symmetric buffer {key[0]!r}: guard region overwritten on rank {self.rank}")
 
     def site(self, name) -> Site:
         s = self._sites.get(name)
@@ -115,6 +142,11 @@ def get_group(kind: str) -> SymmGroup:
             raise ValueError(kind)
         _groups[kind] = g
     return g
+
+
+def check_all_canaries() -> None:
+    for g in _groups.values():
+        g.check_canaries()
 
 
 def reset() -> None:

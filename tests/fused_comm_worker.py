@@ -143,7 +143,12 @@ def main():
     log("TP losses fused", traj["fused"])
     for a, b in zip(traj["fused"], traj["nccl"]):
         assert abs(a - b) < 2e-2, (traj)
-    log("TP training ok")
+    # run-twice check: the fused kernels sum in a fixed (rank) order, so a second run from the
+    # same seed must reproduce the losses bit for bit; a missing fence or a flag race shows up here
+    eng = TrainEngine(cfg, lr=1e-3, seed=3)
+    again = [float(eng.train_step(t[:2, :-1].contiguous().to(dev), t[:2, 1:].contiguous().to(dev))) for t in data]
+    assert again == traj["fused"], (again, traj["fused"])
+    log("TP training ok (fused path reproducible)")
 
     # ---- DP = world with the fused distributed optimizer ----
     ps.destroy_model_parallel()
@@ -173,6 +178,12 @@ def main():
     close(finals["fused"], finals["nccl"], "DP final parameters", 2e-3)
     log("DP training ok")
     torch.cuda.synchronize()
+    dist.barrier()
+    # no fused kernel of any rank wrote outside the usable range of a symmetric buffer
+    from gpt_from_scratch_b200.parallel import symm
+    if symm.CANARIES:
+        symm.check_all_canaries()
+        log("canaries intact")
     dist.barrier()
     log("WORKER OK")
     dist.destroy_process_group()
