@@ -380,6 +380,60 @@ __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t ta
     }
   }
 }
+// Final step of a fused GEMM -> reduce-scatter: out[row, :] = sum over source ranks of the staged
+// bf16 partial rows (in rank order: deterministic) + optional residual, rounded once. `stage` is
+// this rank's staging area [world][rows][N]. The vectors (8 columns each) are dealt to
+// `nthreads_total` threads of the whole grid, of which the caller is number `tid_global`; four
+// independent vectors are in flight per thread so the pass runs at memory speed, not latency.
+__device__ __forceinline__ void rs_reduce_rows(const __nv_bfloat16* __restrict__ stage, int world, int rows, int N,
+                                               const __nv_bfloat16* __restrict__ res, int ld_res,
+                                               __nv_bfloat16* __restrict__ out, int ld_out, size_t tid_global,
+                                               size_t nthreads_total) {
+  const int vpr = N >> 3;
+  const size_t total = static_cast<size_t>(rows) * vpr;
+  const size_t chunk_elems = static_cast<size_t>(rows) * N;
+  constexpr int U = 4;
+  for (size_t v0 = tid_global; v0 < total; v0 += nthreads_total * U) {
+    float acc[U][8];
+    uint4 rr[U];
+    size_t off_out[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + static_cast<size_t>(u) * nthreads_total;
+      live[u] = v < total;
+      const int row = live[u] ? static_cast<int>(v / vpr) : 0;
+      const int col = live[u] ? static_cast<int>(v % vpr) << 3 : 0;
+      off_out[u] = static_cast<size_t>(row) * ld_out + col;
+      rr[u] = make_uint4(0, 0, 0, 0);
+      if (live[u] && res != nullptr) rr[u] = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * ld_res + col);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      if (live[u]) {
+        const __nv_bfloat16* src0 = stage + static_cast<size_t>(row) * N + col;
+        for (int src = 0; src < world; ++src) {
+          const uint4 w = *reinterpret_cast<const uint4*>(src0 + src * chunk_elems);
+          const float2 a = unpack_bf16x2(w.x), b = unpack_bf16x2(w.y), c = unpack_bf16x2(w.z), d = unpack_bf16x2(w.w);
+          acc[u][0] += a.x; acc[u][1] += a.y; acc[u][2] += b.x; acc[u][3] += b.y;
+          acc[u][4] += c.x; acc[u][5] += c.y; acc[u][6] += d.x; acc[u][7] += d.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const float2 a = unpack_bf16x2(rr[u].x), b = unpack_bf16x2(rr[u].y), c = unpack_bf16x2(rr[u].z),
+                   d = unpack_bf16x2(rr[u].w);
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0] + a.x, acc[u][1] + a.y);
+      o.y = pack_bf16x2(acc[u][2] + b.x, acc[u][3] + b.y);
+      o.z = pack_bf16x2(acc[u][4] + c.x, acc[u][5] + c.y);
+      o.w = pack_bf16x2(acc[u][6] + d.x, acc[u][7] + d.y);
+      *reinterpret_cast<uint4*>(out + off_out[u]) = o;
+    }
+  }
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -588,6 +588,19 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         acc_phase ^= 1u;
       }
     }
+    if (COMM == COMM_REDUCE_SCATTER) {
+      // tiles done: join the reduction of this rank's row chunk (second share of the vectors)
+      const CommParams& c = p.comm;
+      bool ok = true;
+      for (int src = 0; src < c.world; ++src)
+        ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
+                               0xB8000000u | (src << 8) | c.rank) && ok;
+      if (!ok) *abort_flag = 1u;
+      constexpr int RED_THREADS = COMM_THREADS + 128;
+      rs_reduce_rows(c.peer_buf[c.rank], c.world, c.rows_per_rank, p.N, c.rs_res, c.rs_ld_res, c.rs_out, c.rs_ld_out,
+                     static_cast<size_t>(blockIdx.x) * RED_THREADS + COMM_THREADS + (threadIdx.x - 64),
+                     static_cast<size_t>(gridDim.x) * RED_THREADS);
+    }
   } else if (COMM == COMM_ALLGATHER) {
     // ------------------------------ all-gather push (warps 6-7) ------------------------------
     // Every CTA pushes its slice of the local shard into every rank's gathered buffer
@@ -636,34 +649,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
                              0xB7000000u | (src << 8) | c.rank) && ok;
     if (!ok) *abort_flag = 1u;
-    const __nv_bfloat16* stage = c.peer_buf[c.rank];
-    const int vpr = p.N >> 3;
-    const size_t total = static_cast<size_t>(c.rows_per_rank) * vpr;
-    const size_t chunk_elems = static_cast<size_t>(c.rows_per_rank) * p.N;
-    for (size_t v = static_cast<size_t>(blockIdx.x) * COMM_THREADS + ct; v < total;
-         v += static_cast<size_t>(gridDim.x) * COMM_THREADS) {
-      const int row = static_cast<int>(v / vpr);
-      const int col = static_cast<int>(v % vpr) << 3;
-      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int src = 0; src < c.world; ++src) {
-        const uint4 u = *reinterpret_cast<const uint4*>(stage + src * chunk_elems + static_cast<size_t>(row) * p.N + col);
-        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
-        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
-      }
-      if (c.rs_res != nullptr) {
-        const uint4 u = *reinterpret_cast<const uint4*>(c.rs_res + static_cast<size_t>(row) * c.rs_ld_res + col);
-        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += b.x; acc8[3] += b.y;
-        acc8[4] += cc.x; acc8[5] += cc.y; acc8[6] += d.x; acc8[7] += d.y;
-      }
-      uint4 o;
-      o.x = pack_bf16x2(acc8[0], acc8[1]);
-      o.y = pack_bf16x2(acc8[2], acc8[3]);
-      o.z = pack_bf16x2(acc8[4], acc8[5]);
-      o.w = pack_bf16x2(acc8[6], acc8[7]);
-      *reinterpret_cast<uint4*>(c.rs_out + static_cast<size_t>(row) * c.rs_ld_out + col) = o;
-    }
+    // these 64 threads take the first share of the vectors; the epilogue warps take the rest once
+    // their tiles are done (see the end of the epilogue loop)
+    constexpr int RED_THREADS = COMM_THREADS + 32 * epi_warps(COMM);
+    rs_reduce_rows(c.peer_buf[c.rank], c.world, c.rows_per_rank, p.N, c.rs_res, c.rs_ld_res, c.rs_out, c.rs_ld_out,
+                   static_cast<size_t>(blockIdx.x) * RED_THREADS + ct, static_cast<size_t>(gridDim.x) * RED_THREADS);
   }
 
   // nobody leaves while the partner may still touch this CTA's shared memory / barriers
