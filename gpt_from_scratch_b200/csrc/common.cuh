@@ -380,6 +380,48 @@ __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t ta
     }
   }
 }
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads);
+
+// First step of a fused all-gather -> GEMM: the calling threads (`nthreads` of this CTA, the caller
+// being number `tid`; all of them must call) copy this CTA's slice of the local shard into every
+// rank's gathered buffer (own rank first, then the peers in ring order) with 16-byte stores and,
+// per destination, bump that rank's counter for this source once the slice is written.
+// `bar_id` is a named barrier reserved for these threads.
+template <typename Comm>
+__device__ __forceinline__ void ag_push_rows(const Comm& c, int tid, int nthreads, int bar_id) {
+  const int rpc = (c.rows_per_rank + gridDim.x - 1) / gridDim.x;
+  const int r0 = min(c.rows_per_rank, static_cast<int>(blockIdx.x) * rpc);
+  const int r1 = min(c.rows_per_rank, r0 + rpc);
+  const int vpr = c.ag_cols >> 3;
+  const int nvec = (r1 - r0) * vpr;
+  for (int i = 0; i < c.world; ++i) {
+    const int peer = (c.rank + i) % c.world;
+    __nv_bfloat16* dst = c.peer_buf[peer] + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
+    for (int v = tid; v < nvec; v += nthreads * 4) {
+      uint4 tmp[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vv = v + u * nthreads;
+        if (vv < nvec) {
+          const int row = r0 + vv / vpr;
+          tmp[u] = *reinterpret_cast<const uint4*>(c.ag_src + static_cast<size_t>(row) * c.ag_ld + (vv % vpr) * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vv = v + u * nthreads;
+        if (vv < nvec) {
+          const int row = r0 + vv / vpr;
+          *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * c.ag_cols + (vv % vpr) * 8) = tmp[u];
+        }
+      }
+    }
+    __threadfence_system();
+    named_barrier_sync(bar_id, nthreads);
+    if (tid == 0) red_release_sys_add_u32(c.peer_flags[peer] + c.rank, 1u);
+  }
+}
+
 // Final step of a fused GEMM -> reduce-scatter: out[row, :] = sum over source ranks of the staged
 // bf16 partial rows (in rank order: deterministic) + optional residual, rounded once. `stage` is
 // this rank's staging area [world][rows][N]. The vectors (8 columns each) are dealt to

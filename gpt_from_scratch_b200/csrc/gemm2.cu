@@ -317,6 +317,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   } else if (warp < 2 + epi_warps(COMM)) {
     // ------------------------------ epilogue (both CTAs, own accumulator half) ------------------------------
     constexpr int EW = epi_warps(COMM);
+    // all-gather variant: until the first accumulator is ready these warps help the two push warps
+    if (COMM == COMM_ALLGATHER) ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - 64, COMM_THREADS + 128, 1);
     const int q = warp & 3;                               // TMEM lane quarter this warp may access
     const int c_begin = (EW == 8) ? ((warp - 2) >> 2) * (BN / 2) : 0;   // this warp's column range of the tile
     const int c_end = (EW == 8) ? c_begin + BN / 2 : BN;
@@ -605,39 +607,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     // ------------------------------ all-gather push (warps 6-7) ------------------------------
     // Every CTA pushes its slice of the local shard into every rank's gathered buffer
     // (own rank first), then bumps that rank's counter for this source.
-    const CommParams& c = p.comm;
-    const int ct = threadIdx.x - (threads2(COMM) - COMM_THREADS);
-    const int rpc = (c.rows_per_rank + gridDim.x - 1) / gridDim.x;
-    const int r0 = min(c.rows_per_rank, static_cast<int>(blockIdx.x) * rpc);
-    const int r1 = min(c.rows_per_rank, r0 + rpc);
-    const int vpr = c.ag_cols >> 3;
-    const int nvec = (r1 - r0) * vpr;
-    for (int i = 0; i < c.world; ++i) {
-      const int peer = (c.rank + i) % c.world;
-      __nv_bfloat16* dst = c.peer_buf[peer] + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
-      for (int v = ct; v < nvec; v += COMM_THREADS * 4) {
-        uint4 tmp[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int vv = v + u * COMM_THREADS;
-          if (vv < nvec) {
-            const int row = r0 + vv / vpr;
-            tmp[u] = *reinterpret_cast<const uint4*>(c.ag_src + static_cast<size_t>(row) * c.ag_ld + (vv % vpr) * 8);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int vv = v + u * COMM_THREADS;
-          if (vv < nvec) {
-            const int row = r0 + vv / vpr;
-            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * c.ag_cols + (vv % vpr) * 8) = tmp[u];
-          }
-        }
-      }
-      __threadfence_system();
-      named_barrier_sync(1, COMM_THREADS);
-      if (ct == 0) red_release_sys_add_u32(c.peer_flags[peer] + c.rank, 1u);
-    }
+    // (the epilogue warps push too, before their first tile: see the top of the epilogue branch)
+    ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - (threads2(COMM) - COMM_THREADS) + 128, COMM_THREADS + 128, 1);
   } else if (COMM == COMM_REDUCE_SCATTER) {
     // ------------------------------ reduce (warps 6-7) ------------------------------
     // Wait until every rank (this one included) has delivered all partial tiles of our row
