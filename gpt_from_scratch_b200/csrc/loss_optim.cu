@@ -138,20 +138,38 @@ __global__ void ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, const float* _
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
   if (v >= nvec) return;
   const int c = v << 3;
-  for (int row = blockIdx.y; row < M; row += gridDim.y) {
-    __nv_bfloat16* p = logits + static_cast<size_t>(row) * ld + c;
-    float f[8];
-    load8(p, f);
-    const float l = lse[row];
-    const float g = grad_rows[row];
-    const long long t = target[row] - v0;
+  // four rows per iteration, their loads issued together (each thread owns one 16-byte column
+  // group; a single row per thread leaves too little in flight to reach memory speed)
+  constexpr int U = 4;
+  for (int row0 = blockIdx.y * U; row0 < M; row0 += gridDim.y * U) {
+    uint4 raw[U];
+    float l[U], g[U];
+    long long t[U];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float sm = __expf(f[e] - l);
-      if (t == c + e) sm -= 1.f;
-      f[e] = sm * g;
+    for (int u = 0; u < U; ++u) {
+      const int row = row0 + u;
+      if (row < M) {
+        raw[u] = *reinterpret_cast<const uint4*>(logits + static_cast<size_t>(row) * ld + c);
+        l[u] = lse[row];
+        g[u] = grad_rows[row];
+        t[u] = target[row] - v0;
+      }
     }
-    store8(p, f);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int row = row0 + u;
+      if (row >= M) break;
+      const float2 a0 = unpack_bf16x2(raw[u].x), a1 = unpack_bf16x2(raw[u].y), a2 = unpack_bf16x2(raw[u].z),
+                   a3 = unpack_bf16x2(raw[u].w);
+      float f[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float sm = __expf(f[e] - l[u]);
+        if (t[u] == c + e) sm -= 1.f;
+        f[e] = sm * g[u];
+      }
+      store8(logits + static_cast<size_t>(row) * ld + c, f);
+    }
   }
 }
 
@@ -327,7 +345,7 @@ int gfs_ce_bwd(void* logits, const void* lse, const void* target, const void* gr
                int v0, void* stream) {
   if ((Vp & 7) || (ld & 7)) return -1;
   if (M == 0 || Vp == 0) return 0;
-  const dim3 grid(((Vp >> 3) + 255) / 256, std::min(M, 32768));
+  const dim3 grid(((Vp >> 3) + 255) / 256, std::min((M + 3) / 4, 1024));
   ce_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(logits), static_cast<const float*>(lse), static_cast<const long long*>(target),
       static_cast<const float*>(grad_rows), M, Vp, ld, v0);
