@@ -55,8 +55,9 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_BYTES = 8 * 4096;     // one [32 rows x 128 B] transpose buffer per epilogue warp
 // Epilogue warps per CTA: 8 in the plain kernel (two per TMEM lane quarter, each taking half of the
 // tile's columns, so epilogues with real work per element still hide behind the next tile's
-// MMAs); 4 in the fused-collective variants, whose two extra warps need the registers.
-__host__ __device__ constexpr int epi_warps(int comm) { return comm == 0 ? 8 : 4; }
+// MMAs), also in the all-gather variant (its two push warps are cheap: 384 threads at up to 170
+// registers); 4 in the reduce-scatter variant, whose reduction warps need the registers.
+__host__ __device__ constexpr int epi_warps(int comm) { return comm == 2 ? 4 : 8; }
 __host__ __device__ constexpr int threads2(int comm) { return 64 + 32 * epi_warps(comm) + (comm != 0 ? 64 : 0); }
 constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 256 + 1024;
 
@@ -318,7 +319,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     // ------------------------------ epilogue (both CTAs, own accumulator half) ------------------------------
     constexpr int EW = epi_warps(COMM);
     // all-gather variant: until the first accumulator is ready these warps help the two push warps
-    if (COMM == COMM_ALLGATHER) ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - 64, COMM_THREADS + 128, 1);
+    if (COMM == COMM_ALLGATHER) ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - 64, COMM_THREADS + 32 * EW, 1);
     const int q = warp & 3;                               // TMEM lane quarter this warp may access
     const int c_begin = (EW == 8) ? ((warp - 2) >> 2) * (BN / 2) : 0;   // this warp's column range of the tile
     const int c_end = (EW == 8) ? c_begin + BN / 2 : BN;
@@ -575,7 +576,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       if (SWI == 3) {
         const int row = m0 + q * 32 + lane;
         const int part = (n0 / BN) * 2 + ((EW == 8) ? ((warp - 2) >> 2) : 0);
-        if (row < p.M) p.ce_partials[static_cast<size_t>(part) * p.M + row] = make_float2(ce_m, ce_s);
+        if (row < p.M) {
+          p.ce_partials[static_cast<size_t>(part) * p.M + row] = make_float2(ce_m, ce_s);
+          // with four epilogue warps a warp covers all 256 columns: the tile's second slot is empty
+          if (EW != 8) p.ce_partials[static_cast<size_t>(part + 1) * p.M + row] = make_float2(-INFINITY, 0.f);
+        }
       }
       }
       tc_fence_before();
@@ -598,7 +603,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         ok = wait_flag_reached(c.peer_flags[c.rank] + src, c.target, c.wait_ns, p.status,
                                0xB8000000u | (src << 8) | c.rank) && ok;
       if (!ok) *abort_flag = 1u;
-      constexpr int RED_THREADS = COMM_THREADS + 128;
+      constexpr int RED_THREADS = COMM_THREADS + 32 * EW;
       rs_reduce_rows(c.peer_buf[c.rank], c.world, c.rows_per_rank, p.N, c.rs_res, c.rs_ld_res, c.rs_out, c.rs_ld_out,
                      static_cast<size_t>(blockIdx.x) * RED_THREADS + COMM_THREADS + (threadIdx.x - 64),
                      static_cast<size_t>(gridDim.x) * RED_THREADS);
@@ -608,7 +613,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     // Every CTA pushes its slice of the local shard into every rank's gathered buffer
     // (own rank first), then bumps that rank's counter for this source.
     // (the epilogue warps push too, before their first tile: see the top of the epilogue branch)
-    ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - (threads2(COMM) - COMM_THREADS) + 128, COMM_THREADS + 128, 1);
+    ag_push_rows(p.comm, static_cast<int>(threadIdx.x) - (threads2(COMM) - COMM_THREADS) + 32 * epi_warps(COMM),
+                 COMM_THREADS + 32 * epi_warps(COMM), 1);
   } else if (COMM == COMM_REDUCE_SCATTER) {
     // ------------------------------ reduce (warps 6-7) ------------------------------
     // Wait until every rank (this one included) has delivered all partial tiles of our row
@@ -1007,13 +1013,14 @@ int gfs_gemm2_bf16_swiglu(int mode, const void* a, const void* b, void* c, void*
 // extra requirement that M/world is a multiple of 256. Returns -20 when the problem does not
 // qualify, in which case the caller uses the single-CTA kernel (nothing has been launched and
 // *target_inout is unchanged).
-int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
-                        const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
-                        const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
-                        unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
-                        int rope_d, int rope_b, long long wait_ns, void* stream_) {
+static int gemm2_comm_impl(int mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
+                           const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
+                           const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
+                           unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
+                           int rope_d, int rope_b, long long wait_ns, void* ce_partials, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (mode != COMM_ALLGATHER && mode != COMM_REDUCE_SCATTER) return -1;
+  if (ce_partials != nullptr && (mode != COMM_ALLGATHER || b_mn_major || rope_cos != nullptr)) return -1;
   if (world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return -1;
   if (M <= 0 || N <= 0 || K <= 0 || (M % world) != 0) return -1;
   if (((M / world) % 256) != 0 || N < 256 || K < 256) return -20;
@@ -1066,11 +1073,39 @@ int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb
   if (ta == nullptr || tb == nullptr) return -3;
   *target_inout += increment;
   c.target = *target_inout;
+  if (ce_partials != nullptr) {
+    p.ce_partials = static_cast<float2*>(ce_partials);
+    return launch2<false, false, COMM_ALLGATHER, 3>(ta, tb, p, grid, stream);
+  }
   if (mode == COMM_ALLGATHER)
     return b_mn_major ? launch2<false, true, COMM_ALLGATHER>(ta, tb, p, grid, stream)
                       : launch2<false, false, COMM_ALLGATHER>(ta, tb, p, grid, stream);
   return b_mn_major ? launch2<false, true, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream)
                     : launch2<false, false, COMM_REDUCE_SCATTER>(ta, tb, p, grid, stream);
+}
+
+int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
+                        const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
+                        const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
+                        unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
+                        int rope_d, int rope_b, long long wait_ns, void* stream_) {
+  return gemm2_comm_impl(mode, a, lda, B, ldb, out, ldo, residual, ldr, M, N, K, b_mn_major, world, rank, peer_bufs,
+                         peer_flags, target_inout, rope_cos, rope_sin, rope_cols, rope_d, rope_b, wait_ns, nullptr,
+                         stream_);
+}
+
+// Vocabulary-parallel LM head under sequence parallelism: the all-gather GEMM
+// (logits[M, N] = gather(a)[M, K] @ B[N, K]^T, B K-major) whose epilogue also writes the
+// cross-entropy statistics of gfs_gemm2_bf16_ce: partials is float2 [gfs_gemm2_ce_parts(N)][M]
+// (the second slot of every 256-column tile holds the empty pair (-inf, 0): four epilogue warps
+// per CTA here, each covering the tile's full width). Returns -20 like gfs_gemm2_bf16_comm.
+int gfs_gemm2_bf16_allgather_ce(const void* a, int lda, const void* B, int ldb, void* out, int ldo, void* partials,
+                                int M, int N, int K, int world, int rank, const unsigned long long* peer_bufs,
+                                const unsigned long long* peer_flags, unsigned int* target_inout, long long wait_ns,
+                                void* stream_) {
+  if (partials == nullptr || (reinterpret_cast<uintptr_t>(partials) & 15)) return -2;
+  return gemm2_comm_impl(COMM_ALLGATHER, a, lda, B, ldb, out, ldo, nullptr, 0, M, N, K, 0, world, rank, peer_bufs,
+                         peer_flags, target_inout, nullptr, nullptr, 0, 0, 1, wait_ns, partials, stream_);
 }
 
 // Grouped weight gradients: for g < n, C_g[M_g, N_g] (+)= A_g^T B_g with A_g = [K_g, M_g] (pitch lda_g),

@@ -84,20 +84,44 @@ ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restr
 
 // Same outputs as ce_fwd_kernel, from per-slice statistics that the LM-head GEMM epilogue already
 // produced (partials: float2 {max, sum exp(x - max)} [parts][M]); only the target logit is read
-// from the logits. One thread per row; consecutive threads read consecutive float2.
-__global__ void ce_from_partials_kernel(const float2* __restrict__ partials, const __nv_bfloat16* __restrict__ logits,
-                                        const long long* __restrict__ target, float* __restrict__ stats,
-                                        float* __restrict__ lse, float* __restrict__ loss, int parts, int M, int Vp,
-                                        long ld, int v0, int single_rank) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= M) return;
+// from the logits. A block owns 32 consecutive rows (lane = row, so a warp reads 256 contiguous
+// bytes per slice); its CE_PW warps split the slices and keep four loads in flight each, then one
+// warp merges the per-warp results in a fixed order. (One thread per row walking all slices was a
+// chain of dependent loads: ~100 us at 8192 rows x 198 slices for 13 MB of input.)
+constexpr int CE_PW = 8;
+__device__ __forceinline__ void ce_merge(float& gm, float& gs, float2 ms) {
+  const float nm = fmaxf(gm, ms.x);
+  if (nm != -INFINITY) gs = gs * __expf(gm - nm) + ms.y * __expf(ms.x - nm);
+  gm = nm;
+}
+__global__ void __launch_bounds__(32 * CE_PW)
+ce_from_partials_kernel(const float2* __restrict__ partials, const __nv_bfloat16* __restrict__ logits,
+                        const long long* __restrict__ target, float* __restrict__ stats, float* __restrict__ lse,
+                        float* __restrict__ loss, int parts, int M, int Vp, long ld, int v0, int single_rank) {
+  __shared__ float2 part_res[CE_PW][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * 32 + lane;
   float gm = -INFINITY, gs = 0.f;
-  for (int i = 0; i < parts; ++i) {
-    const float2 ms = partials[static_cast<size_t>(i) * M + row];
-    const float nm = fmaxf(gm, ms.x);
-    if (nm != -INFINITY) gs = gs * __expf(gm - nm) + ms.y * __expf(ms.x - nm);
-    gm = nm;
+  if (row < M) {
+    const float2 empty = make_float2(-INFINITY, 0.f);
+    for (int i = warp; i < parts; i += 4 * CE_PW) {
+      float2 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int pi = i + u * CE_PW;
+        v[u] = (pi < parts) ? partials[static_cast<size_t>(pi) * M + row] : empty;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ce_merge(gm, gs, v[u]);
+    }
   }
+  part_res[warp][lane] = make_float2(gm, gs);
+  __syncthreads();
+  if (warp != 0 || row >= M) return;
+  gm = -INFINITY;
+  gs = 0.f;
+#pragma unroll
+  for (int w = 0; w < CE_PW; ++w) ce_merge(gm, gs, part_res[w][lane]);
   const long long t = target[row];
   float tz = 0.f;
   if (t >= v0 && t < v0 + Vp) tz = __bfloat162float(logits[static_cast<size_t>(row) * ld + (t - v0)]);
@@ -327,7 +351,7 @@ int gfs_ce_fwd(const void* logits, const void* target, void* stats, void* lse, v
 int gfs_ce_from_partials(const void* partials, const void* logits, const void* target, void* stats, void* lse,
                          void* loss, int parts, int M, int Vp, long ld, int v0, int single_rank, void* stream) {
   if (M == 0) return 0;
-  ce_from_partials_kernel<<<(M + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  ce_from_partials_kernel<<<(M + 31) / 32, 32 * CE_PW, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float2*>(partials), static_cast<const __nv_bfloat16*>(logits),
       static_cast<const long long*>(target), static_cast<float*>(stats), static_cast<float*>(lse),
       static_cast<float*>(loss), parts, M, Vp, ld, v0, single_rank);

@@ -112,6 +112,24 @@ def main() -> None:
         bench_ag("all-gather -> GEMM   QKV      ", 3 * H, H)
         bench_ag("all-gather -> GEMM   gate_up  ", 2 * I, H)
         bench_ag("all-gather -> GEMM   LM head  ", V, H)
+        # LM head + local cross-entropy statistics: statistics in the all-gather GEMM's epilogue vs
+        # the plain fused all-gather GEMM followed by one pass over the logits ("nccl us" column)
+        from .ops import cross_entropy as ce_ops
+        x_lm, w_lm = rnd(Ms // B, B, H), rnd(V // world, H)
+        tgt = torch.randint(0, V, (M,), device=dev, generator=torch.Generator(device="cuda").manual_seed(9))
+        v0 = rank * (V // world)
+        ps.set_comm_impl("fused")
+
+        def lm_epilogue_stats():
+            out = fused_comm.allgather_linear(x_lm, w_lm, ce_stats=True)
+            return ce_ops.ce_stats_from_partials(out._gfs_ce_partials, out.view(M, -1), tgt, v0, False)
+
+        def lm_then_pass():
+            out = fused_comm.allgather_linear(x_lm, w_lm)
+            return ce_ops.ce_local_stats(out.view(M, -1), tgt, v0, False)
+        t_f, t_n = timed(lm_epilogue_stats), timed(lm_then_pass)
+        rows.append(("AG -> GEMM LM head + CE stats (vs + pass)", t_f, t_n, 2.0 * M * (V // world) * H,
+                     (M - Ms) * H * 2))
         bench_rs("GEMM -> reduce-scatter out_proj (+res)", H, H)
         bench_rs("GEMM -> reduce-scatter down     (+res)", H, I)
         # embedding lookup -> reduce-scatter

@@ -152,6 +152,10 @@ def build_cases(dev, small: bool):
     stats, lse_ce, _ = ce_ops.ce_local_stats(logits, tgt, 0, True)
     grows = torch.full((M,), 1.0 / M, device=dev)
     cases.append(("ce_fwd", lambda: ce_ops.ce_local_stats(logits, tgt, 0, True), 0, 2 * M * V))
+    n_parts = 2 * ((V + 255) // 256)
+    ce_parts = torch.randn(n_parts, M, 2, device=dev).abs_()
+    cases.append(("ce_from_gemm_partials", lambda: ce_ops.ce_stats_from_partials(ce_parts, logits, tgt, 0, True), 0,
+                  8 * n_parts * M))
     cases.append(("ce_bwd_inplace", lambda: ce_ops.ce_backward_inplace(logits, lse_ce, tgt, grows, 0), 0, 4 * M * V))
     n = 124_475_904 if not small else 8 * 1024 * 1024   # parameter count of the GPT-124M shape (vocab 50304)
     grad = rnd(n)

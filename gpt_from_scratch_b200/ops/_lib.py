@@ -90,6 +90,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_gemm2_wgrad_grouped": ([i, ulp, ulp, ulp, ip, ip, ip, ip, ip, ip, ip, vp], i),
         "gfs_gemm2_bf16_comm": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i, ulp, ulp, uip, vp, vp, i, i, i,
                                  ctypes.c_longlong, vp], i),
+        "gfs_gemm2_bf16_allgather_ce": ([vp, i, vp, i, vp, i, vp, i, i, i, i, i, ulp, ulp, uip, ctypes.c_longlong,
+                                         vp], i),
         "gfs_symm_barrier": ([ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_allgather": ([vp, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_embedding_scatter": ([vp, vp, i, i, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),

@@ -73,6 +73,26 @@ def _gemm_comm_launch(mode, a, b, out, residual, M, N, K, b_mn_major, grp, buf, 
     _lib.check(rc, "gfs_gemm_bf16_comm")
 
 
+_next_weight_key = 0
+
+
+def _weight_site_key(weight: torch.Tensor) -> int:
+    """Key of the gathered-input buffer and flag slots that belong to ``weight``'s call site.
+
+    Symmetric allocation is collective, so every rank must derive the same sequence of keys: the
+    key is a counter assigned at the weight's first use (ranks run the same program, so the
+    counters agree) and stored on the tensor object. ``id(weight)`` would not do: a freed
+    tensor's id can be handed to a new tensor on one rank and not on another, and the ranks
+    would then disagree on whether a buffer has to be created."""
+    global _next_weight_key
+    key = getattr(weight, "_gfs_site_key", None)
+    if key is None:
+        key = _next_weight_key
+        _next_weight_key += 1
+        weight._gfs_site_key = key
+    return key
+
+
 def _as2d(t: torch.Tensor, cols: int) -> torch.Tensor:
     t2 = t.reshape(-1, cols)
     if not t2.is_contiguous() or t2.data_ptr() % 16:
@@ -85,9 +105,31 @@ def supported(rows_per_rank: int, *dims: int) -> bool:
 
 
 # --------------------------------------------------------------------------- column parallel
+def _allgather_gemm_ce(x2, weight, out, M, N, K, grp, gathered, site):
+    """LM head: all-gather GEMM on CTA pairs whose epilogue also emits the cross-entropy statistics
+    of every 128-column slice (``[parts, M, 2]`` fp32). ``None`` when the problem does not qualify
+    for the CTA-pair kernel (nothing launched)."""
+    if not (gemm_ops._CE_EPILOGUE and gemm_ops._PAIR_ENABLED and
+            (M // 256) * ((N + 255) // 256) >= gemm_ops._PAIR_MIN_TILES and weight.stride(1) == 1):
+        return None
+    parts = _lib.lib().gfs_gemm2_ce_parts(N)
+    partials = torch.empty((parts, M, 2), dtype=torch.float32, device=x2.device)
+    with _lib.nvtx("fused:allgather_gemm_ce_stats"):
+        rc = _lib.lib().gfs_gemm2_bf16_allgather_ce(
+            x2.data_ptr(), x2.stride(0), weight.data_ptr(), weight.stride(0), out.data_ptr(), out.stride(0),
+            partials.data_ptr(), M, N, K, grp.world, grp.rank, gathered.ptrs, _site_flag_ptrs(grp, site),
+            ctypes.byref(site.target), WAIT_NS, _lib.stream_ptr())
+    if rc == -20:
+        return None
+    _lib.check(rc, "gfs_gemm2_bf16_allgather_ce")
+    return partials
+
+
 class _AllGatherLinear(torch.autograd.Function):
+    last_ce_partials = None   # statistics produced by the most recent forward with ce_stats=True
+
     @staticmethod
-    def forward(ctx, x_shard, weight, sink, rope, site_key):
+    def forward(ctx, x_shard, weight, sink, rope, site_key, ce_stats=False):
         grp = symm.get_group("tp")
         K = x_shard.shape[-1]
         N = weight.shape[0]
@@ -97,7 +139,12 @@ class _AllGatherLinear(torch.autograd.Function):
         gathered = grp.alloc(("ag", site_key), M * K, torch.bfloat16)     # lives until backward
         site = grp.site(("ag", site_key))
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
-        _gemm_comm(MODE_AG, x2, weight, out, None, M, N, K, False, grp, gathered, site, rope)
+        partials = None
+        if ce_stats and rope is None:
+            partials = _allgather_gemm_ce(x2, weight, out, M, N, K, grp, gathered, site)
+        _AllGatherLinear.last_ce_partials = partials
+        if partials is None:
+            _gemm_comm(MODE_AG, x2, weight, out, None, M, N, K, False, grp, gathered, site, rope)
         ctx.save_for_backward(weight)
         ctx.gathered = gathered
         ctx.sink = sink
@@ -122,18 +169,28 @@ class _AllGatherLinear(torch.autograd.Function):
             sink.done()
         else:
             dw = gemm_ops.linear_wgrad(dy2, x_full)
-        return dx.view(in_shape), dw, None, None, None
+        return dx.view(in_shape), dw, None, None, None, None
 
 
-def allgather_linear(x_shard: torch.Tensor, weight: torch.Tensor, rope=None) -> torch.Tensor:
-    """``gather_S(x_shard) @ weight^T`` with the all-gather done by the GEMM kernel."""
+def allgather_linear(x_shard: torch.Tensor, weight: torch.Tensor, rope=None, ce_stats: bool = False) -> torch.Tensor:
+    """``gather_S(x_shard) @ weight^T`` with the all-gather done by the GEMM kernel.
+
+    ``ce_stats``: the output is the LM head's logits; when the CTA-pair kernel serves the problem
+    its epilogue also produces the per-row softmax statistics, attached to the returned tensor as
+    ``_gfs_ce_partials`` (the vocabulary-parallel cross entropy then makes no pass over the logits
+    in the forward)."""
     world = ps.get_tensor_model_parallel_world_size()
     rows = x_shard.numel() // x_shard.shape[-1]
     if not (x_shard.dtype == weight.dtype == torch.bfloat16 and supported(rows, x_shard.shape[-1], weight.shape[0])):
         from . import mappings
         from .layers import linear_with_sink
-        return linear_with_sink(mappings.gather_from_sequence_parallel_region(x_shard), weight, rope=rope)
-    return _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, id(weight))
+        return linear_with_sink(mappings.gather_from_sequence_parallel_region(x_shard), weight, rope=rope,
+                                ce_stats=ce_stats)
+    out = _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, _weight_site_key(weight), ce_stats)
+    if ce_stats and _AllGatherLinear.last_ce_partials is not None:
+        out._gfs_ce_partials = _AllGatherLinear.last_ce_partials
+        _AllGatherLinear.last_ce_partials = None
+    return out
 
 
 # --------------------------------------------------------------------------- row parallel

@@ -142,7 +142,8 @@ class ColumnParallelLinear(nn.Module):
         world = ps.get_tensor_model_parallel_world_size()
         if world > 1 and ps.get_comm_impl() == "fused" and input_.is_cuda:
             from . import fused_comm
-            out = fused_comm.allgather_linear(input_, self.weight, rope=rope)
+            out = fused_comm.allgather_linear(input_, self.weight, rope=rope,
+                                              ce_stats=ce_stats and self.bias is None)
         else:
             full = mappings.gather_from_sequence_parallel_region(input_)
             out = linear_with_sink(full, self.weight, rope=rope, ce_stats=ce_stats and self.bias is None)

@@ -86,6 +86,31 @@ def main():
                 assert torch.equal(ra.grad, dout)
         log("linear_reduce_scatter ok")
 
+        # ---- LM head: all-gather -> GEMM with the cross-entropy statistics in its epilogue ----
+        if pair_min is not None:
+            Vp = 392                        # ragged last tile: 136 valid columns of 256
+            wl = (torch.randn(Vp, K, device=dev, generator=g) * 0.3).bfloat16()
+            tg = torch.randint(0, Vp * world, (S, B), device=dev,
+                               generator=torch.Generator(device="cuda").manual_seed(8))
+            prev_impl = ps.get_comm_impl()
+            ps.set_comm_impl("fused")
+            xa, wa = x.clone().requires_grad_(), wl.clone().requires_grad_()
+            la = fused_comm.allgather_linear(xa, wa, ce_stats=True)
+            assert getattr(la, "_gfs_ce_partials", None) is not None, "LM-head epilogue statistics missing"
+            loss_a = vocab_parallel_cross_entropy(la, tg)
+            loss_a.mean().backward()
+            ps.set_comm_impl("nccl")
+            xb, wb = x.clone().requires_grad_(), wl.clone().requires_grad_()
+            lb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
+            loss_b = vocab_parallel_cross_entropy(lb, tg)
+            loss_b.mean().backward()
+            torch.cuda.synchronize()
+            ps.set_comm_impl(prev_impl)
+            assert (loss_a - loss_b).abs().max().item() < 2e-3, (loss_a - loss_b).abs().max().item()
+            close(xa.grad, xb.grad, "LM head dX")
+            close(wa.grad, wb.grad, "LM head dW", 2e-3)
+            log("allgather_linear + cross-entropy statistics ok")
+
         gemm_ops._PAIR_MIN_TILES = saved_min
     S, B = 128 * world * 2, 2
     Ss = S // world
