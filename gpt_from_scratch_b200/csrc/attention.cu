@@ -24,6 +24,7 @@
 //
 // Reference counterparts: core/myFlashAttn.py:460-728 (_attn_fwd), :740-790 (pre-pass),
 // :805-1066 (_attn_bwd_LoopQ), :1079-1317 (_attn_bwd_LoopKV).
+#include <cstdlib>
 #include <algorithm>
 #include <type_traits>
 
@@ -45,6 +46,13 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 // causal / sequence-end mask: 0 = every element alive, 1 = mixed, 2 = every element dead.
 // KEY_ROWS: rows are key positions and columns are query positions (dead when col < row);
 // otherwise rows are queries and columns are keys (dead when col > row). Warp-uniform.
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool KEY_ROWS>
 __device__ __forceinline__ int mask_class(int row_min, int row_max, int col_min, int col_max, bool causal, int S) {
   if (col_min >= S) return 2;
@@ -427,6 +435,14 @@ constexpr int FWD64_SMEM = 2 * 16384 + FWD64_KS * 32768 + 256;
 // first, so barrier set-up, the TMEM allocation and the CTA launch gap are paid once per SM
 // instead of once per item (at sequence length 1024 they were ~45 % of the kernel's time).
 // All barrier parities therefore run on counters that continue across items.
+//
+// OTMEM: the output accumulates in tensor memory (P V issued with accumulate) instead of being
+// folded into registers after every key block, and the running maximum is only raised when it
+// grows by more than 2^8 (any consistent offset gives the same softmax; the stale one keeps
+// exp2 arguments <= 8). Raising it rescales the accumulator in tensor memory, which after the
+// first blocks is rare. This frees the 64 accumulator registers per thread, so a block's 128
+// scores are loaded once and stay in registers for both the maximum and the exponentials.
+template <bool OTMEM>
 __global__ void __launch_bounds__(FWD64_THREADS, 1)
 flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const FwdParams p, int n_pairs, int n_items) {
@@ -543,6 +559,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       int g0 = 0;            // ring position of this item's first key block
       int cx[2] = {0, 0};    // blocks processed so far per query tile (barrier phase counters)
+      int it[2] = {0, 0};    // OTMEM: items in which the tile had blocks (phase of o_empty)
       for (int rnd = 0; rnd * G < n_items; ++rnd) {
         const int w = snake(rnd);
         if (w >= n_items) break;
@@ -566,27 +583,73 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         if (n_x[1] > 0) issue_s(1, 0);
         if (n_kv > 0) umma_commit_e(&k_empty[g0 % KS]);
         if (n_kv == 1) umma_commit_e(q_empty);
-        for (int j = 0; j < n_kv; ++j) {
-          const int g = g0 + j;
+        // The two query tiles are served in the order in which their probabilities become ready
+        // (not in lockstep): a tile that waits for its next S leaves the schedulers to the other
+        // tile's softmax. A tile may lead the other by one key block at most, which the K/V ring
+        // (three stages, released when both tiles have used a block) always allows.
+        int s_iss[2] = {n_x[0] > 0 ? 1 : 0, n_x[1] > 0 ? 1 : 0};   // S MMAs issued per tile
+        int pv_iss[2] = {0, 0};                                     // P V MMAs issued per tile
+        uint32_t spins = 0;
+        uint64_t spin_t0 = 0;
+        bool dead = false;
+        while ((pv_iss[0] < n_x[0] || pv_iss[1] < n_x[1]) && !dead) {
+          bool progressed = false;
+#pragma unroll
           for (int x = 0; x < 2; ++x) {
+            const int j = pv_iss[x];
+            const int ot = x ^ 1;
             if (j >= n_x[x]) continue;
+            if (pv_iss[ot] < n_x[ot] && j > pv_iss[ot] + 1) continue;   // bounded lead
             const int c = cx[x] + j;
-            mbar_wait(&p_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);   // S_x(j) consumed, P_x(j) in TMEM
-            if (j + 1 < n_x[x]) issue_s(x, j + 1);
+            if (!mbar_try_wait(&p_full[x], c & 1)) continue;             // S_x(j) consumed, P_x(j) in TMEM
+            progressed = true;
+            const int g = g0 + j;
+            if (j + 1 < n_x[x]) {
+              issue_s(x, j + 1);
+              s_iss[x] = j + 2;
+              // the K block is free once both tiles' S MMAs on it have been issued
+              if (s_iss[ot] > j + 1 || j + 1 >= n_x[ot]) umma_commit_e(&k_empty[(g + 1) % KS]);
+              if (s_iss[0] >= n_x[0] && s_iss[1] >= n_x[1]) umma_commit_e(q_empty);   // the item's last S
+            }
             mbar_wait(&v_full[g % KS], (g / KS) & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
-            mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+            if (OTMEM) {
+              // the accumulator is overwritten once per item: wait until the softmax warps have
+              // read the previous item's result out of it
+              if (j == 0) mbar_wait(&o_empty[x], (it[x] & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+            } else {
+              mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+            }
             tc_fence_after();
             mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384), 0,
-                       idesc_o, false);
+                       idesc_o, OTMEM && j > 0);
             umma_commit_e(&o_full[x]);
+            pv_iss[x] = j + 1;
+            if (pv_iss[ot] > j || j >= n_x[ot]) umma_commit_e(&v_empty[g % KS]);
           }
-          if (j + 1 < n_kv) umma_commit_e(&k_empty[(g + 1) % KS]);  // both tiles' S(j+1) have been issued
-          if (j + 2 == n_kv) umma_commit_e(q_empty);                // the item's last S MMAs are issued
-          umma_commit_e(&v_empty[g % KS]);
+          if (progressed) {
+            spins = 0;
+            spin_t0 = 0;
+          } else if (((++spins) & 0xfffu) == 0u) {
+            // bounded like mbar_wait: give up (status recorded) when nothing becomes ready in time
+            if (*abort_flag) {
+              dead = true;
+            } else {
+              const uint64_t now = globaltimer_ns();
+              if (spin_t0 == 0) {
+                spin_t0 = now;
+              } else if (now - spin_t0 > GFS_WAIT_LIMIT_NS) {
+                *abort_flag = 1u;
+                record_status(p.status, STATUS_TIMEOUT_SOFTMAX, (blockIdx.x << 8) | 0xE1u);
+                dead = true;
+              }
+            }
+          }
         }
         g0 += n_kv;
         cx[0] += n_x[0];
         cx[1] += n_x[1];
+        it[0] += n_x[0] > 0;
+        it[1] += n_x[1] > 0;
       }
     }
   } else {
@@ -599,6 +662,177 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const uint32_t p_addr = tmem_base + lane_base + P_COL + x * 64;
     const float sl2 = p.scale * LOG2E_F;
     int cdone = 0;  // blocks of this tile processed in earlier items
+    if constexpr (OTMEM) {
+      for (int rnd = 0; rnd * G < n_items; ++rnd) {
+        const int w = snake(rnd);
+        if (w >= n_items) break;
+        int qp, bh, na, nbk;
+        decode(w, qp, bh, na, nbk);
+        const int b = bh / p.nh, h = bh % p.nh;
+        const int qtx = 2 * qp + x;
+        const int row_g = qtx * 128 + r;
+        const int n_mine = x == 0 ? na : nbk;
+        const int row_lo = qtx * 128 + quarter * 32;
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_mine; ++j) {
+          const int c = cdone + j;
+          const bool need_mask = (p.causal && j == qtx) || ((j + 1) * 128 > p.S);
+          auto kind_of = [&](int cc) {
+            return need_mask
+                       ? mask_class<false>(row_lo, row_lo + 31, j * 128 + cc, j * 128 + cc + 31, p.causal != 0, p.S)
+                       : 0;
+          };
+          mbar_wait(&s_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+          tc_fence_after();
+          uint32_t v0[32], v1[32], v2[32], v3[32];
+          tmem_ld_32x32(s_addr + 0, v0);
+          tmem_ld_32x32(s_addr + 32, v1);
+          tmem_ld_32x32(s_addr + 64, v2);
+          tmem_ld_32x32(s_addr + 96, v3);
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+          auto max_chunk = [&](const uint32_t (&v)[32], int cc) {
+            const int kind = kind_of(cc);
+            if (kind == 2) return;
+            if (kind == 1) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int col_g = j * 128 + cc + e;
+                const bool dead = (p.causal && col_g > row_g) || col_g >= p.S;
+                mx0 = fmaxf(mx0, dead ? -INFINITY : __uint_as_float(v[e]));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; e += 4) {
+                mx0 = fmax3(mx0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                mx1 = fmax3(mx1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+              }
+            }
+          };
+          tmem_ld_wait_for(v0);
+          max_chunk(v0, 0);
+          tmem_ld_wait_for(v1);
+          max_chunk(v1, 32);
+          tmem_ld_wait_for(v2);
+          max_chunk(v2, 64);
+          tmem_ld_wait_for(v3);
+          max_chunk(v3, 96);
+          const float m_new = fmaxf(m, fmaxf(mx0, mx1));
+          // raise the running maximum only when it grew by more than 2^8 (or was still -inf)
+          bool grow = false;
+          float alpha = 1.f;
+          if (m_new > m && (m == -INFINITY || (m_new - m) * sl2 > 8.f)) {
+            grow = true;
+            alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * sl2);
+          }
+          if (j > 0 && __any_sync(0xffffffffu, grow)) {
+            // rescale this warp's 32 accumulator rows in tensor memory (warp-collective accesses;
+            // rows whose maximum stays get factor 1). P V of the previous block must be done.
+            mbar_wait(&o_full[x], (c - 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+            tc_fence_after();
+            const float a = grow ? alpha : 1.f;
+#pragma unroll 1
+            for (int cc = 0; cc < D; cc += 16) {
+              uint32_t wv[16];
+              tmem_ld_32x16(o_addr + cc, wv);
+              tmem_ld_wait_for16(wv);
+#pragma unroll
+              for (int e = 0; e < 16; ++e) wv[e] = __float_as_uint(__uint_as_float(wv[e]) * a);
+              tmem_st_32x16(o_addr + cc, wv);
+            }
+            tmem_st_wait();
+          }
+          if (grow) {
+            l *= alpha;
+            m = m_new;
+          }
+          const float moff = ((m == -INFINITY) ? 0.f : m) * sl2;
+          float rs0 = 0.f, rs1 = 0.f;
+          auto prob_chunk_impl = [&](auto mask_tag, const uint32_t (&v)[32], int cc, uint32_t (&packed)[16]) {
+            constexpr bool MASKED = decltype(mask_tag)::value;
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
+              float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
+              if constexpr (MASKED) {
+                const int col_g = j * 128 + cc + e;
+                const bool dead0 = (p.causal && col_g > row_g) || col_g >= p.S;
+                const bool dead1 = (p.causal && col_g + 1 > row_g) || col_g + 1 >= p.S;
+                x0 = dead0 ? 0.f : x0;
+                x1 = dead1 ? 0.f : x1;
+              }
+              rs0 += x0;
+              rs1 += x1;
+              packed[e >> 1] = pack_bf16x2(x0, x1);
+            }
+          };
+          auto prob_chunk = [&](const uint32_t (&v)[32], int cc, uint32_t (&packed)[16]) {
+            const int kind = kind_of(cc);
+            if (kind == 2) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) packed[e] = 0u;
+            } else if (kind == 1) {
+              prob_chunk_impl(std::true_type{}, v, cc, packed);
+            } else {
+              prob_chunk_impl(std::false_type{}, v, cc, packed);
+            }
+          };
+          uint32_t p0[16], p1[16], p2[16], p3[16];
+          prob_chunk(v0, 0, p0);
+          prob_chunk(v1, 32, p1);
+          prob_chunk(v2, 64, p2);
+          prob_chunk(v3, 96, p3);
+          l += rs0 + rs1;
+          // P of the previous block is read by its P V MMA: overwrite it only when that is done
+          if (j > 0) {
+            mbar_wait(&o_full[x], (c - 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+            tc_fence_after();
+          }
+          tmem_st_32x16(p_addr + 0, p0);
+          tmem_st_32x16(p_addr + 16, p1);
+          tmem_st_32x16(p_addr + 32, p2);
+          tmem_st_32x16(p_addr + 48, p3);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[x]);
+        }
+        if (n_mine > 0) {
+          mbar_wait(&o_full[x], (cdone + n_mine - 1) & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
+          tc_fence_after();
+          uint32_t wa[32], wb[32];
+          tmem_ld_32x32(o_addr, wa);
+          tmem_ld_32x32(o_addr + 32, wb);
+          tmem_ld_wait_for(wa);
+          tmem_ld_wait_for(wb);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_empty[x]);   // the next item's first P V may overwrite the accumulator
+          const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+          if (row_g < p.S) {
+            __nv_bfloat16* dst = p.O + row_g * p.o_ss + b * p.o_bs + h * p.o_hs;
+#pragma unroll
+            for (int cc = 0; cc < 32; cc += 8) {
+              uint4 wv;
+              wv.x = pack_bf16x2(__uint_as_float(wa[cc + 0]) * inv_l, __uint_as_float(wa[cc + 1]) * inv_l);
+              wv.y = pack_bf16x2(__uint_as_float(wa[cc + 2]) * inv_l, __uint_as_float(wa[cc + 3]) * inv_l);
+              wv.z = pack_bf16x2(__uint_as_float(wa[cc + 4]) * inv_l, __uint_as_float(wa[cc + 5]) * inv_l);
+              wv.w = pack_bf16x2(__uint_as_float(wa[cc + 6]) * inv_l, __uint_as_float(wa[cc + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + cc) = wv;
+              wv.x = pack_bf16x2(__uint_as_float(wb[cc + 0]) * inv_l, __uint_as_float(wb[cc + 1]) * inv_l);
+              wv.y = pack_bf16x2(__uint_as_float(wb[cc + 2]) * inv_l, __uint_as_float(wb[cc + 3]) * inv_l);
+              wv.z = pack_bf16x2(__uint_as_float(wb[cc + 4]) * inv_l, __uint_as_float(wb[cc + 5]) * inv_l);
+              wv.w = pack_bf16x2(__uint_as_float(wb[cc + 6]) * inv_l, __uint_as_float(wb[cc + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + 32 + cc) = wv;
+            }
+          }
+          if (row_g < p.S_pad) {
+            const float mm = (m == -INFINITY) ? 0.f : m;
+            p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] = mm * p.scale + logf(fmaxf(l, 1e-37f));
+          }
+        }
+        cdone += n_mine;
+      }
+    } else
     for (int rnd = 0; rnd * G < n_items; ++rnd) {
       const int w = snake(rnd);
       if (w >= n_items) break;
@@ -1274,11 +1508,23 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   if (D == 64) {
     const int smem = 16384 * 5 + 1 * 32768 + 256;   // single-buffered: two CTAs per SM
     (void)smem;
-    if (!set64) { if (set_smem(flash_fwd64_kernel, FWD64_SMEM)) return -10; set64 = true; }
+    if (!set64) {
+      if (set_smem(flash_fwd64_kernel<false>, FWD64_SMEM) || set_smem(flash_fwd64_kernel<true>, FWD64_SMEM))
+        return -10;
+      set64 = true;
+    }
+    // GFS_ATTN_FWD_OTMEM=0 selects the variant that folds the output into registers per key block
+    static const bool otmem = [] {
+      const char* e = std::getenv("GFS_ATTN_FWD_OTMEM");
+      return !(e && e[0] == '0');
+    }();
     const int n_pairs = (static_cast<int>(grid.x) + 1) / 2;
     const int n_items = n_pairs * B * nh;
     const int ctas = std::min(n_items, gfs_host::sm_count());
-    flash_fwd64_kernel<<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
+    if (otmem)
+      flash_fwd64_kernel<true><<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
+    else
+      flash_fwd64_kernel<false><<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
   } else {
     const int smem = 32768 * 5 + 2 * 32768 + 256;
     if (!set128) { if (set_smem(flash_fwd_kernel<128, 2>, smem)) return -10; set128 = true; }

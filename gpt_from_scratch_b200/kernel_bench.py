@@ -51,6 +51,9 @@ class Timer:
         total = 0.0
         for _ in range(iters):
             self.flush_buf.zero_()
+            # a device-side delay in front of the timed region: the host enqueues the launch while
+            # the GPU is still busy, so Python launch latency is not part of a short kernel's number
+            torch.cuda._sleep(600_000)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()

@@ -39,6 +39,34 @@ def test_flash_attention_fwd_bwd(cuda_device, B, nh, S, D):
         assert rel < 2e-2, f"{name}: relative error {rel:.4g}"
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_flash_attention_growing_scores(cuda_device, causal):
+    """Keys whose magnitude grows along the sequence: the row maximum rises by far more than 2^8
+    from one key block to the next, so the head_dim-64 forward has to rescale the output it
+    accumulates in tensor memory (with random-normal inputs the maximum settles in the first
+    block and that path never runs). Some rows get a negative query, so their maximum stays."""
+    from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
+    g = torch.Generator(device="cuda").manual_seed(11)
+    B, nh, S, D = 2, 3, 640, 64
+    q = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
+    k = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
+    v = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
+    ramp = torch.linspace(0.25, 6.0, S, device=cuda_device).view(1, 1, S, 1)
+    k = k * ramp + 0.5 * ramp * torch.sign(q.mean(dim=2, keepdim=True))
+    q[:, :, ::3] *= -1.0
+    q, k, v = (t.bfloat16().requires_grad_() for t in (q, k, v))
+    do = torch.randn(B, nh, S, D, device=cuda_device, generator=g).bfloat16()
+    o = apply_flash_attn(q, k, v, causal)
+    o.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = attention_reference(qf, kf, vf, causal)
+    of.backward(do.float())
+    _close(o, of, 2e-2, what="O")
+    for name, a, b in (("O", o, of), ("dQ", q.grad, qf.grad), ("dK", k.grad, kf.grad), ("dV", v.grad, vf.grad)):
+        rel = (a.float() - b).norm() / (b.norm() + 1e-12)
+        assert rel < 3e-2, f"{name}: relative error {rel:.4g}"
+
+
 def test_flash_attention_noncausal_and_ragged(cuda_device):
     from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
     g = torch.Generator(device="cuda").manual_seed(3)
