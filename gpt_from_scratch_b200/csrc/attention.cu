@@ -464,7 +464,8 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
   uint64_t* o_empty = o_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+  uint64_t* s_free = o_empty + 2;            // [2] the tile's scores have been read out of tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -490,6 +491,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       mbar_init(&p_full[i], 4);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 4);
+      mbar_init(&s_free[i], 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -583,10 +585,13 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         if (n_x[1] > 0) issue_s(1, 0);
         if (n_kv > 0) umma_commit_e(&k_empty[g0 % KS]);
         if (n_kv == 1) umma_commit_e(q_empty);
-        // The two query tiles are served in the order in which their probabilities become ready
-        // (not in lockstep): a tile that waits for its next S leaves the schedulers to the other
-        // tile's softmax. A tile may lead the other by one key block at most, which the K/V ring
-        // (three stages, released when both tiles have used a block) always allows.
+        // Event loop over both query tiles. Two kinds of events per tile: "scores read out"
+        // (s_free: the softmax warps hold block j's scores in registers) lets S(j+1) be issued
+        // into the same columns while the exponentials of block j are still being computed, so
+        // the next scores are ready when the softmax gets there; "probabilities stored" (p_full)
+        // lets P V(j) be issued. Every wait here is a poll, so a tile that is ahead (bounded by
+        // the three-stage K/V ring, whose stages are released when both tiles have used a
+        // block) never blocks the warp that the other tile needs.
         int s_iss[2] = {n_x[0] > 0 ? 1 : 0, n_x[1] > 0 ? 1 : 0};   // S MMAs issued per tile
         int pv_iss[2] = {0, 0};                                     // P V MMAs issued per tile
         uint32_t spins = 0;
@@ -596,35 +601,44 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           bool progressed = false;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int j = pv_iss[x];
             const int ot = x ^ 1;
-            if (j >= n_x[x]) continue;
-            if (pv_iss[ot] < n_x[ot] && j > pv_iss[ot] + 1) continue;   // bounded lead
-            const int c = cx[x] + j;
-            if (!mbar_try_wait(&p_full[x], c & 1)) continue;             // S_x(j) consumed, P_x(j) in TMEM
-            progressed = true;
-            const int g = g0 + j;
-            if (j + 1 < n_x[x]) {
-              issue_s(x, j + 1);
-              s_iss[x] = j + 2;
-              // the K block is free once both tiles' S MMAs on it have been issued
-              if (s_iss[ot] > j + 1 || j + 1 >= n_x[ot]) umma_commit_e(&k_empty[(g + 1) % KS]);
-              if (s_iss[0] >= n_x[0] && s_iss[1] >= n_x[1]) umma_commit_e(q_empty);   // the item's last S
+            const int bn = s_iss[x];          // next block whose S is to be issued
+            if (bn > 0 && bn < n_x[x]) {
+              const int gb = g0 + bn;
+              if (mbar_try_wait(&s_free[x], (cx[x] + bn - 1) & 1) &&
+                  mbar_try_wait(&k_full[gb % KS], (gb / KS) & 1)) {
+                tc_fence_after();
+                mma_kk<D / 16>(tmem_base + S_COL + x * 128, smem_u32(Qs + x * 16384), 0,
+                               smem_u32(Ks + (gb % KS) * 16384), 0, idesc_s, false);
+                umma_commit_e(&s_full[x]);
+                s_iss[x] = bn + 1;
+                // the K block is free once both tiles' S MMAs on it have been issued
+                if (s_iss[ot] > bn || bn >= n_x[ot]) umma_commit_e(&k_empty[gb % KS]);
+                if (s_iss[0] >= n_x[0] && s_iss[1] >= n_x[1]) umma_commit_e(q_empty);   // the item's last S
+                progressed = true;
+              }
             }
-            mbar_wait(&v_full[g % KS], (g / KS) & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
-            if (OTMEM) {
-              // the accumulator is overwritten once per item: wait until the softmax warps have
-              // read the previous item's result out of it
-              if (j == 0) mbar_wait(&o_empty[x], (it[x] & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
-            } else {
-              mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+            const int j = pv_iss[x];
+            if (j < n_x[x]) {
+              const int c = cx[x] + j;
+              const int g = g0 + j;
+              if (mbar_try_wait(&p_full[x], c & 1) && mbar_try_wait(&v_full[g % KS], (g / KS) & 1)) {
+                if (OTMEM) {
+                  // the accumulator is overwritten once per item: wait until the softmax warps
+                  // have read the previous item's result out of it
+                  if (j == 0) mbar_wait(&o_empty[x], (it[x] & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+                } else {
+                  mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
+                }
+                tc_fence_after();
+                mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384),
+                           0, idesc_o, OTMEM && j > 0);
+                umma_commit_e(&o_full[x]);
+                pv_iss[x] = j + 1;
+                if (pv_iss[ot] > j || j >= n_x[ot]) umma_commit_e(&v_empty[g % KS]);
+                progressed = true;
+              }
             }
-            tc_fence_after();
-            mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384), 0,
-                       idesc_o, OTMEM && j > 0);
-            umma_commit_e(&o_full[x]);
-            pv_iss[x] = j + 1;
-            if (pv_iss[ot] > j || j >= n_x[ot]) umma_commit_e(&v_empty[g % KS]);
           }
           if (progressed) {
             spins = 0;
@@ -709,6 +723,13 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             }
           };
           tmem_ld_wait_for(v0);
+          tmem_ld_wait_for(v1);
+          tmem_ld_wait_for(v2);
+          tmem_ld_wait_for(v3);
+          // all 128 scores are in registers: the MMA warp may overwrite S with the next block's
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_free[x]);
           max_chunk(v0, 0);
           tmem_ld_wait_for(v1);
           max_chunk(v1, 32);
@@ -965,7 +986,10 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[x]);
+        if (lane == 0) {
+          mbar_arrive(&s_free[x]);   // this variant reads the scores twice: free only now
+          mbar_arrive(&p_full[x]);
+        }
         alpha_prev = alpha;
       }
       if (n_mine > 0) fold_pv(cdone + n_mine - 1, alpha_prev);
