@@ -730,13 +730,22 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_free[x]);
-          max_chunk(v0, 0);
-          tmem_ld_wait_for(v1);
-          max_chunk(v1, 32);
-          tmem_ld_wait_for(v2);
-          max_chunk(v2, 64);
-          tmem_ld_wait_for(v3);
-          max_chunk(v3, 96);
+          if (!need_mask) {
+            // hot path kept as one straight run of code (the masked variants below are reached on
+            // the diagonal and the last key block only)
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              mx0 = fmax3(mx0, __uint_as_float(v0[e]), __uint_as_float(v0[e + 1]));
+              mx1 = fmax3(mx1, __uint_as_float(v1[e]), __uint_as_float(v1[e + 1]));
+              mx0 = fmax3(mx0, __uint_as_float(v2[e]), __uint_as_float(v2[e + 1]));
+              mx1 = fmax3(mx1, __uint_as_float(v3[e]), __uint_as_float(v3[e + 1]));
+            }
+          } else {
+            max_chunk(v0, 0);
+            max_chunk(v1, 32);
+            max_chunk(v2, 64);
+            max_chunk(v3, 96);
+          }
           const float m_new = fmaxf(m, fmaxf(mx0, mx1));
           // raise the running maximum only when it grew by more than 2^8 (or was still -inf)
           bool grow = false;
@@ -798,10 +807,17 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             }
           };
           uint32_t p0[16], p1[16], p2[16], p3[16];
-          prob_chunk(v0, 0, p0);
-          prob_chunk(v1, 32, p1);
-          prob_chunk(v2, 64, p2);
-          prob_chunk(v3, 96, p3);
+          if (!need_mask) {
+            prob_chunk_impl(std::false_type{}, v0, 0, p0);
+            prob_chunk_impl(std::false_type{}, v1, 32, p1);
+            prob_chunk_impl(std::false_type{}, v2, 64, p2);
+            prob_chunk_impl(std::false_type{}, v3, 96, p3);
+          } else {
+            prob_chunk(v0, 0, p0);
+            prob_chunk(v1, 32, p1);
+            prob_chunk(v2, 64, p2);
+            prob_chunk(v3, 96, p3);
+          }
           l += rs0 + rs1;
           // P of the previous block is read by its P V MMA: overwrite it only when that is done
           if (j > 0) {
