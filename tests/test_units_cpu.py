@@ -284,3 +284,26 @@ def test_train_step_async_cpu():
     t = torch.randint(0, 64, (2, 17), generator=torch.Generator().manual_seed(0))
     h = eng.train_step_async(t[:, :-1].contiguous(), t[:, 1:].contiguous())
     assert h.ready() and 0 < h.value() < 10
+
+
+def test_collective_site_keys_follow_program_order():
+    """Keys of collectively allocated buffers come from a counter stored on the weight at its
+    first use: a freed weight's key is never handed to a new tensor (``id()`` can be), so ranks
+    that run the same program derive the same key sequence."""
+    import torch
+    from gpt_from_scratch_b200.parallel import fused_comm
+    a, b = torch.zeros(2, 2), torch.zeros(2, 2)
+    ka, kb = fused_comm._weight_site_key(a), fused_comm._weight_site_key(b)
+    assert kb == ka + 1
+    assert fused_comm._weight_site_key(a) == ka          # stable for the life of the tensor
+    seen = {ka, kb}
+    for _ in range(50):                                    # freed tensors: their ids get recycled, keys do not
+        t = torch.zeros(2, 2)
+        k = fused_comm._weight_site_key(t)
+        assert k not in seen
+        seen.add(k)
+        del t
+    p = torch.nn.Parameter(torch.zeros(2, 2))
+    kp = fused_comm._weight_site_key(p)
+    p.data = torch.ones(2, 2)                              # re-pointing the storage keeps the key
+    assert fused_comm._weight_site_key(p) == kp
