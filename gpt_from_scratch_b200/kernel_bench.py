@@ -160,7 +160,9 @@ def build_cases(dev, small: bool):
     cases.append(("ce_from_gemm_partials", lambda: ce_ops.ce_stats_from_partials(ce_parts, logits, tgt, 0, True), 0,
                   8 * n_parts * M))
     cases.append(("ce_bwd_inplace", lambda: ce_ops.ce_backward_inplace(logits, lse_ce, tgt, grows, 0), 0, 4 * M * V))
-    n = 124_475_904 if not small else 8 * 1024 * 1024   # parameter count of the GPT-124M shape (vocab 50304)
+    # parameter count of the benchmark model: 12 layers x (QKV + out + gate_up + down) + untied
+    # embedding and LM head at vocab 50304 + norms
+    n = 190_532_352 if not small else 8 * 1024 * 1024
     grad = rnd(n)
     master = torch.randn(n, device=dev)
     m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
