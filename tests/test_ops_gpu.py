@@ -16,7 +16,7 @@ def _close(a, b, atol, rtol=0.0, what=""):
 
 
 @pytest.mark.parametrize("B,nh,S,D", [(2, 2, 128, 64), (1, 3, 256, 64), (2, 2, 512, 128), (1, 2, 384, 128),
-                                      (4, 12, 1024, 64)])
+                                      (4, 12, 1024, 64), (1, 2, 2048, 64)])
 def test_flash_attention_fwd_bwd(cuda_device, B, nh, S, D):
     from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
     g = torch.Generator(device="cuda").manual_seed(S + D)
