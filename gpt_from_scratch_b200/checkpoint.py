@@ -1,12 +1,14 @@
 """Checkpoint save / resume. The reference never saves anything (its optimizer
 ``state_dict`` even omits the fp32 master weights); this module stores, per
 (tp_rank, dp_rank): the model ``state_dict`` in the reference's key layout, the optimizer
-shard (fp32 master, moments, step), and the loop state (step, epoch, RNG)."""
+shard (fp32 master, moments, step), and the loop state (step, epoch, batches consumed in that
+epoch, RNG)."""
 from __future__ import annotations
 
 import os
 
 import torch
+import torch.distributed as dist
 
 from .parallel import parallel_state as ps
 
@@ -32,9 +34,15 @@ def save_checkpoint(directory: str, step: int, model, optimizer, extra: dict | N
     tmp = path + ".tmp"
     torch.save(payload, tmp)
     os.replace(tmp, path)
+    # `latest` may only name a step whose files are all in place: every rank's rename has to be
+    # done before the pointer moves (a crash in between leaves the previous checkpoint current)
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
     if ps.get_tensor_model_parallel_group_rank() == 0 and ps.get_data_parallel_group_rank() == 0:
-        with open(os.path.join(directory, "latest"), "w") as f:
+        latest = os.path.join(directory, "latest")
+        with open(latest + ".tmp", "w") as f:
             f.write(str(step))
+        os.replace(latest + ".tmp", latest)
     return path
 
 

@@ -44,11 +44,30 @@ class DistributedDataset(Dataset):
         return {"input": chunk[:-1], "label": chunk[1:]}
 
 
+class ResumableDistributedSampler(DistributedSampler):
+    """``DistributedSampler`` that can start an epoch part-way: ``skip_samples(n)`` drops the
+    first ``n`` indices of the NEXT iteration only, so a run resumed in the middle of an epoch
+    continues with the batch the interrupted run would have read next."""
+
+    _skip = 0
+
+    def skip_samples(self, n: int) -> None:
+        self._skip = int(n)
+
+    def __iter__(self):
+        it = super().__iter__()
+        skip, self._skip = self._skip, 0
+        for _ in range(skip):
+            next(it, None)
+        return it
+
+
 def create_distributed_dataloader(data_path: str, seq_len: int, batch_size: int, num_workers: int = 4,
                                   seed: int = 0, pin_memory: bool | None = None):
-    """Returns ``(dataloader, sampler)``; call ``sampler.set_epoch(epoch)`` every epoch."""
+    """Returns ``(dataloader, sampler)``; call ``sampler.set_epoch(epoch)`` every epoch (and
+    ``sampler.skip_samples(batches_done * batch_size)`` before iterating to resume inside one)."""
     dataset = DistributedDataset(data_path, seq_len)
-    sampler = DistributedSampler(dataset, num_replicas=ps.get_data_parallel_world_size(),
+    sampler = ResumableDistributedSampler(dataset, num_replicas=ps.get_data_parallel_world_size(),
                                  rank=ps.get_data_parallel_group_rank(), shuffle=True, drop_last=True, seed=seed)
     if pin_memory is None:
         pin_memory = torch.cuda.is_available()

@@ -60,9 +60,9 @@ class TrainEngine:
 
     def forward_loss(self, inputs: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         """inputs, labels: ``[B, S]`` token ids on the engine's device -> mean loss (scalar)."""
-        logits = self.model(inputs)                               # [S, B, V/P]
-        labels_t = labels.transpose(0, 1).contiguous()            # [S, B]
-        loss = vocab_parallel_cross_entropy(logits, labels_t)     # [S, B]
+        logits, ce_partials = self.model(inputs, return_ce_stats=True)        # [S, B, V/P]
+        labels_t = labels.transpose(0, 1).contiguous()                        # [S, B]
+        loss = vocab_parallel_cross_entropy(logits, labels_t, ce_partials)    # [S, B]
         return loss.mean()
 
     def train_step(self, inputs: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:

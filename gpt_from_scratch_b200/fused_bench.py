@@ -9,7 +9,7 @@ timed launches; a device-side delay in front of the first event lets the host en
 operator ahead of time), and the MAX over ranks is reported next to the same operation built from an
 NCCL collective plus the plain GEMM (``--comm-impl nccl`` path). The roofline of a fused path
 is the slower of (FLOPs / measured GEMM peak) and (bytes that must cross NVLink per GPU /
-measured peer-copy bandwidth, 770 GB/s per direction on this pool); ``frac`` = roofline time
+measured peer-copy bandwidth, 770 GB/s per direction here); ``frac`` = roofline time
 / measured time.
 """
 from __future__ import annotations
@@ -121,8 +121,8 @@ def main() -> None:
         ps.set_comm_impl("fused")
 
         def lm_epilogue_stats():
-            out = fused_comm.allgather_linear(x_lm, w_lm, ce_stats=True)
-            return ce_ops.ce_stats_from_partials(out._gfs_ce_partials, out.view(M, -1), tgt, v0, False)
+            out, partials = fused_comm.allgather_linear(x_lm, w_lm, ce_stats=True)
+            return ce_ops.ce_stats_from_partials(partials, out.view(M, -1), tgt, v0, False)
 
         def lm_then_pass():
             out = fused_comm.allgather_linear(x_lm, w_lm)

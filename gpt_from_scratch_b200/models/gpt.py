@@ -24,10 +24,13 @@ class GPTModel(nn.Module):
         self.output = ColumnParallelLinear(config.hidden_size, config.vocab_size, bias=False,
                                            init_method=init_method)
 
-    def forward(self, inputs):
+    def forward(self, inputs, return_ce_stats: bool = False):
+        """``return_ce_stats=True`` returns ``(logits, partials)``: the LM head's GEMM epilogue also
+        emits the softmax statistics the loss needs (``None`` on paths without that epilogue)."""
         hidden = self.embedding(inputs)            # [S/P, B, H]
         for layer in self.layers:
             hidden = layer(hidden)
         hidden = self.final_norm(hidden)
-        # the LM head's GEMM epilogue also emits the softmax statistics the loss needs
-        return self.output(hidden, ce_stats=True)  # [S, B, V/P]
+        if return_ce_stats:
+            return self.output(hidden, ce_stats=True)
+        return self.output(hidden)                 # [S, B, V/P]

@@ -23,6 +23,28 @@ _PAIR_ENABLED = os.environ.get("GFS_GEMM_PAIR", "1") != "0"
 _workspaces: dict[int, torch.Tensor] = {}
 
 
+class pair_min_tiles:
+    """``with pair_min_tiles(n):`` every kernel-selection rule inside the block uses ``n`` as the
+    number of 256 x 256 tiles from which a problem goes to the CTA-pair kernel (``1``: always when
+    eligible; a huge value: never). For tests and microbenchmarks that want a particular kernel on
+    a small problem; all ranks of a group must use the same value. ``None`` changes nothing."""
+
+    def __init__(self, n: int | None):
+        self.n = n
+
+    def __enter__(self):
+        global _PAIR_MIN_TILES
+        self.saved = _PAIR_MIN_TILES
+        if self.n is not None:
+            _PAIR_MIN_TILES = int(self.n)
+        return self
+
+    def __exit__(self, *exc):
+        global _PAIR_MIN_TILES
+        _PAIR_MIN_TILES = self.saved
+        return False
+
+
 def _workspace(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ws = _workspaces.get(idx)

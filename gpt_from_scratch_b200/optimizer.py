@@ -18,7 +18,9 @@ Differences that are deliberate:
 * On CUDA/bf16 the clip + AdamW + cast is one kernel and the clip decision stays on the
   device (the reference synchronises the host on ``if norm > clip``, core/optimizer.py:103).
 * ``zero_grad()`` does not memset: backward kernels overwrite each gradient slice on first
-  use in a step (see ``ops/grad_sink.py``).
+  use in a step (see ``ops/grad_sink.py``); a parameter whose gradient arrives through plain
+  autograd instead (a bias, a fallback path) has its slice cleared by a tensor hook right
+  before autograd accumulates into it.
 * The gradient norm is global over TP x DP with replicated parameters counted once, and
   the gradients of TP-replicated parameters (the RMSNorm weights, which only see their
   sequence shard) are summed over the TP group before the step. ``reference_quirks=True``
@@ -95,6 +97,10 @@ class DistributedOptimizer:
             p.grad = self.grad_buffer[offset:offset + n].view(p.shape)
             p._grad_sink_ok = bool(self.use_fused_kernels)
             p._grad_fresh = False
+            if self.use_fused_kernels:
+                # a gradient that reaches this parameter through plain autograd (a bias, a
+                # fallback path) is ADDED onto the slice: clear last step's values first
+                p.register_hook(self._clear_stale_slice_hook(p))
             if getattr(p, "tp_replicated", False):
                 replicated_ranges.append((offset, offset + n))
             self.param_offsets.append(offset)
@@ -137,6 +143,15 @@ class DistributedOptimizer:
             self.grad_buffer.zero_()
             for p in self.params:
                 p._grad_fresh = False
+
+    @staticmethod
+    def _clear_stale_slice_hook(p):
+        def hook(grad):
+            if getattr(p, "_grad_fresh", False):
+                p.grad.zero_()
+                p._grad_fresh = False
+            return None
+        return hook
 
     def _materialise_unwritten(self) -> None:
         for p in self.params:

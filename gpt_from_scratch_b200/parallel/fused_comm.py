@@ -126,8 +126,6 @@ def _allgather_gemm_ce(x2, weight, out, M, N, K, grp, gathered, site):
 
 
 class _AllGatherLinear(torch.autograd.Function):
-    last_ce_partials = None   # statistics produced by the most recent forward with ce_stats=True
-
     @staticmethod
     def forward(ctx, x_shard, weight, sink, rope, site_key, ce_stats=False):
         grp = symm.get_group("tp")
@@ -142,17 +140,22 @@ class _AllGatherLinear(torch.autograd.Function):
         partials = None
         if ce_stats and rope is None:
             partials = _allgather_gemm_ce(x2, weight, out, M, N, K, grp, gathered, site)
-        _AllGatherLinear.last_ce_partials = partials
         if partials is None:
             _gemm_comm(MODE_AG, x2, weight, out, None, M, N, K, False, grp, gathered, site, rope)
         ctx.save_for_backward(weight)
         ctx.gathered = gathered
         ctx.sink = sink
         ctx.dims = (M, N, K, Ms, x_shard.shape)
-        return out.view(x_shard.shape[0] * grp.world, *x_shard.shape[1:-1], N)
+        y = out.view(x_shard.shape[0] * grp.world, *x_shard.shape[1:-1], N)
+        if not ce_stats:
+            return y
+        if partials is None:
+            partials = x2.new_empty(0, dtype=torch.float32)
+        ctx.mark_non_differentiable(partials)
+        return y, partials
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, _dpartials=None):
         (weight,) = ctx.saved_tensors
         grp = symm.get_group("tp")
         M, N, K, Ms, in_shape = ctx.dims
@@ -175,10 +178,10 @@ class _AllGatherLinear(torch.autograd.Function):
 def allgather_linear(x_shard: torch.Tensor, weight: torch.Tensor, rope=None, ce_stats: bool = False) -> torch.Tensor:
     """``gather_S(x_shard) @ weight^T`` with the all-gather done by the GEMM kernel.
 
-    ``ce_stats``: the output is the LM head's logits; when the CTA-pair kernel serves the problem
-    its epilogue also produces the per-row softmax statistics, attached to the returned tensor as
-    ``_gfs_ce_partials`` (the vocabulary-parallel cross entropy then makes no pass over the logits
-    in the forward)."""
+    ``ce_stats``: the output is the LM head's logits and the return value is ``(logits, partials)``;
+    when the CTA-pair kernel serves the problem its epilogue also produces the per-row softmax
+    statistics (the vocabulary-parallel cross entropy then makes no pass over the logits in the
+    forward), otherwise ``partials`` is ``None``."""
     world = ps.get_tensor_model_parallel_world_size()
     rows = x_shard.numel() // x_shard.shape[-1]
     if not (x_shard.dtype == weight.dtype == torch.bfloat16 and supported(rows, x_shard.shape[-1], weight.shape[0])):
@@ -186,11 +189,11 @@ def allgather_linear(x_shard: torch.Tensor, weight: torch.Tensor, rope=None, ce_
         from .layers import linear_with_sink
         return linear_with_sink(mappings.gather_from_sequence_parallel_region(x_shard), weight, rope=rope,
                                 ce_stats=ce_stats)
-    out = _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, _weight_site_key(weight), ce_stats)
-    if ce_stats and _AllGatherLinear.last_ce_partials is not None:
-        out._gfs_ce_partials = _AllGatherLinear.last_ce_partials
-        _AllGatherLinear.last_ce_partials = None
-    return out
+    if not ce_stats:
+        return _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, _weight_site_key(weight), False)
+    out, partials = _AllGatherLinear.apply(x_shard, weight, GradSink.of(weight), rope, _weight_site_key(weight),
+                                           True)
+    return out, (partials if partials.numel() else None)
 
 
 # --------------------------------------------------------------------------- row parallel

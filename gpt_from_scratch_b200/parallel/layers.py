@@ -61,26 +61,32 @@ class _LinearFn(torch.autograd.Function):
     """``y = x @ W^T (+ residual)`` with explicit dgrad/wgrad so the weight gradient can go
     to a :class:`GradSink`."""
 
-    last_ce_partials = None   # statistics produced by the most recent forward with ce_stats=True
-
     @staticmethod
     def forward(ctx, x, weight, residual, sink, rope=None, ce_stats=False):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         res2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
+        partials = None
         if ce_stats and residual is None and rope is None:
-            y2, _LinearFn.last_ce_partials = gemm_ops.linear_fwd_ce(x2, weight)
+            y2, partials = gemm_ops.linear_fwd_ce(x2, weight)
         else:
-            _LinearFn.last_ce_partials = None
             y2 = gemm_ops.linear_fwd(x2, weight, res2, rope=rope)
         ctx.save_for_backward(x2, weight)
         ctx.sink = sink
         ctx.has_res = residual is not None
         ctx.in_shape = x.shape
-        return y2.view(*x.shape[:-1], weight.shape[0])
+        y = y2.view(*x.shape[:-1], weight.shape[0])
+        if not ce_stats:
+            return y
+        # second output: the softmax statistics of the logits (an empty tensor when the GEMM that
+        # served the problem has no statistics epilogue); not differentiable
+        if partials is None:
+            partials = x2.new_empty(0, dtype=torch.float32)
+        ctx.mark_non_differentiable(partials)
+        return y, partials
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, _dpartials=None):
         x2, weight = ctx.saved_tensors
         N = weight.shape[0]
         dy2 = dy.reshape(-1, N)
@@ -105,15 +111,14 @@ def linear_with_sink(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tens
     function's backward: the caller's next operator must return gradients w.r.t. the
     un-rotated output (the fused attention backward does).
 
-    ``ce_stats``: the output is the LM head's logits; when the CTA-pair GEMM serves the problem its
-    epilogue also produces the per-row softmax statistics, attached to the returned tensor as
-    ``_gfs_ce_partials`` for :func:`vocab_parallel_cross_entropy` (which then skips its pass over the
-    logits)."""
-    out = _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope, ce_stats)
-    if ce_stats and _LinearFn.last_ce_partials is not None:
-        out._gfs_ce_partials = _LinearFn.last_ce_partials
-        _LinearFn.last_ce_partials = None
-    return out
+    ``ce_stats``: the output is the LM head's logits and the return value is ``(logits, partials)``;
+    when the CTA-pair GEMM serves the problem ``partials`` holds the per-row softmax statistics its
+    epilogue produced (pass them to :func:`vocab_parallel_cross_entropy`, which then skips its pass
+    over the logits), otherwise it is ``None``."""
+    if not ce_stats:
+        return _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope, False)
+    out, partials = _LinearFn.apply(x, weight, residual, GradSink.of(weight), rope, True)
+    return out, (partials if partials.numel() else None)
 
 
 class ColumnParallelLinear(nn.Module):
@@ -139,17 +144,22 @@ class ColumnParallelLinear(nn.Module):
         _init_sharded(self.weight, init_method, ColumnParallelLinear._salt)
 
     def forward(self, input_, rope=None, ce_stats=False):
+        """``ce_stats=True`` (LM head): returns ``(logits, partials)`` where ``partials`` are the
+        softmax statistics produced by the GEMM epilogue, or ``None`` when there are none."""
         world = ps.get_tensor_model_parallel_world_size()
+        want = ce_stats and self.bias is None
         if world > 1 and ps.get_comm_impl() == "fused" and input_.is_cuda:
             from . import fused_comm
-            out = fused_comm.allgather_linear(input_, self.weight, rope=rope,
-                                              ce_stats=ce_stats and self.bias is None)
+            out = fused_comm.allgather_linear(input_, self.weight, rope=rope, ce_stats=want)
         else:
             full = mappings.gather_from_sequence_parallel_region(input_)
-            out = linear_with_sink(full, self.weight, rope=rope, ce_stats=ce_stats and self.bias is None)
+            out = linear_with_sink(full, self.weight, rope=rope, ce_stats=want)
+        partials = None
+        if want:
+            out, partials = out
         if self.bias is not None:
             out = out + self.bias
-        return out
+        return (out, partials) if ce_stats else out
 
 
 class RowParallelLinear(nn.Module):
@@ -173,6 +183,9 @@ class RowParallelLinear(nn.Module):
                                                dtype=torch.float32))
         if bias:
             self.bias = nn.Parameter(torch.zeros(output_size, device=dev, dtype=torch.float32))
+            # added after the reduce-scatter, so every TP rank holds a copy that only sees its
+            # sequence shard's gradient: the optimizer sums those over the TP group
+            self.bias.tp_replicated = True
         else:
             self.register_parameter("bias", None)
         RowParallelLinear._salt += 1

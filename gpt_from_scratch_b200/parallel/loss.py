@@ -18,7 +18,7 @@ from . import parallel_state as ps
 
 class _VocabParallelCrossEntropy(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, vocab_parallel_logits, target):
+    def forward(ctx, vocab_parallel_logits, target, partials=None):
         world = ps.get_tensor_model_parallel_world_size()
         rank = ps.get_tensor_model_parallel_group_rank()
         group = ps.get_tensor_model_parallel_group()
@@ -33,7 +33,6 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
             tgt = target.reshape(-1).contiguous()
             if tgt.dtype != torch.int64:
                 tgt = tgt.long()
-            partials = getattr(lg, "_gfs_ce_partials", None)
             if (partials is not None and lg2.data_ptr() == lg.data_ptr() and partials.shape[1] == lg2.shape[0]
                     and partials.device == lg2.device):
                 # statistics already produced by the LM-head GEMM epilogue: no pass over the logits
@@ -81,14 +80,19 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
             lg2, lse, tgt = ctx.saved_tensors
             g = grad_output.reshape(-1).float().contiguous()
             dlogits = ce_ops.ce_backward_inplace(lg2, lse, tgt, g, ctx.v0)
-            return dlogits.view(ctx.shape), None
+            return dlogits.view(ctx.shape), None, None
         softmax, mask, local_t = ctx.saved_tensors
         grad = softmax.clone()
         grad.scatter_add_(-1, local_t.unsqueeze(-1), -mask.unsqueeze(-1).to(grad.dtype))
         grad = grad * grad_output.unsqueeze(-1)
-        return grad.to(ctx.out_dtype), None
+        return grad.to(ctx.out_dtype), None, None
 
 
-def vocab_parallel_cross_entropy(vocab_parallel_logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
-    """Public wrapper (the reference exposes only the private Function, train.py:12,180)."""
-    return _VocabParallelCrossEntropy.apply(vocab_parallel_logits, target)
+def vocab_parallel_cross_entropy(vocab_parallel_logits: torch.Tensor, target: torch.Tensor,
+                                 partials: torch.Tensor | None = None) -> torch.Tensor:
+    """Public wrapper (the reference exposes only the private Function, train.py:12,180).
+
+    ``partials``: softmax statistics of these logits produced by the LM-head GEMM epilogue
+    (``GPTModel.forward(..., return_ce_stats=True)``); with them the forward makes no pass over the
+    logits."""
+    return _VocabParallelCrossEntropy.apply(vocab_parallel_logits, target, partials)

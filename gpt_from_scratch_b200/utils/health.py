@@ -1,8 +1,9 @@
 """Host-side failure detection. The reference has none: a dead rank hangs NCCL until the
 watchdog fires. Here every rank publishes a heartbeat (its step counter and a wall-clock
-stamp) in the job's key-value store between steps, and checks its peers' stamps before
-launching the next step, so a rank that died or stalled is reported as a Python exception
-on the survivors instead of a hang inside a collective. Recovery is a restart from the last
+stamp) in the job's key-value store after every step; at every log interval the training
+loop waits (bounded) until all peers have reported that step before it launches the next one,
+so a rank that died or stalled between steps is reported as a Python exception on the
+survivors instead of a hang inside the next collective (``train.py --heartbeat-timeout``). Recovery is a restart from the last
 checkpoint (``torchrun --max-restarts``); no in-job elasticity is claimed.
 
 Device-side waits are bounded separately (see ``csrc/common.cuh``): they end with a status
@@ -49,6 +50,26 @@ class Heartbeat:
         for r, (step, stamp) in self.peers().items():
             if r != self.rank and now - stamp > self.stale_after:
                 raise PeerFailure(r, now - stamp, step)
+
+
+    def wait_for_peers(self, step: int, timeout: float | None = None, poll: float = 0.02) -> None:
+        """Block until every peer has reported ``step`` (or a later one); raise
+        :class:`PeerFailure` for the first peer that has not done so within ``timeout`` seconds
+        (default: ``stale_after``). Call it between steps, before the next collective is
+        launched."""
+        timeout = self.stale_after if timeout is None else timeout
+        start = time.time()
+        while True:
+            seen = self.peers()
+            behind = [r for r in range(self.world) if r != self.rank and seen.get(r, (-1, 0.0))[0] < step]
+            if not behind:
+                return
+            now = time.time()
+            if now - start > timeout:
+                r = behind[0]
+                last_step, stamp = seen.get(r, (-1, start))
+                raise PeerFailure(r, now - stamp, last_step)
+            time.sleep(poll)
 
 
 def default_heartbeat(stale_after: float = 60.0) -> Heartbeat | None:

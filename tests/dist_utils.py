@@ -15,12 +15,13 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, result_dir):
+def _entry(rank, world, port, fn, args, result_dir, init):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     torch.set_num_threads(1)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if init:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         out = fn(rank, world, *args)
         torch.save(out, os.path.join(result_dir, f"rank{rank}.pt"))
     except Exception:
@@ -31,8 +32,9 @@ def _entry(rank, world, port, fn, args, result_dir):
             dist.destroy_process_group()
 
 
-def run_ranks(fn, world: int, args=(), tmp_path=None):
-    """Run ``fn(rank, world, *args)`` on ``world`` CPU ranks; returns the list of results."""
+def run_ranks(fn, world: int, args=(), tmp_path=None, init: bool = True):
+    """Run ``fn(rank, world, *args)`` on ``world`` CPU ranks; returns the list of results.
+    ``init=False`` leaves the process group to ``fn`` (the rendezvous variables are set)."""
     result_dir = str(tmp_path)
-    mp.spawn(_entry, args=(world, free_port(), fn, args, result_dir), nprocs=world, join=True)
+    mp.spawn(_entry, args=(world, free_port(), fn, args, result_dir, init), nprocs=world, join=True)
     return [torch.load(os.path.join(result_dir, f"rank{r}.pt"), weights_only=False) for r in range(world)]

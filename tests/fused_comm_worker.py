@@ -12,6 +12,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from gpt_from_scratch_b200.config import GPTConfig  # noqa: E402
 from gpt_from_scratch_b200.engine import TrainEngine  # noqa: E402
 from gpt_from_scratch_b200.ops import _lib  # noqa: E402
+from gpt_from_scratch_b200.ops import gemm as gemm_ops  # noqa: E402
 from gpt_from_scratch_b200.parallel import fused_comm, mappings  # noqa: E402
 from gpt_from_scratch_b200.parallel import parallel_state as ps  # noqa: E402
 from gpt_from_scratch_b200.parallel.layers import VocabParallelEmbedding, linear_with_sink  # noqa: E402
@@ -26,6 +27,76 @@ def close(a, b, what, rel=2e-2):
     return float(err.detach())
 
 
+def operator_checks(S, B, K, N, pair_min, world, dev, g, log):
+    """AG->GEMM, GEMM->RS and the LM-head variant against their NCCL compositions at one shape."""
+    log(f"shapes S={S} B={B} K={K} N={N} pair_min_tiles={pair_min}")
+    Ss = S // world
+    # ---- all-gather -> GEMM (column parallel) ----
+    x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    dy = torch.randn(S, B, N, device=dev, generator=g).bfloat16()
+    dist.broadcast(dy, 0)   # the gradient w.r.t. a column-parallel output differs per rank in general; any value works
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    ya = fused_comm.allgather_linear(xa, wa)
+    ya.backward(dy)
+    xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+    yb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
+    yb.backward(dy)
+    torch.cuda.synchronize()
+    assert torch.equal(ya, yb), "AG->GEMM forward differs from NCCL all-gather + GEMM"
+    close(xa.grad, xb.grad, "AG->GEMM dX (GEMM->RS)")
+    close(wa.grad, wb.grad, "AG->GEMM dW", 1e-3)
+    log("allgather_linear ok")
+
+    # ---- GEMM -> reduce-scatter (row parallel) ----
+    xr = torch.randn(S, B, K, device=dev, generator=g).bfloat16()
+    wr = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    res = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+    dout = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
+    for use_res in (False, True):
+        xa, wa = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+        ra = res.clone().requires_grad_() if use_res else None
+        ya = fused_comm.linear_reduce_scatter(xa, wa, ra)
+        ya.backward(dout)
+        xb, wb = xr.clone().requires_grad_(), wr.clone().requires_grad_()
+        yb = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(xb, wb))
+        if use_res:
+            yb = yb + res
+        yb.backward(dout)
+        torch.cuda.synchronize()
+        close(ya, yb, f"GEMM->RS forward (residual={use_res})")
+        close(xa.grad, xb.grad, "GEMM->RS dX (AG->GEMM)", 1e-3)
+        close(wa.grad, wb.grad, "GEMM->RS dW", 1e-3)
+        if use_res:
+            assert torch.equal(ra.grad, dout)
+    log("linear_reduce_scatter ok")
+
+    # ---- LM head: all-gather -> GEMM with the cross-entropy statistics in its epilogue ----
+    if pair_min is not None:
+        Vp = 392                        # ragged last tile: 136 valid columns of 256
+        wl = (torch.randn(Vp, K, device=dev, generator=g) * 0.3).bfloat16()
+        tg = torch.randint(0, Vp * world, (S, B), device=dev,
+                           generator=torch.Generator(device="cuda").manual_seed(8))
+        prev_impl = ps.get_comm_impl()
+        ps.set_comm_impl("fused")
+        xa, wa = x.clone().requires_grad_(), wl.clone().requires_grad_()
+        la, parts_a = fused_comm.allgather_linear(xa, wa, ce_stats=True)
+        assert parts_a is not None, "LM-head epilogue statistics missing"
+        loss_a = vocab_parallel_cross_entropy(la, tg, parts_a)
+        loss_a.mean().backward()
+        ps.set_comm_impl("nccl")
+        xb, wb = x.clone().requires_grad_(), wl.clone().requires_grad_()
+        lb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
+        loss_b = vocab_parallel_cross_entropy(lb, tg)
+        loss_b.mean().backward()
+        torch.cuda.synchronize()
+        ps.set_comm_impl(prev_impl)
+        assert (loss_a - loss_b).abs().max().item() < 2e-3, (loss_a - loss_b).abs().max().item()
+        close(xa.grad, xb.grad, "LM head dX")
+        close(wa.grad, wb.grad, "LM head dW", 2e-3)
+        log("allgather_linear + cross-entropy statistics ok")
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -37,81 +108,11 @@ def main():
     log = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
 
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    from gpt_from_scratch_b200.ops import gemm as gemm_ops
     # second pass: shapes that qualify for the CTA-pair kernel (rows per rank a multiple of 256),
     # with its tile-count threshold lowered so that these small problems take it
     for S, B, K, N, pair_min in ((128 * world * 2, 2, 256, 384, None), (256 * world, 2, 256, 512, 1)):
-        saved_min = gemm_ops._PAIR_MIN_TILES
-        if pair_min is not None:
-            gemm_ops._PAIR_MIN_TILES = pair_min
-        log(f"shapes S={S} B={B} K={K} N={N} pair_min_tiles={gemm_ops._PAIR_MIN_TILES}")
-        Ss = S // world
-        # ---- all-gather -> GEMM (column parallel) ----
-        x = torch.randn(Ss, B, K, device=dev, generator=g).bfloat16()
-        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
-        dy = torch.randn(S, B, N, device=dev, generator=g).bfloat16()
-        dist.broadcast(dy, 0)   # the gradient w.r.t. a column-parallel output differs per rank in general; any value works
-        xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
-        ya = fused_comm.allgather_linear(xa, wa)
-        ya.backward(dy)
-        xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
-        yb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
-        yb.backward(dy)
-        torch.cuda.synchronize()
-        assert torch.equal(ya, yb), "AG->GEMM forward differs from NCCL all-gather + GEMM"
-        close(xa.grad, xb.grad, "AG->GEMM dX (GEMM->RS)")
-        close(wa.grad, wb.grad, "AG->GEMM dW", 1e-3)
-        log("allgather_linear ok")
-
-        # ---- GEMM -> reduce-scatter (row parallel) ----
-        xr = torch.randn(S, B, K, device=dev, generator=g).bfloat16()
-        wr = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
-        res = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
-        dout = torch.randn(Ss, B, N, device=dev, generator=g).bfloat16()
-        for use_res in (False, True):
-            xa, wa = xr.clone().requires_grad_(), wr.clone().requires_grad_()
-            ra = res.clone().requires_grad_() if use_res else None
-            ya = fused_comm.linear_reduce_scatter(xa, wa, ra)
-            ya.backward(dout)
-            xb, wb = xr.clone().requires_grad_(), wr.clone().requires_grad_()
-            yb = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(xb, wb))
-            if use_res:
-                yb = yb + res
-            yb.backward(dout)
-            torch.cuda.synchronize()
-            close(ya, yb, f"GEMM->RS forward (residual={use_res})")
-            close(xa.grad, xb.grad, "GEMM->RS dX (AG->GEMM)", 1e-3)
-            close(wa.grad, wb.grad, "GEMM->RS dW", 1e-3)
-            if use_res:
-                assert torch.equal(ra.grad, dout)
-        log("linear_reduce_scatter ok")
-
-        # ---- LM head: all-gather -> GEMM with the cross-entropy statistics in its epilogue ----
-        if pair_min is not None:
-            Vp = 392                        # ragged last tile: 136 valid columns of 256
-            wl = (torch.randn(Vp, K, device=dev, generator=g) * 0.3).bfloat16()
-            tg = torch.randint(0, Vp * world, (S, B), device=dev,
-                               generator=torch.Generator(device="cuda").manual_seed(8))
-            prev_impl = ps.get_comm_impl()
-            ps.set_comm_impl("fused")
-            xa, wa = x.clone().requires_grad_(), wl.clone().requires_grad_()
-            la = fused_comm.allgather_linear(xa, wa, ce_stats=True)
-            assert getattr(la, "_gfs_ce_partials", None) is not None, "LM-head epilogue statistics missing"
-            loss_a = vocab_parallel_cross_entropy(la, tg)
-            loss_a.mean().backward()
-            ps.set_comm_impl("nccl")
-            xb, wb = x.clone().requires_grad_(), wl.clone().requires_grad_()
-            lb = linear_with_sink(mappings.gather_from_sequence_parallel_region(xb), wb)
-            loss_b = vocab_parallel_cross_entropy(lb, tg)
-            loss_b.mean().backward()
-            torch.cuda.synchronize()
-            ps.set_comm_impl(prev_impl)
-            assert (loss_a - loss_b).abs().max().item() < 2e-3, (loss_a - loss_b).abs().max().item()
-            close(xa.grad, xb.grad, "LM head dX")
-            close(wa.grad, wb.grad, "LM head dW", 2e-3)
-            log("allgather_linear + cross-entropy statistics ok")
-
-        gemm_ops._PAIR_MIN_TILES = saved_min
+        with gemm_ops.pair_min_tiles(pair_min):       # None: the library's own threshold
+            operator_checks(S, B, K, N, pair_min, world, dev, g, log)
     S, B = 128 * world * 2, 2
     Ss = S // world
 

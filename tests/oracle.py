@@ -32,8 +32,9 @@ class NaiveAttention(nn.Module):
         H = cfg.hidden_size
         self.nh = cfg.num_attention_heads
         self.D = H // self.nh
-        self.qkv_proj = nn.Linear(H, 3 * H, bias=False)
-        self.out_proj = nn.Linear(H, H, bias=False)
+        bias = getattr(cfg, "bias", False)
+        self.qkv_proj = nn.Linear(H, 3 * H, bias=bias)
+        self.out_proj = nn.Linear(H, H, bias=bias)
         freqs = 1.0 / (10000.0 ** (torch.arange(0, self.D, 2, dtype=torch.float32) / self.D))
         self.rotary_emb = nn.Module()
         self.rotary_emb.register_buffer("freqs", freqs)
@@ -53,8 +54,9 @@ class NaiveAttention(nn.Module):
 class NaiveMLP(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.gate_up_proj = nn.Linear(cfg.hidden_size, 2 * cfg.intermediate_size, bias=False)
-        self.down_proj = nn.Linear(cfg.intermediate_size, cfg.hidden_size, bias=False)
+        bias = getattr(cfg, "bias", False)
+        self.gate_up_proj = nn.Linear(cfg.hidden_size, 2 * cfg.intermediate_size, bias=bias)
+        self.down_proj = nn.Linear(cfg.intermediate_size, cfg.hidden_size, bias=bias)
 
     def forward(self, x):
         g, u = self.gate_up_proj(x).chunk(2, dim=-1)

@@ -20,16 +20,24 @@ def _tokens(step, dp_rank, dp_size):
     return t[:, :-1].contiguous(), t[:, 1:].contiguous()
 
 
-def _worker(rank, world, tp, grad_reduce):
+def _worker(rank, world, tp, grad_reduce, bias=False):
     from gpt_from_scratch_b200.config import GPTConfig
     from gpt_from_scratch_b200.engine import TrainEngine
     from gpt_from_scratch_b200.parallel import parallel_state as ps
     from gpt_from_scratch_b200.utils.reshard import merge_state_dicts
     ps.set_device("cpu")
     ps.initialize_parallel_state(tp)
-    cfg = GPTConfig(**CFG, init_method="normal", attention_impl="torch")
+    cfg = GPTConfig(**CFG, init_method="normal", attention_impl="torch", bias=bias)
     eng = TrainEngine(cfg, lr=LR, weight_decay=0.1, clip_grad=CLIP, dtype=torch.float32, grad_reduce=grad_reduce,
                       seed=11)
+    if bias:
+        # biases start at zero; give them distinct values so a missing gradient shows
+        with torch.no_grad():
+            for n, p in eng.model.named_parameters():
+                if n.endswith(".bias"):
+                    p.copy_(torch.linspace(-0.05, 0.05, p.numel()).view(p.shape) * (1 + (len(n) % 3)))
+        eng.optimizer.fp32_master_shard.data.copy_(
+            eng.optimizer.param_buffer[eng.optimizer.shard_start:eng.optimizer.shard_end])
     sd0 = {k: v.clone() for k, v in eng.model.state_dict().items()}
     gathered = [None] * world
     dist.all_gather_object(gathered, sd0)
@@ -58,9 +66,9 @@ def _worker(rank, world, tp, grad_reduce):
     return {"losses": losses, "full0": full0, "full1": full1}
 
 
-def _oracle(full0, dp_size, scale_lossgrad=1.0):
+def _oracle(full0, dp_size, scale_lossgrad=1.0, bias=False):
     from gpt_from_scratch_b200.config import GPTConfig
-    cfg = GPTConfig(**CFG)
+    cfg = GPTConfig(**CFG, bias=bias)
     torch.manual_seed(0)
     m = NaiveGPT(cfg)
     missing = m.load_state_dict(full0, strict=True)
@@ -84,6 +92,23 @@ def test_matches_unsharded_oracle(tmp_path, world, tp):
     for k, v in ref_sd.items():
         err = (res[0]["full1"][k] - v).abs().max().item()
         assert err < 5e-5, f"{k}: {err}"
+
+
+def test_bias_parameters_train_like_the_oracle(tmp_path):
+    """bias=True: column biases are sharded, row biases are replicated over TP and see only their
+    sequence shard's gradient, which the optimizer sums over the TP group."""
+    torch.set_num_threads(2)
+    res = run_ranks(_worker, 2, args=(2, "mean", True), tmp_path=tmp_path)
+    ref_losses, ref_sd = _oracle(res[0]["full0"], 1, bias=True)
+    for a, b in zip(res[0]["losses"], ref_losses):
+        assert abs(a - b) < 2e-4, (res[0]["losses"], ref_losses)
+    moved = 0
+    for k, v in ref_sd.items():
+        err = (res[0]["full1"][k] - v).abs().max().item()
+        assert err < 5e-5, f"{k}: {err}"
+        if k.endswith(".bias"):
+            moved += int((res[0]["full1"][k] - res[0]["full0"][k]).abs().max().item() > 1e-4)
+    assert moved >= 8    # 4 biases per layer, 2 layers: all of them trained
 
 
 def test_sum_reduction_matches_reference_semantics(tmp_path):

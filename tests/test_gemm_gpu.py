@@ -135,16 +135,12 @@ def test_grouped_weight_gradients(cuda_device):
         sinks.append(Sink(flat[off:off + o * i].view(o, i), accumulate=(n == 1)))
         operands.append((dy, x))
         off += o * i
-    saved = gemm_ops._PAIR_MIN_TILES
-    gemm_ops._PAIR_MIN_TILES = 10 ** 6   # park everything until the explicit flush
-    try:
+    with gemm_ops.pair_min_tiles(10 ** 6):   # park everything until the explicit flush
         for n, ((dy, x), sk) in enumerate(zip(operands, sinks)):
             gemm_ops.linear_wgrad_to_sink(dy, x, sk)
             if n == 2:
                 assert not any(s_.finished for s_ in sinks)   # parked, nothing launched yet
         gemm_ops.flush_wgrad()   # (the fourth problem filled the group and launched it already)
-    finally:
-        gemm_ops._PAIR_MIN_TILES = saved
     torch.cuda.synchronize()
     off = 0
     for n, ((dy, x), sk, (o, i)) in enumerate(zip(operands, sinks, shapes)):

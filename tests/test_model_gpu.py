@@ -146,6 +146,39 @@ def test_training_matches_fp32_oracle(cuda_device):
         assert rel < 2e-2, f"{k}: {rel}"
 
 
+def test_training_with_bias_matches_fp32_oracle(cuda_device):
+    """bias=True: the bias gradients come through plain autograd while the weight gradients go to
+    gradient sinks; with the lazy gradient-buffer clearing both must still track the oracle."""
+    from oracle import NaiveGPT, naive_step
+    from gpt_from_scratch_b200.config import GPTConfig
+    from gpt_from_scratch_b200.engine import TrainEngine
+    from gpt_from_scratch_b200.parallel import parallel_state as ps
+    ps.set_device(cuda_device)
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_parallel_state(1)
+    cfg = GPTConfig(vocab_size=512, hidden_size=256, num_layers=2, num_attention_heads=4,
+                    max_position_embeddings=128, intermediate_size=512, init_method="normal", bias=True)
+    eng = TrainEngine(cfg, lr=1e-3, clip_grad=1.0, seed=5)
+    full0 = {k: v.detach().float().cpu() for k, v in eng.model.state_dict().items()}
+    oracle = NaiveGPT(cfg)
+    oracle.load_state_dict(full0)
+    opt = torch.optim.AdamW(oracle.parameters(), lr=1e-3, weight_decay=0.1, betas=(0.9, 0.95))
+    g = torch.Generator().manual_seed(3)
+    for i in range(6):
+        t = torch.randint(0, 512, (4, 129), generator=g)
+        x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
+        a = float(eng.train_step(x.cuda(), y.cuda()))
+        b = float(naive_step(oracle, opt, x, y, 1.0))
+        assert abs(a - b) < 3e-2, (i, a, b)
+    sd = eng.model.state_dict()
+    for k, v in oracle.state_dict().items():
+        if k.endswith(".bias"):
+            # biases start at zero and move by about lr per step: compare the movement itself
+            err = (sd[k].float().cpu() - v).abs().max().item()
+            assert v.abs().max().item() > 1e-3, f"{k} did not train in the oracle"
+            assert err < 0.35 * v.abs().max().item() + 2e-4, f"{k}: {err} vs {v.abs().max().item()}"
+
+
 def test_checkpoint_roundtrip_gpu(cuda_device, tmp_path):
     from gpt_from_scratch_b200.checkpoint import load_checkpoint, save_checkpoint
     from gpt_from_scratch_b200.config import GPTConfig
@@ -180,12 +213,8 @@ def test_lm_head_epilogue_ce_statistics(cuda_device, M, K, N):
     x = torch.randn(M, K, device=cuda_device, generator=g).bfloat16()
     w = (torch.randn(N, K, device=cuda_device, generator=g) * 0.2).bfloat16()
     tgt = torch.randint(0, N, (M,), device=cuda_device, generator=g)
-    saved = gemm_ops._PAIR_MIN_TILES
-    gemm_ops._PAIR_MIN_TILES = 1
-    try:
+    with gemm_ops.pair_min_tiles(1):
         logits, partials = gemm_ops.linear_fwd_ce(x, w)
-    finally:
-        gemm_ops._PAIR_MIN_TILES = saved
     assert partials is not None
     ref_logits = x.float() @ w.float().t()
     assert (logits.float() - ref_logits).abs().max() <= 2e-2 * ref_logits.abs().max() + 1e-3

@@ -39,15 +39,40 @@ def test_flash_attention_fwd_bwd(cuda_device, B, nh, S, D):
         assert rel < 2e-2, f"{name}: relative error {rel:.4g}"
 
 
-@pytest.mark.parametrize("causal", [True, False])
-def test_flash_attention_growing_scores(cuda_device, causal):
+def test_flash_attention_fp16_inputs_run_the_native_kernels(cuda_device):
+    """fp16 in, fp16 out (the reference's self-test dtype): served by the bf16 kernels, never by the
+    eager fallback; compared against the fp32 oracle with the reference's tolerances."""
+    from gpt_from_scratch_b200.ops import _lib
+    from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
+    g = torch.Generator(device="cuda").manual_seed(77)
+    B, nh, S, D = 2, 3, 256, 64
+    q, k, v = (torch.randn(B, nh, S, D, device=cuda_device, generator=g).half().requires_grad_() for _ in range(3))
+    do = torch.randn(B, nh, S, D, device=cuda_device, generator=g).half()
+    before = _lib.launch_count()
+    o = apply_flash_attn(q, k, v, True)
+    o.backward(do)
+    assert _lib.launch_count() - before >= 2 and o.dtype == torch.float16 and q.grad.dtype == torch.float16
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = attention_reference(qf, kf, vf, True)
+    of.backward(do.float())
+    _close(o, of, 2e-2, what="O")
+    for name, a, b in (("O", o, of), ("dQ", q.grad, qf.grad), ("dK", k.grad, kf.grad), ("dV", v.grad, vf.grad)):
+        _close(a, b, 5e-2, what=name)
+        rel = (a.float() - b).norm() / (b.norm() + 1e-12)
+        assert rel < 2e-2, f"{name}: relative error {rel:.4g}"
+    with pytest.raises(ValueError):
+        apply_flash_attn(q[..., :32], k[..., :32], v[..., :32], True)
+
+
+@pytest.mark.parametrize("causal,D", [(True, 64), (False, 64), (True, 128)])
+def test_flash_attention_growing_scores(cuda_device, causal, D):
     """Keys whose magnitude grows along the sequence: the row maximum rises by far more than 2^8
     from one key block to the next, so the head_dim-64 forward has to rescale the output it
     accumulates in tensor memory (with random-normal inputs the maximum settles in the first
     block and that path never runs). Some rows get a negative query, so their maximum stays."""
     from gpt_from_scratch_b200.ops.attention import apply_flash_attn, attention_reference
     g = torch.Generator(device="cuda").manual_seed(11)
-    B, nh, S, D = 2, 3, 640, 64
+    B, nh, S = 2, 3, 640
     q = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
     k = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
     v = torch.randn(B, nh, S, D, device=cuda_device, generator=g)
@@ -199,13 +224,9 @@ def test_swiglu_gemm_epilogues(cuda_device, M, H, I, pair):
     w_gu = (torch.randn(2 * I, H, device=cuda_device, generator=g) * 0.05).bfloat16()
     w_dn = (torch.randn(H, I, device=cuda_device, generator=g) * 0.05).bfloat16()
     dy = torch.randn(M, H, device=cuda_device, generator=g).bfloat16()
-    saved = gemm_ops._PAIR_MIN_TILES
-    gemm_ops._PAIR_MIN_TILES = 1 if pair else 10 ** 9
-    try:
+    with gemm_ops.pair_min_tiles(1 if pair else 10 ** 9):
         gu, act = swiglu_gemm_fwd(x, w_gu)
         dgu = swiglu_gemm_bwd(dy, w_dn, gu)
-    finally:
-        gemm_ops._PAIR_MIN_TILES = saved
     gu_ref = x.float() @ w_gu.float().t()
     _close(gu, gu_ref, 2e-2, 2e-2, what="gate_up projection")
     guf = gu.float().requires_grad_()          # the kernels compute act and the gradient from the bf16 projection

@@ -29,7 +29,7 @@ def test_parallel_state_single_process():
         ps.initialize_parallel_state(2)
 
 
-def test_flops_and_param_count_match_survey_numbers():
+def test_flops_and_param_count_of_the_three_model_shapes():
     cfg = GPTConfig()
     assert abs(cfg.flops_per_token(1024) / 1e9 - 0.968) < 1e-3
     assert abs(cfg.num_parameters() / 1e6 - 190.5) < 0.1
@@ -307,3 +307,23 @@ def test_collective_site_keys_follow_program_order():
     kp = fused_comm._weight_site_key(p)
     p.data = torch.ones(2, 2)                              # re-pointing the storage keeps the key
     assert fused_comm._weight_site_key(p) == kp
+
+
+def test_lazy_zero_grad_clears_slices_written_by_plain_autograd():
+    """With the kernel path's lazy ``zero_grad`` (no memset) a gradient that arrives through plain
+    autograd must not be added onto the previous step's values."""
+    from gpt_from_scratch_b200.optimizer import DistributedOptimizer
+    lin = torch.nn.Linear(4, 3, bias=True)
+    opt = DistributedOptimizer(lin, torch.optim.AdamW, {"lr": 1e-3}, dtype=torch.float32, fused=True)
+    x = torch.ones(2, 4)
+    for _ in range(3):
+        opt.zero_grad()
+        lin(x).sum().backward()
+        assert torch.equal(lin.bias.grad, torch.full((3,), 2.0))
+        assert torch.equal(lin.weight.grad, torch.full((3, 4), 2.0))
+        opt._materialise_unwritten()                      # what step() does before it reads the buffer
+        assert torch.equal(lin.bias.grad, torch.full((3,), 2.0))
+    # a parameter nothing wrote in a step reads as zero
+    opt.zero_grad()
+    opt._materialise_unwritten()
+    assert float(lin.bias.grad.abs().sum()) == 0.0

@@ -19,6 +19,7 @@ from gpt_from_scratch_b200.config import GPTConfig
 from gpt_from_scratch_b200.data import PrefetchLoader, create_distributed_dataloader, write_synthetic_tokens
 from gpt_from_scratch_b200.engine import TrainEngine
 from gpt_from_scratch_b200.parallel import parallel_state as ps
+from gpt_from_scratch_b200.utils.health import default_heartbeat
 from gpt_from_scratch_b200.utils.logging import JsonlLogger, format_step_line, print_rank0
 
 
@@ -64,6 +65,9 @@ def parse_args(argv=None):
     p.add_argument("--load", type=str, default=None, help="checkpoint directory to resume from")
     p.add_argument("--log-jsonl", type=str, default=None)
     p.add_argument("--peak-tflops", type=float, default=None, help="per-GPU peak for the MFU column")
+    p.add_argument("--heartbeat-timeout", type=float, default=300.0,
+                   help="seconds a peer may lag behind at a log interval before PeerFailure is raised "
+                        "(0 disables the heartbeat)")
     return p.parse_args(argv)
 
 
@@ -125,11 +129,14 @@ def main(argv=None):
 
     step = 0
     epoch = 0
+    batches_in_epoch = 0      # batches of the current epoch already consumed (saved for resume)
     if args.load and latest_step(args.load) is not None:
         payload = load_checkpoint(args.load, engine.model, engine.optimizer)
         step = payload["step"]
         epoch = payload.get("extra", {}).get("epoch", 0)
-        print_rank0(f"Resumed from {args.load} at step {step}")
+        batches_in_epoch = payload.get("extra", {}).get("batches_in_epoch", 0)
+        print_rank0(f"Resumed from {args.load} at step {step} (epoch {epoch}, batch {batches_in_epoch})")
+    heartbeat = default_heartbeat(args.heartbeat_timeout) if args.heartbeat_timeout > 0 else None
     print_rank0(f"Starting training for {args.max_steps} steps...")
 
     jsonl = JsonlLogger(args.log_jsonl)
@@ -140,6 +147,11 @@ def main(argv=None):
     flops_per_token = config.flops_per_token(args.seq_len)
     while step < args.max_steps:
         sampler.set_epoch(epoch)
+        if batches_in_epoch:
+            if batches_in_epoch >= len(loader):     # the checkpoint was written at the epoch's last batch
+                epoch, batches_in_epoch = epoch + 1, 0
+                continue
+            sampler.skip_samples(batches_in_epoch * args.batch_size)
         for batch in batches:
             if step >= args.max_steps:
                 break
@@ -147,8 +159,15 @@ def main(argv=None):
             labels = batch["label"].to(device, non_blocking=True)
             loss = engine.train_step(inputs, labels)
             step += 1
+            batches_in_epoch += 1
             log_loss += loss.float()
+            if heartbeat is not None:
+                heartbeat.beat(step)
             if step % args.log_interval == 0:
+                if heartbeat is not None:
+                    # every peer must have finished this step before the next collective is
+                    # launched: raises PeerFailure instead of hanging on a dead or stalled rank
+                    heartbeat.wait_for_peers(step)
                 avg_loss = float(log_loss) / args.log_interval     # one host sync per log interval
                 elapsed = time.time() - log_start
                 tps = args.log_interval * args.batch_size * args.seq_len * dp / elapsed
@@ -169,12 +188,15 @@ def main(argv=None):
                 log_loss.zero_()
                 log_start = time.time()
             if args.save_dir and args.save_interval and step % args.save_interval == 0:
-                save_checkpoint(args.save_dir, step, engine.model, engine.optimizer, {"epoch": epoch})
+                save_checkpoint(args.save_dir, step, engine.model, engine.optimizer,
+                                {"epoch": epoch, "batches_in_epoch": batches_in_epoch})
         epoch += 1
+        batches_in_epoch = 0
 
     print_rank0("Training finished.")
     jsonl.close()
     if dist.is_initialized():
+        dist.barrier()      # rank 0 hosts the key-value store: it must not leave while peers still read it
         dist.destroy_process_group()
 
 
