@@ -17,7 +17,9 @@ same workload with the same timing harness and prints the same JSON line.
 
 The JSON line carries two measurements: ``value`` (inputs already resident on the device)
 and ``e2e`` (every step copies its token batch from pinned host memory and reads the loss
-back to the host).
+back to the host). With N >= 2 GPUs and the default config the same processes then rebuild the
+model as TP=2 (+ sequence parallel) x DP=N/2 with micro-batch 8 and report that layout's numbers
+under ``"tp"`` (same fields), for either ``--impl``.
 """
 from __future__ import annotations
 
@@ -59,6 +61,10 @@ def parse_args():
     p.add_argument("--micro-batch", type=int, default=None)
     p.add_argument("--comm-impl", choices=["fused", "nccl"], default=None)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-graph", action="store_true",
+                   help="ours: launch every kernel from Python instead of replaying the captured step")
+    p.add_argument("--no-tp", action="store_true",
+                   help="skip the tensor-parallel (TP2 x DP N/2) sub-measurement that runs for N >= 2")
     return p.parse_args()
 
 
@@ -173,7 +179,7 @@ def build_ours(cfgd, args, world):
                     num_attention_heads=cfgd["num_attention_heads"], max_position_embeddings=cfgd["seq_len"],
                     intermediate_size=cfgd["intermediate_size"])
     engine = TrainEngine(cfg, lr=3e-4, weight_decay=0.1, betas=(0.9, 0.95), clip_grad=1.0, dtype=torch.bfloat16,
-                         seed=1234)
+                         seed=1234, cuda_graph=not args.no_graph, graph_warmup=2)
 
     def step_fn(x, y):
         return engine.train_step(x, y)
@@ -228,26 +234,30 @@ def build_reference(cfgd, args):
     return step_fn, None
 
 
-def main():
-    args = parse_args()
-    cfgd = dict(CONFIGS[args.config])
-    if args.tp:
-        cfgd["tp"] = args.tp
-    if args.micro_batch:
-        cfgd["micro_batch"] = args.micro_batch
-    if not torch.cuda.is_available():
-        if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}))
-            return
-        raise SystemExit("bench.py needs a CUDA device")
-    rank, world, local_rank = setup_dist(args.gpus, force_init=(args.impl == "reference"))
+def release_ours():
+    """Drop the engine of a finished measurement (model, optimizer, symmetric buffers, groups) so
+    the next layout can be built in the same processes."""
+    import gc
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    from gpt_from_scratch_b200.parallel import parallel_state as ps
+    from gpt_from_scratch_b200.parallel import symm
+    gemm_ops.flush_wgrad()
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    symm.reset()
+    ps.destroy_model_parallel()
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def measure(config_name: str, cfgd: dict, args, rank: int, world: int, local_rank: int, with_e2e: bool):
+    """Build the model in layout ``cfgd`` for ``args.impl`` and time it. Returns the fields of the
+    JSON line that depend on the layout (``None`` plus a reason if the reference is unavailable)."""
+    from gpt_from_scratch_b200.utils.timing import ClockSampler   # timing harness only (no kernels)
     tp = cfgd["tp"]
-    if world % tp != 0:
-        raise SystemExit(f"{world} GPUs cannot host TP={tp}")
     dp = world // tp
     B, S = cfgd["micro_batch"], cfgd["seq_len"]
-
-    from gpt_from_scratch_b200.utils.timing import ClockSampler   # timing harness only (no kernels)
     launches = None
     check = None
     comm = "nccl"
@@ -256,9 +266,7 @@ def main():
     else:
         step_fn, why = build_reference(cfgd, args)
         if step_fn is None:
-            if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": why}))
-            return
+            return None, why
 
     # TP peers read the same batch, DP replicas different ones
     dp_rank = rank // tp
@@ -273,7 +281,7 @@ def main():
     ms_dev, _ = timed_loop(step_fn, batches, args.steps, "device")
     n_launch = (launches() - l0) if launches else None
     e2e = None
-    if not args.no_e2e:
+    if with_e2e:
         ms_e2e, last_loss = timed_loop(step_fn, batches, args.steps, "e2e")
     clocks = sampler.stop() if sampler else None
     if check:
@@ -283,35 +291,97 @@ def main():
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     fpt = flops_per_token(cfgd)
     peak = measured_peak_tflops()
-    if not args.no_e2e:
+    if with_e2e:
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss,
                "loss_read": ("asynchronous copy to pinned memory every step, value read one step later "
                              "(TrainEngine.train_step_async)" if args.impl == "ours" else
                              "blocking read every step")}
+    par = (f"tp{tp}" if tp > 1 else "") + (f"dp{dp}" if (dp > 1 or tp == 1) else "")
+    out = {
+        "value": value, "unit": "tokens/s", "ms_per_step": ms_dev / args.steps,
+        "config": {"model": config_name, "layers": cfgd["num_layers"], "hidden": cfgd["hidden_size"],
+                   "heads": cfgd["num_attention_heads"], "ffn": cfgd["intermediate_size"],
+                   "vocab": cfgd["vocab_size"], "global_batch": B * dp, "micro_batch": B, "seq_len": S,
+                   "parallelism": par, "optimizer": "AdamW, fp32 master weights, sharded over DP, clip 1.0",
+                   "l2": "per-step working set (weights+grads+activations, >2 GB) exceeds the 126 MB L2; "
+                         "no explicit flush"},
+        # how the collectives and the launches are done: implementation labels, not workload
+        "comm_impl": comm,
+        "step_launch": ("CUDA graph replay of the whole step" if (args.impl == "ours" and not args.no_graph)
+                        else "one host launch per kernel"),
+        "mfu_of_measured_peak": (value * fpt / (world * peak * 1e12)) if peak else None,
+        "flops_per_token": fpt,
+        "clocks": clocks,
+        "e2e": e2e,
+        "gpu_launches": n_launch,
+    }
+    del step_fn
+    return out, None
+
+
+def main():
+    args = parse_args()
+    cfgd = dict(CONFIGS[args.config])
+    if args.tp:
+        cfgd["tp"] = args.tp
+    if args.micro_batch:
+        cfgd["micro_batch"] = args.micro_batch
+    if not torch.cuda.is_available():
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}))
+            return
+        raise SystemExit("bench.py needs a CUDA device")
+    rank, world, local_rank = setup_dist(args.gpus, force_init=(args.impl == "reference"))
+    if world % cfgd["tp"] != 0:
+        raise SystemExit(f"{world} GPUs cannot host TP={cfgd['tp']}")
+
+    head, why = measure(args.config, cfgd, args, rank, world, local_rank, with_e2e=not args.no_e2e)
+    if head is None:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return
+
+    # Second layout of the same model on the same GPUs: tensor parallel 2 (+ sequence parallel) x
+    # data parallel N/2, micro-batch 8 per DP rank. It exercises the tensor-parallel collectives
+    # (all-gather -> GEMM, GEMM -> reduce-scatter, embedding, cross entropy), which the data-parallel
+    # headline layout does not touch. Reported under "tp"; the headline fields are unaffected.
+    tp_block = None
+    if world >= 2 and world % 2 == 0 and args.config == "gpt124m" and not args.tp and not args.no_tp:
+        if args.impl == "ours":
+            release_ours()
+        else:
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+        tcfg = dict(CONFIGS["gpt124m_tp2"])
+        try:
+            tp_block, why = measure("gpt124m_tp2", tcfg, args, rank, world, local_rank, with_e2e=not args.no_e2e)
+            if tp_block is None:
+                tp_block = {"unavailable": why}
+        except Exception as e:  # noqa: BLE001 - the headline number must survive a failure here
+            tp_block = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
     if rank == 0:
-        par = (f"tp{tp}" if tp > 1 else "") + (f"dp{dp}" if (dp > 1 or tp == 1) else "")
         line = {
             "metric": "train tokens/sec (whole job, device-timed, max over ranks)",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
+            "value": head["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random token ids in [0,50257), random-init weights",
-            "config": {"model": args.config, "layers": cfgd["num_layers"], "hidden": cfgd["hidden_size"],
-                       "heads": cfgd["num_attention_heads"], "ffn": cfgd["intermediate_size"],
-                       "vocab": cfgd["vocab_size"], "global_batch": B * dp, "micro_batch": B, "seq_len": S,
-                       "parallelism": par, "optimizer": "AdamW, fp32 master weights, sharded over DP, clip 1.0",
-                       "comm_impl": comm,
-                       "l2": "per-step working set (weights+grads+activations, >2 GB) exceeds the 126 MB L2; "
-                             "no explicit flush"},
+            "config": head["config"],
             "impl": args.impl,
-            "mfu_of_measured_peak": (value * fpt / (world * peak * 1e12)) if peak else None,
-            "flops_per_token": fpt,
-            "clocks": clocks,
-            "e2e": e2e,
-            "gpu_launches": n_launch,
+            "comm_impl": head["comm_impl"],
+            "step_launch": head["step_launch"],
+            "mfu_of_measured_peak": head["mfu_of_measured_peak"],
+            "flops_per_token": head["flops_per_token"],
+            "clocks": head["clocks"],
+            "e2e": head["e2e"],
+            "gpu_launches": head["gpu_launches"],
         }
+        if tp_block is not None:
+            line["tp"] = tp_block
         print(json.dumps(line))
     if dist.is_initialized():
         dist.destroy_process_group()

@@ -202,12 +202,6 @@ dp_reduce_norm_kernel(PeerTable grads, PeerTable norm, __nv_bfloat16* __restrict
   }
 }
 
-struct AdamArgs {
-  float lr, beta1, beta2, eps, weight_decay;
-  float bias_corr1, bias_corr2_sqrt;
-  float clip, grad_scale;
-};
-
 // Phase 2: wait for every rank's squared-norm, clip, AdamW on the fp32 master shard, and
 // write the bf16 parameters into every rank's parameter buffer (all-gather by peer
 // stores). Ends with a signal/wait so that when the kernel completes, this rank's own
@@ -238,8 +232,10 @@ dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __r
   }
   __syncthreads();
   const float coef = s_coef;
+  float bc1, bc2_sqrt;
+  adam_bias_corrections(a, bc1, bc2_sqrt);
   const float decay = 1.f - a.lr * a.weight_decay;
-  const float step = a.lr / a.bias_corr1;
+  const float step = a.lr / bc1;
   const float ob1 = 1.f - a.beta1, ob2 = 1.f - a.beta2;
   const long long nvec = n >> 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
@@ -256,7 +252,7 @@ dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __r
       pp[e] *= decay;
       mm[e] = a.beta1 * mm[e] + ob1 * g[e];
       vv[e] = a.beta2 * vv[e] + ob2 * g[e] * g[e];
-      pp[e] -= step * (mm[e] / (sqrtf(vv[e]) / a.bias_corr2_sqrt + a.eps));
+      pp[e] -= step * (mm[e] / (sqrtf(vv[e]) / bc2_sqrt + a.eps));
     }
     reinterpret_cast<float4*>(master)[i] = p;
     reinterpret_cast<float4*>(exp_avg)[i] = m;
@@ -370,19 +366,21 @@ int gfs_dp_reduce_norm(const unsigned long long* peer_grads, const unsigned long
 // extern_sumsq: device scalar with the global squared gradient norm computed elsewhere
 // (e.g. reduced over tensor-parallel ranks as well), or null to use the per-rank values
 // exchanged by gfs_dp_reduce_norm (target_norm = the value that call left in its counter).
+// step_dev: as in gfs_adamw_step (loss_optim.cu).
 int gfs_dp_adam_gather(const unsigned long long* peer_params, const unsigned long long* peer_flags,
                        const unsigned long long* peer_norm_slots, const void* reduced, void* master, void* exp_avg,
                        void* exp_avg_sq, long long shard_start, long long shard_numel, int world, int rank,
                        int slot_norm, unsigned int target_norm, int slot_param, unsigned int* target_param_inout,
-                       const void* extern_sumsq, void* norm_out, float lr, float beta1, float beta2, float eps,
+                       const void* extern_sumsq, void* norm_out, float lr, double beta1, double beta2, float eps,
                        float weight_decay, float bias_corr1, float bias_corr2_sqrt, float clip, float grad_scale,
-                       long long wait_ns, void* stream) {
+                       const void* step_dev, long long wait_ns, void* stream) {
   PeerTable pr, nm;
   if (fill_table(pr, peer_params, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
   if ((shard_numel & 7) || (shard_start & 7)) return -1;
   const int grid = resident_grid(static_cast<int>(((shard_numel >> 2) + 255) / 256));
   *target_param_inout += static_cast<unsigned int>(grid);
-  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2_sqrt, clip, grad_scale};
+  AdamArgs a{lr, static_cast<float>(beta1), static_cast<float>(beta2), eps, weight_decay, bias_corr1,
+             bias_corr2_sqrt, clip, grad_scale, static_cast<const float*>(step_dev), beta1, beta2};
   dp_adam_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pr, nm, static_cast<const __nv_bfloat16*>(reduced), static_cast<float*>(master), static_cast<float*>(exp_avg),
       static_cast<float*>(exp_avg_sq), shard_start, shard_numel, world, rank, slot_norm, target_norm, slot_param,

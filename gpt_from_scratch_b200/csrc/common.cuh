@@ -369,8 +369,17 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // ----------------------------------------------------------------------------
 // Cross-GPU flags (peer memory over NVLink). Counters only grow; a waiter compares
-// against a cumulative target kept by the host, so no flag is ever reset.
+// against a cumulative target, so no flag is ever reset.
+//
+// Layout of a rank's flag array: FLAG_SLOTS counters followed by FLAG_SLOTS "base" words, one per
+// counter. The value a counter must reach is  base[slot] + target  where `target` is the kernel
+// argument the host computed. In ordinary (eager) launches the base words are zero and `target` is
+// the host's cumulative count. A step captured in a CUDA graph replays with frozen kernel
+// arguments: there `target` is the count relative to the start of the step and the last node of
+// the graph adds the step's total to the base words, so every replay waits for the right value.
+// Base words are local (only this rank's kernels read or write them).
 // ----------------------------------------------------------------------------
+constexpr uint32_t FLAG_SLOTS = 8192;
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -388,6 +397,7 @@ __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t ta
                                                   uint32_t* status, uint32_t detail) {
   uint32_t it = 0;
   uint64_t t0 = 0;
+  target += *reinterpret_cast<const volatile uint32_t*>(p + FLAG_SLOTS);   // this counter's base word
   while (true) {
     if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
     __nanosleep(64);
@@ -402,6 +412,34 @@ __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t ta
     }
   }
 }
+// Hyper-parameters of one AdamW update. The bias corrections are either given by the host
+// (bias_corr1 = 1 - beta1^t, bias_corr2_sqrt = sqrt(1 - beta2^t)) or, when `step_dev` is set,
+// computed by the kernel from the step count t kept in device memory, so that a launch captured
+// in a CUDA graph (frozen arguments) still sees the current step on every replay.
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_corr1, bias_corr2_sqrt;
+  float clip, grad_scale;
+  const float* step_dev;
+  double beta1_d, beta2_d;
+};
+// Called by all threads of the CTA (contains a __syncthreads when step_dev is set).
+__device__ __forceinline__ void adam_bias_corrections(const AdamArgs& a, float& bc1, float& bc2_sqrt) {
+  bc1 = a.bias_corr1;
+  bc2_sqrt = a.bias_corr2_sqrt;
+  if (a.step_dev != nullptr) {
+    __shared__ float s_bc[2];
+    if (threadIdx.x == 0) {
+      const double t = static_cast<double>(*a.step_dev);
+      s_bc[0] = static_cast<float>(1.0 - pow(a.beta1_d, t));
+      s_bc[1] = static_cast<float>(sqrt(1.0 - pow(a.beta2_d, t)));
+    }
+    __syncthreads();
+    bc1 = s_bc[0];
+    bc2_sqrt = s_bc[1];
+  }
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads);
 
 // First step of a fused all-gather -> GEMM: the calling threads (`nthreads` of this CTA, the caller

@@ -44,6 +44,14 @@ int encode_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a driver-API call on a thread that has made no runtime call yet (e.g. the first operator an
+    // autograd worker thread runs): bind the device's primary context to the thread and retry
+    cudaFree(nullptr);
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     fprintf(stderr, "[gfs] cuTensorMapEncodeTiled failed: %d (rank %d base %p dims %llu %llu box %u %u)\n", (int)r,
             rank, base, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0), box[0],
@@ -174,6 +182,10 @@ extern "C" {
 
 // Reads (and optionally clears) the status words of the current device. Synchronises
 // the device. out must hold 2 uint32: [code, detail]. Returns the code.
+// Number of counters in a flag array; the array handed to the fused collectives must hold twice
+// as many uint32 words (counters, then their base words: see common.cuh).
+int gfs_flag_slots() { return static_cast<int>(gfs::FLAG_SLOTS); }
+
 int gfs_read_status(uint32_t* out, int clear) {
   uint32_t* p = gfs_host::status_words();
   uint32_t h[2] = {0, 0};

@@ -260,11 +260,6 @@ sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long n, float* __res
   }
 }
 
-struct AdamArgs {
-  float lr, beta1, beta2, eps, weight_decay;
-  float bias_corr1, bias_corr2_sqrt;
-  float clip, grad_scale;
-};
 
 // g <- grad * grad_scale * clip_coef (clip_coef from the device scalar *sumsq, which holds the
 // squared norm of grad * grad_scale... see launcher), then torch.optim.AdamW's update on the fp32
@@ -279,15 +274,17 @@ __global__ void adamw_kernel(const __nv_bfloat16* __restrict__ grad, float* __re
     if (norm_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *norm_out = norm;
     if (a.clip > 0.f && norm > a.clip) coef *= a.clip / (norm + 1e-6f);
   }
+  float bc1, bc2_sqrt;
+  adam_bias_corrections(a, bc1, bc2_sqrt);
   const float decay = 1.f - a.lr * a.weight_decay;
-  const float step = a.lr / a.bias_corr1;
+  const float step = a.lr / bc1;
   const float ob1 = 1.f - a.beta1, ob2 = 1.f - a.beta2;
   auto update = [&](float g, float& p, float& m, float& v) {
     g *= coef;
     p *= decay;
     m = a.beta1 * m + ob1 * g;
     v = a.beta2 * v + ob2 * g * g;
-    p -= step * (m / (sqrtf(v) / a.bias_corr2_sqrt + a.eps));
+    p -= step * (m / (sqrtf(v) / bc2_sqrt + a.eps));
   };
   // vector body: 4 elements per thread (8-byte bf16 and 16-byte fp32 accesses); all four
   // arrays are 16-byte aligned slices when n's base offset is a multiple of 4 elements
@@ -389,13 +386,16 @@ int gfs_sumsq_bf16(const void* x, long long n, void* out, void* scratch, void* s
 }
 
 // sumsq: device scalar with the squared norm of the (unscaled) gradient over all shards, or null
-// to skip clipping. norm_out (optional) receives the scaled norm.
+// to skip clipping. norm_out (optional) receives the scaled norm. step_dev (optional): device
+// float holding the step count t; when set the kernel derives the bias corrections from it
+// (beta1, beta2 as doubles) and ignores bias_corr1 / bias_corr2_sqrt.
 int gfs_adamw_step(const void* grad, void* master, void* exp_avg, void* exp_avg_sq, void* param_out, long long n,
-                   const void* sumsq, void* norm_out, float lr, float beta1, float beta2, float eps,
+                   const void* sumsq, void* norm_out, float lr, double beta1, double beta2, float eps,
                    float weight_decay, float bias_corr1, float bias_corr2_sqrt, float clip, float grad_scale,
-                   void* stream) {
+                   const void* step_dev, void* stream) {
   if (n == 0) return 0;
-  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2_sqrt, clip, grad_scale};
+  AdamArgs a{lr, static_cast<float>(beta1), static_cast<float>(beta2), eps, weight_decay, bias_corr1,
+             bias_corr2_sqrt, clip, grad_scale, static_cast<const float*>(step_dev), beta1, beta2};
   const long long blocks =
       std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, static_cast<long long>(gfs_host::sm_count()) * 16));
   adamw_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(

@@ -51,7 +51,7 @@ def available() -> bool:
 
 
 def _declare(lib: ctypes.CDLL) -> None:
-    vp, i, sz, f, i64 = c_void_p, c_int, c_size_t, c_float, c_int64
+    vp, i, sz, f, i64, d = c_void_p, c_int, c_size_t, c_float, c_int64, ctypes.c_double
     lp = POINTER(ctypes.c_longlong)
     ulp = POINTER(ctypes.c_ulonglong)
     uip = POINTER(ctypes.c_uint)
@@ -76,7 +76,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_ce_bwd": ([vp, vp, vp, vp, i, i, cl, i, vp], i),
         "gfs_sumsq_scratch_bytes": ([], i),
         "gfs_sumsq_bf16": ([vp, i64, vp, vp, vp], i),
-        "gfs_adamw_step": ([vp, vp, vp, vp, vp, i64, vp, vp, f, f, f, f, f, f, f, f, f, vp], i),
+        "gfs_adamw_step": ([vp, vp, vp, vp, vp, i64, vp, vp, f, d, d, f, f, f, f, f, f, vp, vp], i),
+        "gfs_flag_slots": ([], i),
         "gfs_wait_probe": ([vp, i64, vp], i),
         "gfs_flash_fwd": ([vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp], i),
         "gfs_flash_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, lp, f, i, vp, vp, vp], i),
@@ -100,7 +101,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_dp_reduce_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i, uip, i, uip, vp,
                                 ctypes.c_longlong, vp], i),
         "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i,
-                                ctypes.c_uint, i, uip, vp, vp, f, f, f, f, f, f, f, f, f, ctypes.c_longlong, vp], i),
+                                ctypes.c_uint, i, uip, vp, vp, f, d, d, f, f, f, f, f, f, vp, ctypes.c_longlong, vp],
+                               i),
         "gfs_gemm_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_gemm2_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_gemm2_bf16": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, i, i, i, vp], i),

@@ -35,11 +35,13 @@ def sumsq_bf16(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 def adamw_step(grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
                param_out: torch.Tensor, *, step: int, lr: float, beta1: float, beta2: float, eps: float,
                weight_decay: float, sumsq: torch.Tensor | None, clip: float, grad_scale: float = 1.0,
-               norm_out: torch.Tensor | None = None) -> None:
+               norm_out: torch.Tensor | None = None, step_dev: torch.Tensor | None = None) -> None:
+    """``step_dev``: optional device float with the step count; the kernel then derives the bias
+    corrections from it instead of from ``step`` (for launches captured in a CUDA graph)."""
     bc1 = 1.0 - beta1 ** step
     bc2_sqrt = math.sqrt(1.0 - beta2 ** step)
     rc = _lib.lib().gfs_adamw_step(grad.data_ptr(), master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
                                    param_out.data_ptr(), grad.numel(), _lib.ptr(sumsq), _lib.ptr(norm_out),
                                    lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, clip, grad_scale,
-                                   _lib.stream_ptr())
+                                   _lib.ptr(step_dev), _lib.stream_ptr())
     _lib.check(rc, "gfs_adamw_step")

@@ -125,7 +125,10 @@ class DistributedOptimizer:
             self._rep_index_full = full
             in_shard = full[(full >= s0) & (full < s1)] - s0
             self._rep_index_shard = in_shard
-        self._sumsq = torch.zeros(2, dtype=torch.float32, device=device)
+        self._sumsq = torch.zeros(4, dtype=torch.float32, device=device)   # [sumsq, replicated sumsq, 0, 0]
+        # CUDA-graph mode: the step count lives on the device (a captured launch has frozen arguments)
+        self.graph_mode = False
+        self._step_dev = torch.zeros(1, dtype=torch.float32, device=device) if device.type == "cuda" else None
         self._norm_out = torch.zeros(1, dtype=torch.float32, device=device)
         self._step_count = 0
         self.last_grad_norm: torch.Tensor | None = None
@@ -162,14 +165,27 @@ class DistributedOptimizer:
     def _sum_replicated_grads_over_tp(self) -> None:
         if self._rep_index_full is None or self.reference_quirks:
             return
+        if self._fused_small_collectives() and self._rep_index_full.numel() % 8 == 0:
+            from .parallel import fused_comm
+            fused_comm.sum_over_tp_inplace(self.grad_buffer, self._rep_index_full)
+            return
         vals = self.grad_buffer.index_select(0, self._rep_index_full)
         dist.all_reduce(vals, group=ps.get_tensor_model_parallel_group())
         self.grad_buffer.index_copy_(0, self._rep_index_full, vals)
+
+    def _fused_small_collectives(self) -> bool:
+        return self.use_fused_kernels and ps.get_comm_impl() == "fused"
+
+    def step_dev(self):
+        """Device step counter for kernels launched inside a captured step (``None`` otherwise)."""
+        return self._step_dev if self.graph_mode else None
 
     # ------------------------------------------------------------------ step
     def step(self):
         gemm_ops.flush_wgrad()   # weight-gradient GEMMs parked for a grouped launch
         flush_dw_reductions()
+        if self.graph_mode:
+            self._step_dev.add_(1.0)
         self._materialise_unwritten()
         self._sum_replicated_grads_over_tp()
         if self.use_fused_comm:
@@ -194,13 +210,17 @@ class DistributedOptimizer:
         return st
 
     def _global_sumsq(self, local: torch.Tensor) -> torch.Tensor:
-        """local: fp32 [2] = {sum of squares of this shard, same over TP-replicated elements}."""
+        """local: fp32 [4] = {sum of squares of this shard, same over TP-replicated elements, 0, 0}."""
         world_tp = self.tp_world_size
         if self.reference_quirks or world_tp == 1:
             if self.dp_world_size > 1:
                 dist.all_reduce(local[0:1], group=self.dp_group)
             return local[0:1]
-        dist.all_reduce(local)  # over TP x DP
+        if self._fused_small_collectives():
+            from .parallel import fused_comm
+            local = fused_comm.allreduce_sum_small(local, "world")   # over TP x DP, no NCCL call
+        else:
+            dist.all_reduce(local)  # over TP x DP
         total = local[0:1] - local[1:2] * ((world_tp - 1) / world_tp)
         return total
 
@@ -215,7 +235,7 @@ class DistributedOptimizer:
             if self._rep_index_shard is not None and not self.reference_quirks:
                 self._sumsq[1] = shard.index_select(0, self._rep_index_shard).float().pow(2).sum()
             else:
-                self._sumsq[1] = 0.0
+                self._sumsq[1:2].zero_()     # (a scalar assignment would be a host-to-device copy)
             sumsq = self._global_sumsq(self._sumsq)
         lr, beta1, beta2, eps, wd = self._hyper()
         st = self._adam_state()
@@ -225,7 +245,7 @@ class DistributedOptimizer:
         adam_ops.adamw_step(shard, self.fp32_master_shard.data, st["exp_avg"], st["exp_avg_sq"], out,
                             step=self._step_count + 1, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=wd,
                             sumsq=sumsq, clip=float(self.clip_grad or 0.0), grad_scale=scale,
-                            norm_out=self._norm_out)
+                            norm_out=self._norm_out, step_dev=self.step_dev())
         self.last_grad_norm = self._norm_out
         if self.dp_world_size > 1:
             dist.all_gather_into_tensor(self.param_buffer, out.clone(), group=self.dp_group)
@@ -276,6 +296,23 @@ class DistributedOptimizer:
         st = self.optimizer.state.get(self.fp32_master_shard, {})
         if "step" in st:
             self._step_count = int(float(st["step"]))
+        self._sync_step_dev()
+
+    def _sync_step_dev(self) -> None:
+        if self._step_dev is not None:
+            self._step_dev.fill_(float(self._step_count))
+
+    def enter_graph_mode(self) -> None:
+        """From now on ``step()`` takes the step count from device memory (incremented by the step
+        itself), so a captured step stays correct when replayed."""
+        self._sync_step_dev()
+        self.graph_mode = True
+
+    def note_replayed_step(self) -> None:
+        """Host bookkeeping for one replay of a captured step (the device did the work)."""
+        self._step_count += 1
+        st = self._adam_state()
+        st["step"] += 1
 
     def full_state_dict(self):
         """Everything needed to resume exactly: inner state + the fp32 master shard (which the
@@ -291,6 +328,7 @@ class DistributedOptimizer:
         with torch.no_grad():
             self.fp32_master_shard.copy_(sd["fp32_master_shard"])
         self._step_count = int(sd["step_count"])
+        self._sync_step_dev()
         # rebuild the low-precision parameters from the master weights
         new_shard = self.fp32_master_shard.detach().to(self.dtype)
         if self.dp_world_size > 1:

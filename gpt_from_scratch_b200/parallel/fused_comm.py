@@ -252,16 +252,39 @@ def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, residual: torch
 
 
 # --------------------------------------------------------------------------- generic all-gather
-def allgather_rows(x2d: torch.Tensor, kind: str) -> torch.Tensor:
-    """Push-style all-gather of a ``[rows, cols]`` block over the TP group -> ``[world*rows, cols]``
-    (a view of a pooled symmetric buffer, valid until two later calls of the same kind and size)."""
-    grp = symm.get_group("tp")
+def allgather_rows(x2d: torch.Tensor, kind: str, group: str = "tp") -> torch.Tensor:
+    """Push-style all-gather of a ``[rows, cols]`` block over a group ("tp", "dp", "world") ->
+    ``[world*rows, cols]`` (a view of a pooled symmetric buffer, valid until two later calls of the
+    same kind and size). The kernel moves 16-byte vectors: any dtype works as long as a row is a
+    multiple of 16 bytes and starts on a 16-byte boundary."""
+    grp = symm.get_group(group)
+    if x2d.dtype != torch.bfloat16:
+        x2d = x2d.view(torch.bfloat16)
     rows, cols = x2d.shape
     buf, site = grp.pooled(kind, grp.world * rows * cols, x2d.dtype)
     rc = _lib.lib().gfs_allgather(x2d.data_ptr(), rows, cols, x2d.stride(0), buf.ptrs, grp.flag_ptrs, grp.world,
                                   grp.rank, site.slot0, ctypes.byref(site.target), WAIT_NS, _lib.stream_ptr())
     _lib.check(rc, "gfs_allgather")
     return buf.tensor.view(grp.world * rows, cols)
+
+
+def allreduce_sum_small(x: torch.Tensor, group: str) -> torch.Tensor:
+    """Sum of a small fp32 vector (numel a multiple of 4) over a group, by a push all-gather and a
+    sum in rank order: identical bits on every rank, no NCCL call, capturable in a CUDA graph.
+    Replaces the scalar all-reduces of the reference's clipping (core/optimizer.py:101)."""
+    assert x.dtype == torch.float32 and x.numel() % 4 == 0 and x.is_contiguous()
+    world = symm.get_group(group).world
+    every = allgather_rows(x.view(1, -1), "ar32", group=group)           # [world, 2*numel] as bf16 words
+    return every.view(torch.float32).view(world, x.numel()).sum(0)
+
+
+def sum_over_tp_inplace(buffer: torch.Tensor, index: torch.Tensor) -> None:
+    """``buffer[index] = sum over the TP group of buffer[index]`` (gradients of parameters that are
+    replicated across tensor-parallel ranks), summed in rank order on every rank."""
+    vals = buffer.index_select(0, index)
+    world = symm.get_group("tp").world
+    every = allgather_rows(vals.view(1, -1), "repg").view(world, -1)
+    buffer.index_copy_(0, index, every.float().sum(0).to(buffer.dtype))
 
 
 # --------------------------------------------------------------------------- embedding
@@ -366,7 +389,7 @@ class DataParallelComm:
         _lib.check(rc, "gfs_dp_reduce_norm")
 
     def adam_and_gather(self, master, exp_avg, exp_avg_sq, *, step, lr, beta1, beta2, eps, weight_decay, clip,
-                        grad_scale, extern_sumsq=None) -> None:
+                        grad_scale, extern_sumsq=None, step_dev=None) -> None:
         g = self.grp
         bc1 = 1.0 - beta1 ** step
         bc2_sqrt = math.sqrt(1.0 - beta2 ** step)
@@ -375,7 +398,8 @@ class DataParallelComm:
             exp_avg.data_ptr(), exp_avg_sq.data_ptr(), self.shard_start, self.shard_size, g.world, g.rank,
             self.site_norm.slot0, self.site_norm.target.value, self.site_param.slot0,
             ctypes.byref(self.site_param.target), _lib.ptr(extern_sumsq), self.norm_out.data_ptr(),
-            lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, clip, grad_scale, WAIT_NS, _lib.stream_ptr())
+            lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, clip, grad_scale, _lib.ptr(step_dev), WAIT_NS,
+            _lib.stream_ptr())
         _lib.check(rc, "gfs_dp_adam_gather")
 
     def step(self, opt, state, *, step, lr, beta1, beta2, eps, weight_decay, clip, grad_scale) -> None:
@@ -383,17 +407,16 @@ class DataParallelComm:
             self.reduce_and_norm()
         extern = None
         if opt.tp_world_size > 1 and not opt.reference_quirks and clip > 0:
-            # global norm over TP x DP with replicated parameters counted once: the tiny
-            # cross-TP part goes through torch.distributed
+            # global norm over TP x DP with replicated parameters counted once
             local = opt._sumsq
             from ..ops import adam as adam_ops
             adam_ops.sumsq_bf16(self.reduced, local[0:1])
             if opt._rep_index_shard is not None:
                 local[1] = self.reduced.index_select(0, opt._rep_index_shard).float().pow(2).sum()
             else:
-                local[1] = 0.0
+                local[1:2].zero_()
             extern = opt._global_sumsq(local)
         with _lib.nvtx("fused:dp_clip_adam_allgather"):
             self.adam_and_gather(opt.fp32_master_shard.data, state["exp_avg"], state["exp_avg_sq"], step=step, lr=lr,
                                  beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip,
-                                 grad_scale=grad_scale, extern_sumsq=extern)
+                                 grad_scale=grad_scale, extern_sumsq=extern, step_dev=opt.step_dev())

@@ -8,6 +8,14 @@ counters: one symmetric ``uint32`` array per group out of which every call site 
 ``world`` consecutive slots, plus a host-side cumulative target per site. Counters are
 never reset; a waiter compares against the target, so no reset races exist.
 
+CUDA graphs: a captured step replays with frozen kernel arguments, so the targets cannot stay
+host-side cumulative counts. Every counter therefore has a local "base" word behind the
+counters (``csrc/common.cuh``); a kernel waits for ``base + target``. :func:`begin_graph_capture`
+moves the counts reached so far into the base words and restarts the host counts at zero,
+:func:`graph_epilogue` (called inside the capture, last) adds the step's per-site totals to the
+base words, and :func:`end_graph_capture` records those totals and restarts the host counts
+again, so eager launches after (or between) replays stay consistent too.
+
 Allocation is collective: all ranks of the group must create the same buffers in the same
 order, which holds because they run the same program.
 """
@@ -19,7 +27,7 @@ import os
 import torch
 import torch.distributed as dist
 
-NUM_FLAG_SLOTS = 8192
+NUM_FLAG_SLOTS = 8192      # must equal gfs_flag_slots() of the native library (checked at first use)
 # Debug aid (GFS_SYMM_CANARIES=1): every symmetric buffer gets a 256-byte guard region on both
 # sides, filled with a pattern; check_canaries() verifies them (the multi-GPU tests do so after
 # exercising every fused kernel). Stands in for a memory checker on peer stores.
@@ -58,9 +66,12 @@ class SymmGroup:
         self._sites: dict = {}
         self._pools: dict = {}
         self._next_slot = 0
-        flags = self.alloc("__flags__", NUM_FLAG_SLOTS, torch.int32, zero=True)
+        # counters [0, NUM_FLAG_SLOTS) + their base words [NUM_FLAG_SLOTS, 2*NUM_FLAG_SLOTS)
+        flags = self.alloc("__flags__", 2 * NUM_FLAG_SLOTS, torch.int32, zero=True)
         self.flags = flags
         self.flag_ptrs = flags.ptrs
+        self.base = flags.tensor[NUM_FLAG_SLOTS:]
+        self.per_step = torch.zeros(NUM_FLAG_SLOTS, dtype=torch.int32, device=device)
         # make sure every rank has zeroed its flags before anyone signals
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
@@ -126,11 +137,55 @@ class SymmGroup:
         return st["bufs"][i], st["sites"][i]
 
 
+    # ---------------------------------------------------------------- CUDA-graph support
+    def _host_counts(self) -> torch.Tensor:
+        import numpy as np
+        counts = np.zeros(NUM_FLAG_SLOTS, dtype=np.uint32)
+        for s in self._sites.values():
+            counts[s.slot0:s.slot0 + self.world] = s.target.value
+        return torch.from_numpy(counts.view(np.int32)).to(self.device)
+
+    def fold_targets_into_base(self) -> None:
+        """base += host counts; host counts restart at zero (launches keep waiting for the same
+        absolute values)."""
+        self.base.add_(self._host_counts())
+        for s in self._sites.values():
+            s.target.value = 0
+
+    def record_per_step(self) -> None:
+        """After a capture: the host counts are the step's per-site totals. Store them where the
+        graph's epilogue reads them and restart the host counts."""
+        self.per_step.copy_(self._host_counts())
+        for s in self._sites.values():
+            s.target.value = 0
+
+
+def begin_graph_capture() -> None:
+    """Call on every rank right before a step is captured (outside the capture)."""
+    for g in _groups.values():
+        g.fold_targets_into_base()
+
+
+def graph_epilogue() -> None:
+    """Call inside the capture after the step's last kernel: one small launch per group that
+    advances the base words by the step's totals (filled in by :func:`end_graph_capture`)."""
+    for g in _groups.values():
+        g.base.add_(g.per_step)
+
+
+def end_graph_capture() -> None:
+    """Call right after the capture, before the first replay."""
+    for g in _groups.values():
+        g.record_per_step()
+
+
 def get_group(kind: str) -> SymmGroup:
-    """``kind``: "tp" or "dp"."""
+    """``kind``: "tp", "dp" or "world" (all ranks of the job)."""
     from . import parallel_state as ps
     g = _groups.get(kind)
     if g is None:
+        from ..ops import _lib
+        assert _lib.lib().gfs_flag_slots() == NUM_FLAG_SLOTS
         dev = ps.get_device()
         if kind == "tp":
             g = SymmGroup(ps.get_tensor_model_parallel_group(), ps.get_tensor_model_parallel_world_size(),
@@ -138,6 +193,8 @@ def get_group(kind: str) -> SymmGroup:
         elif kind == "dp":
             g = SymmGroup(ps.get_data_parallel_group(), ps.get_data_parallel_world_size(),
                           ps.get_data_parallel_group_rank(), dev)
+        elif kind == "world":
+            g = SymmGroup(None, dist.get_world_size(), dist.get_rank(), dev)
         else:
             raise ValueError(kind)
         _groups[kind] = g

@@ -8,6 +8,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (B200) and the native library")
+    config.addinivalue_line("markers", "expects_status: the test makes a bounded device wait run out on purpose "
+                                       "and checks the status words itself")
 
 
 @pytest.fixture(scope="session")

@@ -175,6 +175,18 @@ def main():
     again = [float(eng.train_step(t[:2, :-1].contiguous().to(dev), t[:2, 1:].contiguous().to(dev))) for t in data]
     assert again == traj["fused"], (again, traj["fused"])
     log("TP training ok (fused path reproducible)")
+    # the same steps replayed from a CUDA graph (flag targets relative to device-side base words)
+    eng = TrainEngine(cfg, lr=1e-3, seed=3, cuda_graph=True, graph_warmup=2)
+    graphed = [float(eng.train_step(t[:2, :-1].contiguous().to(dev), t[:2, 1:].contiguous().to(dev)))
+               for t in data + data]
+    torch.cuda.synchronize()
+    _lib.raise_on_status()
+    assert eng._graph is not None
+    log("TP losses graph", graphed[:4])
+    for a, b in zip(graphed[:4], traj["fused"]):
+        assert abs(a - b) < 5e-3, (graphed, traj["fused"])
+    assert all(x == x and x < 20 for x in graphed)
+    log("TP training under a CUDA graph ok")
 
     # ---- DP = world with the fused distributed optimizer ----
     ps.destroy_model_parallel()
@@ -203,6 +215,18 @@ def main():
         assert abs(a - b) < 2e-2, traj
     close(finals["fused"], finals["nccl"], "DP final parameters", 2e-3)
     log("DP training ok")
+    eng = TrainEngine(cfg, lr=1e-3, seed=3, cuda_graph=True, graph_warmup=2)
+    graphed = []
+    for t in data:
+        tt = t[rank::world]
+        graphed.append(float(eng.train_step(tt[:, :-1].contiguous().to(dev), tt[:, 1:].contiguous().to(dev))))
+    torch.cuda.synchronize()
+    _lib.raise_on_status()
+    assert eng._graph is not None
+    for a, b in zip(graphed, traj["fused"]):
+        assert abs(a - b) < 5e-3, (graphed, traj["fused"])
+    close(eng.optimizer.param_buffer.float(), finals["fused"], "DP final parameters under a CUDA graph", 2e-3)
+    log("DP training under a CUDA graph ok")
     torch.cuda.synchronize()
     dist.barrier()
     # no fused kernel of any rank wrote outside the usable range of a symmetric buffer

@@ -173,10 +173,18 @@ def test_training_with_bias_matches_fp32_oracle(cuda_device):
     sd = eng.model.state_dict()
     for k, v in oracle.state_dict().items():
         if k.endswith(".bias"):
-            # biases start at zero and move by about lr per step: compare the movement itself
-            err = (sd[k].float().cpu() - v).abs().max().item()
+            # biases start at zero and Adam moves each element by about lr per step: compare the
+            # direction and size of the movement. The key part of the qkv bias is left out: its
+            # gradient is zero in exact arithmetic (softmax ignores a constant added to a row of
+            # scores), so Adam only amplifies rounding noise there.
+            ours = sd[k].float().cpu()
+            if k.endswith("qkv_proj.bias"):
+                H = cfg.hidden_size
+                ours, v = torch.cat([ours[:H], ours[2 * H:]]), torch.cat([v[:H], v[2 * H:]])
             assert v.abs().max().item() > 1e-3, f"{k} did not train in the oracle"
-            assert err < 0.35 * v.abs().max().item() + 2e-4, f"{k}: {err} vs {v.abs().max().item()}"
+            cos = float((ours * v).sum() / (ours.norm() * v.norm() + 1e-12))
+            assert cos > 0.8, f"{k}: cosine {cos}"
+            assert 0.7 < float(ours.norm() / v.norm()) < 1.3, f"{k}: norm ratio {float(ours.norm() / v.norm())}"
 
 
 def test_checkpoint_roundtrip_gpu(cuda_device, tmp_path):
@@ -299,3 +307,40 @@ def test_training_is_bitwise_reproducible(cuda_device):
     assert runs[0][0] == runs[1][0], (runs[0][0], runs[1][0])
     for k, v in runs[0][1].items():
         assert torch.equal(v, runs[1][1][k]), k
+
+
+def test_cuda_graph_step_matches_eager(cuda_device):
+    """The step captured in a CUDA graph and replayed gives the eager loop's losses and weights
+    (same seed, same batches); the optimizer's host-side step count keeps up with the replays."""
+    from gpt_from_scratch_b200.config import GPTConfig
+    from gpt_from_scratch_b200.engine import TrainEngine
+    from gpt_from_scratch_b200.ops import _lib
+    from gpt_from_scratch_b200.parallel import parallel_state as ps
+    ps.set_device(cuda_device)
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_parallel_state(1)
+    cfg = GPTConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_attention_heads=4,
+                    max_position_embeddings=256, intermediate_size=768, init_method="normal")
+    g = torch.Generator().manual_seed(12)
+    batches = [torch.randint(0, 1024, (8, 257), generator=g) for _ in range(8)]
+    runs = []
+    for graph in (False, True):
+        eng = TrainEngine(cfg, lr=1e-3, clip_grad=1.0, seed=21, cuda_graph=graph, graph_warmup=2)
+        before = _lib.launch_count()
+        losses = [float(eng.train_step(t[:, :-1].contiguous().cuda(), t[:, 1:].contiguous().cuda())) for t in batches]
+        runs.append((losses, {k: v.detach().clone() for k, v in eng.model.state_dict().items()},
+                     _lib.launch_count() - before, eng))
+    eager, graphed = runs
+    assert graphed[3]._graph is not None and graphed[3].launches_per_graph_step > 20
+    assert graphed[2] == eager[2], "launch accounting of replays differs from the eager loop"
+    assert graphed[3].optimizer._step_count == 8 == eager[3].optimizer._step_count
+    for a, b in zip(eager[0], graphed[0]):
+        assert abs(a - b) < 2e-3, (eager[0], graphed[0])
+    for k, v in eager[1].items():
+        rel = (graphed[1][k].float() - v.float()).norm() / (v.float().norm() + 1e-9)
+        assert rel < 1e-3, f"{k}: {rel}"
+    # an eager step after replays still works (the flag/step bookkeeping is shared)
+    eng = graphed[3]
+    t = batches[0][:4]
+    loss = float(eng.train_step(t[:, :-1].contiguous().cuda(), t[:, 1:].contiguous().cuda()))   # other shape: eager
+    assert loss == loss and eng.optimizer._step_count == 9

@@ -54,6 +54,8 @@ def parse_args(argv=None):
     p.add_argument("--attention-impl", choices=["fused", "torch"], default="fused")
     p.add_argument("--comm-impl", choices=["fused", "nccl"], default="nccl",
                    help="fused: peer-memory kernels that overlap the collective with the GEMM")
+    p.add_argument("--cuda-graph", action="store_true",
+                   help="capture the whole step in a CUDA graph after a few eager steps (one launch per step)")
     p.add_argument("--synthetic-data", action="store_true", help="generate a seeded random token file")
     p.add_argument("--synthetic-tokens", type=int, default=None)
     p.add_argument("--dp-grad-reduce", choices=["sum", "mean"], default="sum")
@@ -112,7 +114,8 @@ def main(argv=None):
         args.dtype]
     config = build_config(args)
     engine = TrainEngine(config, lr=args.lr, weight_decay=args.weight_decay, betas=(0.9, 0.95),
-                         clip_grad=args.clip_grad, dtype=dtype, grad_reduce=args.dp_grad_reduce, seed=args.seed)
+                         clip_grad=args.clip_grad, dtype=dtype, grad_reduce=args.dp_grad_reduce, seed=args.seed,
+                         cuda_graph=args.cuda_graph)
     print_rank0(f"Model params (per TP rank): {engine.params_per_tp_rank / 1e6:.1f}M")
 
     data_path = args.data_path
