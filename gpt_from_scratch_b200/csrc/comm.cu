@@ -10,7 +10,9 @@
 //                           into the sequence-shard owner's output (lookup + reduce-scatter)
 //   gfs_ce_exchange         vocab-parallel cross entropy: exchange of (max, sum-exp, target
 //                           logit) and the combine into lse / loss, replacing two all-reduces
-//   gfs_dp_reduce_norm      data-parallel gradient reduce-scatter by peer loads + squared-norm partial
+//   gfs_dp_push_grads       data-parallel gradient reduce-scatter, part 1: per-bucket push of the
+//                           peers' slices into their staging buffers (overlaps the backward pass)
+//   gfs_dp_sum_norm         part 2: sum of the staged contributions + squared-norm partial
 //   gfs_dp_adam_gather      global-norm clip + AdamW on the fp32 shard + bf16 parameter
 //                           all-gather by peer stores
 //
@@ -31,12 +33,6 @@ struct PeerTable {
   void* buf[MAX_PEERS];
   uint32_t* flags[MAX_PEERS];
 };
-
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-}
 
 // Every CTA signals each destination once, then waits until each source has signalled
 // `target` times in total. Called by all threads of the CTA after their stores.
@@ -140,41 +136,113 @@ __global__ void ce_exchange_kernel(PeerTable t, const float* __restrict__ stats,
 }
 
 // ---------------------------------------------------------------------------
-// Data-parallel optimizer, phase 1: reduced[i] = sum over ranks of grad_r[s0 + i] (peer
-// loads, fp32 sum in rank order, rounded to bf16 like a bf16 reduce-scatter), plus the
-// squared norm of the reduced shard. The last CTA to finish adds the per-CTA partials in
-// index order and publishes the shard's total to every rank's norm slots.
+// Data-parallel optimizer. The flat gradient / parameter buffers are cut into buckets (runs of
+// whole parameters, in the order the backward pass completes them); every rank owns one slice of
+// EVERY bucket, and a rank's optimizer shard is the concatenation of its slices:
+//
+//   flat buffer : | bucket 0: r0 r1 .. | bucket 1: r0 r1 .. | ...      slice[b] elements per rank
+//   shard of r  : | its slice of bucket 0 | its slice of bucket 1 | ...  (off[b] = start of slice b)
+//
+// so the gradient reduction of a bucket can start as soon as the backward pass has produced it,
+// with equal work for every rank. Three kernels:
+//   dp_push_grads   (per bucket, during backward, never waits): every rank stores the peers'
+//                   slices of its local gradients into the owners' staging buffers over NVLink
+//   dp_sum_norm     (once, at the step): the owner waits for all pushes, sums the staged
+//                   contributions in rank order (fp32, rounded to bf16 like a bf16 reduce-scatter)
+//                   and publishes the squared norm of its shard to every rank
+//   dp_adam_gather  (once): global-norm clip + AdamW on the fp32 shard + bf16 parameters stored
+//                   into every rank's parameter buffer (all-gather by peer stores)
+constexpr int MAX_BUCKETS = 16;
+struct BucketTable {
+  int nb;
+  long long flat0[MAX_BUCKETS];    // first element of bucket b in the flat buffers
+  long long slice[MAX_BUCKETS];    // elements per rank in bucket b (multiple of 8)
+  long long off[MAX_BUCKETS + 1];  // first element of bucket b's slice in a shard; off[nb] = shard size
+};
+
+// staging buffer of rank r: [world (source)][shard] bf16
 __global__ void __launch_bounds__(256)
-dp_reduce_norm_kernel(PeerTable grads, PeerTable norm, __nv_bfloat16* __restrict__ reduced, long long s0,
-                      long long n, int world, int rank, int slot_ready, uint32_t target_ready, int slot_norm,
-                      float* __restrict__ partials, unsigned int* __restrict__ ticket,
-                      unsigned long long wait_ns, uint32_t* status) {
-  // every rank's backward must be complete before its gradients are read
-  if (threadIdx.x < world && blockIdx.x == 0)
-    red_release_sys_add_u32(grads.flags[threadIdx.x] + slot_ready + rank, 1u);
+dp_push_grads_kernel(PeerTable stage, const __nv_bfloat16* __restrict__ grads, long long flat0, long long slice,
+                     long long off, long long shard, int world, int rank, int slot) {
+  const long long vps = slice >> 3;                 // 16-byte vectors per slice
+  const long long total = vps * world;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;                              // vectors in flight per thread
+  for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < total; v0 += U * stride) {
+    uint4 val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * stride;
+      if (v < total) {
+        const int dst = static_cast<int>((rank + 1 + v / vps) % world);      // peers first, own slice last
+        val[u] = *reinterpret_cast<const uint4*>(grads + flat0 + dst * slice + ((v % vps) << 3));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * stride;
+      if (v < total) {
+        const int dst = static_cast<int>((rank + 1 + v / vps) % world);
+        __nv_bfloat16* to = static_cast<__nv_bfloat16*>(stage.buf[dst]) + rank * shard + off + ((v % vps) << 3);
+        *reinterpret_cast<uint4*>(to) = val[u];
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) red_release_sys_add_u32(stage.flags[threadIdx.x] + slot + rank, 1u);
+}
+
+template <int WORLD>
+__global__ void __launch_bounds__(256)
+dp_sum_norm_kernel(PeerTable stage, PeerTable norm, __nv_bfloat16* __restrict__ reduced, long long shard, int world_rt,
+                   int rank, int slot_push, uint32_t target_push, int slot_norm, float* __restrict__ partials,
+                   unsigned int* __restrict__ ticket, unsigned long long wait_ns, uint32_t* status) {
+  const int world = WORLD > 0 ? WORLD : world_rt;
+  // every source's pushes of all buckets must have landed in our staging buffer
   if (threadIdx.x < world)
-    wait_flag_reached(grads.flags[rank] + slot_ready + threadIdx.x, target_ready, wait_ns, status,
+    wait_flag_reached(stage.flags[rank] + slot_push + threadIdx.x, target_push, wait_ns, status,
                       0xD1000000u | (threadIdx.x << 4) | rank);
   __syncthreads();
+  const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(stage.buf[rank]);
   float acc = 0.f;
-  const long long nvec = n >> 3;
-  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
-       v += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      float f[8];
-      load8(static_cast<const __nv_bfloat16*>(grads.buf[r]) + s0 + 8 * v, f);
+  const long long nvec = shard >> 3;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 2;
+  for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += U * stride) {
+    uint4 in[U][WORLD > 0 ? WORLD : MAX_PEERS];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum[e] += f[e];
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * stride;
+      if (v < nvec) {
+#pragma unroll
+        for (int r = 0; r < (WORLD > 0 ? WORLD : MAX_PEERS); ++r)
+          if (r < world) in[u][r] = *reinterpret_cast<const uint4*>(mine + r * shard + (v << 3));
+      }
     }
-    uint4 o;
-    o.x = pack_bf16x2(sum[0], sum[1]);
-    o.y = pack_bf16x2(sum[2], sum[3]);
-    o.z = pack_bf16x2(sum[4], sum[5]);
-    o.w = pack_bf16x2(sum[6], sum[7]);
-    *reinterpret_cast<uint4*>(reduced + 8 * v) = o;
-    const float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), d = unpack_bf16x2(o.w);
-    acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * stride;
+      if (v >= nvec) continue;
+      float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int r = 0; r < (WORLD > 0 ? WORLD : MAX_PEERS); ++r) {
+        if (r < world) {
+          const float2 a = unpack_bf16x2(in[u][r].x), b = unpack_bf16x2(in[u][r].y), c = unpack_bf16x2(in[u][r].z),
+                       d = unpack_bf16x2(in[u][r].w);
+          sum[0] += a.x; sum[1] += a.y; sum[2] += b.x; sum[3] += b.y;
+          sum[4] += c.x; sum[5] += c.y; sum[6] += d.x; sum[7] += d.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(sum[0], sum[1]);
+      o.y = pack_bf16x2(sum[2], sum[3]);
+      o.z = pack_bf16x2(sum[4], sum[5]);
+      o.w = pack_bf16x2(sum[6], sum[7]);
+      *reinterpret_cast<uint4*>(reduced + (v << 3)) = o;
+      const float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), d = unpack_bf16x2(o.w);
+      acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    }
   }
   __shared__ float sm[8];
   __shared__ bool is_last;
@@ -203,13 +271,14 @@ dp_reduce_norm_kernel(PeerTable grads, PeerTable norm, __nv_bfloat16* __restrict
 }
 
 // Phase 2: wait for every rank's squared-norm, clip, AdamW on the fp32 master shard, and
-// write the bf16 parameters into every rank's parameter buffer (all-gather by peer
-// stores). Ends with a signal/wait so that when the kernel completes, this rank's own
-// parameter buffer has received all shards.
+// write the bf16 parameters into every rank's parameter buffer (all-gather by 16-byte peer
+// stores; the bucket table maps a shard position to its place in the flat buffer). Ends with a
+// signal/wait so that when the kernel completes, this rank's own parameter buffer has
+// received all shards.
 __global__ void __launch_bounds__(256)
 dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __restrict__ reduced,
                       float* __restrict__ master, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
-                      long long s0, long long n, int world, int rank, int slot_norm, uint32_t target_norm,
+                      BucketTable bt, int world, int rank, int slot_norm, uint32_t target_norm,
                       int slot_param, uint32_t target_param, const float* __restrict__ extern_sumsq,
                       float* __restrict__ norm_out, AdamArgs a, unsigned long long wait_ns, uint32_t* status) {
   __shared__ float s_coef;
@@ -237,29 +306,51 @@ dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __r
   const float decay = 1.f - a.lr * a.weight_decay;
   const float step = a.lr / bc1;
   const float ob1 = 1.f - a.beta1, ob2 = 1.f - a.beta2;
-  const long long nvec = n >> 2;
+  const long long nvec = bt.off[bt.nb] >> 3;          // 8 elements per thread and iteration
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint2 gr = reinterpret_cast<const uint2*>(reduced)[i];
-    float4 p = reinterpret_cast<float4*>(master)[i];
-    float4 m = reinterpret_cast<float4*>(exp_avg)[i];
-    float4 v = reinterpret_cast<float4*>(exp_avg_sq)[i];
-    const float2 g01 = unpack_bf16x2(gr.x), g23 = unpack_bf16x2(gr.y);
-    float g[4] = {g01.x * coef, g01.y * coef, g23.x * coef, g23.y * coef};
-    float* pp = &p.x; float* mm = &m.x; float* vv = &v.x;
+    const long long e0 = i << 3;
+    const uint4 gr = *reinterpret_cast<const uint4*>(reduced + e0);
+    float g[8];
+    {
+      const float2 q0 = unpack_bf16x2(gr.x), q1 = unpack_bf16x2(gr.y), q2 = unpack_bf16x2(gr.z),
+                   q3 = unpack_bf16x2(gr.w);
+      g[0] = q0.x; g[1] = q0.y; g[2] = q1.x; g[3] = q1.y; g[4] = q2.x; g[5] = q2.y; g[6] = q3.x; g[7] = q3.y;
+    }
+    float4 p[2], m[2], v[2];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int h = 0; h < 2; ++h) {
+      p[h] = reinterpret_cast<const float4*>(master + e0)[h];
+      m[h] = reinterpret_cast<const float4*>(exp_avg + e0)[h];
+      v[h] = reinterpret_cast<const float4*>(exp_avg_sq + e0)[h];
+    }
+    float* pp = &p[0].x; float* mm = &m[0].x; float* vv = &v[0].x;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ge = g[e] * coef;
       pp[e] *= decay;
-      mm[e] = a.beta1 * mm[e] + ob1 * g[e];
-      vv[e] = a.beta2 * vv[e] + ob2 * g[e] * g[e];
+      mm[e] = a.beta1 * mm[e] + ob1 * ge;
+      vv[e] = a.beta2 * vv[e] + ob2 * ge * ge;
       pp[e] -= step * (mm[e] / (sqrtf(vv[e]) / bc2_sqrt + a.eps));
     }
-    reinterpret_cast<float4*>(master)[i] = p;
-    reinterpret_cast<float4*>(exp_avg)[i] = m;
-    reinterpret_cast<float4*>(exp_avg_sq)[i] = v;
-    const uint2 o = make_uint2(pack_bf16x2(p.x, p.y), pack_bf16x2(p.z, p.w));
-    for (int r = 0; r < world; ++r)
-      reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(params.buf[r]) + s0)[i] = o;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      reinterpret_cast<float4*>(master + e0)[h] = p[h];
+      reinterpret_cast<float4*>(exp_avg + e0)[h] = m[h];
+      reinterpret_cast<float4*>(exp_avg_sq + e0)[h] = v[h];
+    }
+    uint4 o;
+    o.x = pack_bf16x2(pp[0], pp[1]);
+    o.y = pack_bf16x2(pp[2], pp[3]);
+    o.z = pack_bf16x2(pp[4], pp[5]);
+    o.w = pack_bf16x2(pp[6], pp[7]);
+    int b = 0;
+    while (b + 1 < bt.nb && e0 >= bt.off[b + 1]) ++b;
+    const long long flat = bt.flat0[b] + rank * bt.slice[b] + (e0 - bt.off[b]);
+    for (int q = 0; q < world; ++q) {
+      const int r = (rank + 1 + q) % world;         // peers first: the remote stores leave early
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.buf[r]) + flat) = o;
+    }
   }
   cta_signal_all_and_wait(params, world, rank, slot_param, target_param, wait_ns, status);
 }
@@ -340,52 +431,101 @@ int gfs_ce_exchange(const void* stats, void* lse, void* loss, int M, const unsig
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// scratch: fp32 [grid + 1] zero-initialised once (per-CTA partials followed by the ticket);
+// ---- data-parallel optimizer (see the kernels above) ----
+// A bucket table is passed as three host arrays of nb (off: nb + 1) entries, in elements.
+static int fill_buckets(BucketTable& bt, int nb, const long long* flat0, const long long* slice, const long long* off) {
+  if (nb < 1 || nb > MAX_BUCKETS) return -1;
+  bt.nb = nb;
+  for (int b = 0; b < nb; ++b) {
+    if ((flat0[b] & 7) || (slice[b] & 7) || (off[b] & 7) || slice[b] <= 0) return -1;
+    bt.flat0[b] = flat0[b];
+    bt.slice[b] = slice[b];
+    bt.off[b] = off[b];
+  }
+  if (off[nb] & 7) return -1;
+  bt.off[nb] = off[nb];
+  return 0;
+}
+
+// Pushes bucket `b` of the local gradient buffer: slice r goes to rank r's staging buffer
+// (peer_stage[r] = rank r's [world][shard] bf16 buffer), at [this rank][off[b] ...). Never waits;
+// may run on a side stream while the backward pass continues. max_ctas > 0 limits the grid.
+// *target_inout: cumulative number of signals each owner must see from each source.
+int gfs_dp_push_grads(const void* grads, const unsigned long long* peer_stage, const unsigned long long* peer_flags,
+                      int nb, const long long* flat0, const long long* slice, const long long* off, int b, int world,
+                      int rank, int slot_push, unsigned int* target_inout, int max_ctas, void* stream) {
+  PeerTable st;
+  BucketTable bt;
+  if (fill_table(st, peer_stage, peer_flags, world) || fill_buckets(bt, nb, flat0, slice, off)) return -1;
+  if (b < 0 || b >= nb) return -1;
+  const long long vecs = (bt.slice[b] >> 3) * world;
+  int grid = resident_grid(static_cast<int>(std::min<long long>((vecs + 4 * 256 - 1) / (4 * 256), 1 << 20)));
+  if (max_ctas > 0) grid = std::min(grid, max_ctas);
+  *target_inout += static_cast<unsigned int>(grid);
+  dp_push_grads_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      st, static_cast<const __nv_bfloat16*>(grads), bt.flat0[b], bt.slice[b], bt.off[b], bt.off[nb], world, rank,
+      slot_push);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// scratch: fp32 [2 * SMs + 8] zero-initialised once (per-CTA partials followed by the ticket);
 // gfs_dp_reduce_norm_scratch_floats() gives its size.
 int gfs_dp_reduce_norm_scratch_floats() { return gfs_host::sm_count() * 2 + 8; }
 
-int gfs_dp_reduce_norm(const unsigned long long* peer_grads, const unsigned long long* peer_flags,
-                       const unsigned long long* peer_norm_slots, void* reduced, long long shard_start,
-                       long long shard_numel, int world, int rank, int slot_ready, unsigned int* target_ready_inout,
-                       int slot_norm, unsigned int* target_norm_inout, void* scratch, long long wait_ns,
-                       void* stream) {
-  PeerTable g, nm;
-  if (fill_table(g, peer_grads, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
-  if ((shard_numel & 7) || (shard_start & 7)) return -1;
-  const int grid = resident_grid(static_cast<int>(((shard_numel >> 3) + 255) / 256));
-  *target_ready_inout += 1;
+// Sums the staged gradient contributions of all ranks into `reduced` (this rank's shard) once
+// every push has arrived (target_push = the value gfs_dp_push_grads left in its counter), and
+// publishes the shard's squared norm to every rank (peer_norm_slots[r][rank], flag slot_norm).
+int gfs_dp_sum_norm(const unsigned long long* peer_stage, const unsigned long long* peer_flags,
+                    const unsigned long long* peer_norm_slots, void* reduced, long long shard_numel, int world,
+                    int rank, int slot_push, unsigned int target_push, int slot_norm, unsigned int* target_norm_inout,
+                    void* scratch, long long wait_ns, void* stream) {
+  PeerTable st, nm;
+  if (fill_table(st, peer_stage, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
+  if (shard_numel & 7) return -1;
+  const int grid = resident_grid(static_cast<int>(((shard_numel >> 3) + 2 * 256 - 1) / (2 * 256)));
   *target_norm_inout += 1;
   float* partials = static_cast<float*>(scratch);
   unsigned int* ticket = reinterpret_cast<unsigned int*>(partials + gfs_host::sm_count() * 2 + 4);
-  dp_reduce_norm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      g, nm, static_cast<__nv_bfloat16*>(reduced), shard_start, shard_numel, world, rank, slot_ready,
-      *target_ready_inout, slot_norm, partials, ticket, limit_of(wait_ns), gfs_host::status_words());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* red = static_cast<__nv_bfloat16*>(reduced);
+#define GFS_SUM_NORM(W)                                                                                          \
+  dp_sum_norm_kernel<W><<<grid, 256, 0, s>>>(st, nm, red, shard_numel, world, rank, slot_push, target_push,      \
+                                             slot_norm, partials, ticket, limit_of(wait_ns),                     \
+                                             gfs_host::status_words())
+  if (world == 2) GFS_SUM_NORM(2);
+  else if (world == 4) GFS_SUM_NORM(4);
+  else if (world == 8) GFS_SUM_NORM(8);
+  else GFS_SUM_NORM(0);
+#undef GFS_SUM_NORM
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 // extern_sumsq: device scalar with the global squared gradient norm computed elsewhere
 // (e.g. reduced over tensor-parallel ranks as well), or null to use the per-rank values
-// exchanged by gfs_dp_reduce_norm (target_norm = the value that call left in its counter).
+// exchanged by gfs_dp_sum_norm (target_norm = the value that call left in its counter).
 // step_dev: as in gfs_adamw_step (loss_optim.cu).
 int gfs_dp_adam_gather(const unsigned long long* peer_params, const unsigned long long* peer_flags,
                        const unsigned long long* peer_norm_slots, const void* reduced, void* master, void* exp_avg,
-                       void* exp_avg_sq, long long shard_start, long long shard_numel, int world, int rank,
-                       int slot_norm, unsigned int target_norm, int slot_param, unsigned int* target_param_inout,
-                       const void* extern_sumsq, void* norm_out, float lr, double beta1, double beta2, float eps,
-                       float weight_decay, float bias_corr1, float bias_corr2_sqrt, float clip, float grad_scale,
-                       const void* step_dev, long long wait_ns, void* stream) {
+                       void* exp_avg_sq, int nb, const long long* flat0, const long long* slice, const long long* off,
+                       int world, int rank, int slot_norm, unsigned int target_norm, int slot_param,
+                       unsigned int* target_param_inout, const void* extern_sumsq, void* norm_out, float lr,
+                       double beta1, double beta2, float eps, float weight_decay, float bias_corr1,
+                       float bias_corr2_sqrt, float clip, float grad_scale, const void* step_dev, long long wait_ns,
+                       void* stream) {
   PeerTable pr, nm;
+  BucketTable bt;
   if (fill_table(pr, peer_params, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
-  if ((shard_numel & 7) || (shard_start & 7)) return -1;
-  const int grid = resident_grid(static_cast<int>(((shard_numel >> 2) + 255) / 256));
+  if (fill_buckets(bt, nb, flat0, slice, off)) return -1;
+  const long long shard_numel = bt.off[nb];
+  const int grid = resident_grid(static_cast<int>(((shard_numel >> 3) + 255) / 256));
   *target_param_inout += static_cast<unsigned int>(grid);
   AdamArgs a{lr, static_cast<float>(beta1), static_cast<float>(beta2), eps, weight_decay, bias_corr1,
              bias_corr2_sqrt, clip, grad_scale, static_cast<const float*>(step_dev), beta1, beta2};
   dp_adam_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pr, nm, static_cast<const __nv_bfloat16*>(reduced), static_cast<float*>(master), static_cast<float*>(exp_avg),
-      static_cast<float*>(exp_avg_sq), shard_start, shard_numel, world, rank, slot_norm, target_norm, slot_param,
-      *target_param_inout, static_cast<const float*>(extern_sumsq), static_cast<float*>(norm_out), a,
-      limit_of(wait_ns), gfs_host::status_words());
+      static_cast<float*>(exp_avg_sq), bt, world, rank, slot_norm, target_norm, slot_param, *target_param_inout,
+      static_cast<const float*>(extern_sumsq), static_cast<float*>(norm_out), a, limit_of(wait_ns),
+      gfs_host::status_words());
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -61,6 +61,9 @@ class TrainEngine:
             {"lr": lr, "weight_decay": weight_decay, "betas": betas},
             clip_grad=clip_grad, dtype=dtype, grad_reduce=grad_reduce,
             reference_quirks=getattr(config, "reference_quirks", False))
+        # one backward pass per step, every parameter used once: gradient buckets may leave for their
+        # owners while backward still runs
+        self.optimizer.overlap_grad_reduce = True
         self.model.train()
         self.steps_done = 0
         self._loss_ring: list[torch.Tensor] = []

@@ -98,11 +98,11 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_embedding_scatter": ([vp, vp, i, i, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_ce_exchange": ([vp, vp, vp, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_dp_reduce_norm_scratch_floats": ([], i),
-        "gfs_dp_reduce_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i, uip, i, uip, vp,
-                                ctypes.c_longlong, vp], i),
-        "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, i, i, i,
-                                ctypes.c_uint, i, uip, vp, vp, f, d, d, f, f, f, f, f, f, vp, ctypes.c_longlong, vp],
-                               i),
+        "gfs_dp_push_grads": ([vp, ulp, ulp, i, lp, lp, lp, i, i, i, i, uip, i, vp], i),
+        "gfs_dp_sum_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, i, i, i, ctypes.c_uint, i, uip, vp,
+                             ctypes.c_longlong, vp], i),
+        "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, i, lp, lp, lp, i, i, i, ctypes.c_uint, i, uip, vp, vp,
+                                f, d, d, f, f, f, f, f, f, vp, ctypes.c_longlong, vp], i),
         "gfs_gemm_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_gemm2_bf16_swiglu": ([i, vp, vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_gemm2_bf16": ([vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, i, i, i, vp], i),

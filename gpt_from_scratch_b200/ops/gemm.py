@@ -263,6 +263,8 @@ def linear_wgrad_to_sink(dy2d: torch.Tensor, x2d: torch.Tensor, sink) -> None:
             and _WgradQueue.tiles_of(N_out, N_in) < _PAIR_MIN_TILES and dy2d.shape[0] >= 256
             and N_out % 8 == 0 and N_in % 8 == 0 and out.stride(1) == 1 and out.stride(0) % 8 == 0):
         _wgrad_queue.push(_rowmajor_2d(dy2d), _rowmajor_2d(x2d), out, accumulate, sink.done)
+        if hasattr(sink, "parked"):
+            sink.parked()
         return
     linear_wgrad(dy2d, x2d, out=out, accumulate=accumulate)
     sink.done()

@@ -33,6 +33,13 @@ class GradSink:
         if cb is not None:
             cb(self.param)
 
+    def parked(self) -> None:
+        """Tell the owner that the kernel producing this gradient has been queued for a batched
+        launch (so it can ask for the launch when nothing else is outstanding)."""
+        cb = getattr(self.param, "_grad_parked_cb", None)
+        if cb is not None:
+            cb(self.param)
+
     @staticmethod
     def of(param: torch.nn.Parameter | None) -> "GradSink | None":
         if param is None or param.grad is None or not getattr(param, "_grad_sink_ok", False):

@@ -120,9 +120,12 @@ class _RMSNorm(torch.autograd.Function):
                                         1 if acc else 0, _lib.stream_ptr())
         _lib.check(rc, "gfs_rmsnorm_bwd")
         if defer:
-            _dw_queue.push(partial, dw, parts, acc, H, None)
+            _dw_queue.push(partial, dw, parts, acc, H, sink.done)
+            sink.parked()
         else:
             _lib.add_launches(1)
+            if sink is not None:
+                sink.done()
         return dx.view(ctx.xshape), (None if sink is not None else dw), None, None, None
 
 

@@ -27,7 +27,13 @@ Differences that are deliberate:
   restores the reference's per-TP-rank norm and missing TP reduction.
 * ``grad_reduce="mean"`` divides the DP-summed gradient by the DP size (the reference sums).
 * With ``comm_impl == "fused"`` and DP > 1 the reduce-scatter, norm partial, AdamW and
-  parameter all-gather run as peer-memory kernels (``parallel/fused_comm.py``).
+  parameter all-gather run as peer-memory kernels (``parallel/fused_comm.py``), and the
+  reduce-scatter's data movement overlaps the backward pass: the flat buffer is cut into a few
+  buckets of whole parameters, every rank owns one slice of EVERY bucket (its optimizer shard is
+  the concatenation of those slices instead of one contiguous range), and as soon as backward
+  has written a bucket its slices are pushed to their owners on a side stream.
+  ``state_dict()`` / ``load_state_dict()`` still speak the reference's layout (the contiguous
+  range ``[r*shard_size, (r+1)*shard_size)``): they convert with a collective over the DP group.
 """
 from __future__ import annotations
 
@@ -78,7 +84,8 @@ class DistributedOptimizer:
 
         if self.use_fused_comm:
             from .parallel import fused_comm
-            self._dp_comm = fused_comm.DataParallelComm(self.padded_numel, self.shard_size, device)
+            self._dp_comm = fused_comm.DataParallelComm(self.padded_numel, self.shard_size, device,
+                                                        self._make_buckets())
             self.param_buffer = self._dp_comm.param_buffer
             self.grad_buffer = self._dp_comm.grad_buffer
         else:
@@ -109,9 +116,16 @@ class DistributedOptimizer:
         s0 = self.shard_size * self.dp_rank
         s1 = s0 + self.shard_size
         self.shard_start, self.shard_end = s0, s1
-        self.fp32_master_shard = (self.param_buffer[s0:s1].to(torch.float32).clone().detach().requires_grad_(True))
+        self.interleaved = self._dp_comm is not None and self._dp_comm.nb > 1
+        if self.interleaved:
+            own = self._dp_comm.gather_shard(self.param_buffer)
+        else:
+            own = self.param_buffer[s0:s1]
+        self.fp32_master_shard = own.to(torch.float32).clone().detach().requires_grad_(True)
         self.optimizer = optimizer_cls([self.fp32_master_shard], **self.optimizer_kwargs)
-        if self.dp_world_size > 1 and not self.use_fused_comm:
+        if self.use_fused_comm:
+            self.reduced_grad_shard = self._dp_comm.reduced
+        elif self.dp_world_size > 1:
             self.reduced_grad_shard = torch.zeros(self.shard_size, dtype=dtype, device=device)
         else:
             self.reduced_grad_shard = self.grad_buffer[s0:s1]
@@ -123,7 +137,15 @@ class DistributedOptimizer:
         if self.tp_world_size > 1 and replicated_ranges:
             full = torch.cat([torch.arange(a, b, device=device) for a, b in replicated_ranges])
             self._rep_index_full = full
-            in_shard = full[(full >= s0) & (full < s1)] - s0
+            if self.use_fused_comm:
+                # position inside this rank's shard of every replicated element it owns
+                pos = []
+                for a, b, o in self._dp_comm.shard_slices():
+                    sel = full[(full >= a) & (full < b)]
+                    pos.append(sel - a + o)
+                in_shard = torch.cat(pos)
+            else:
+                in_shard = full[(full >= s0) & (full < s1)] - s0
             self._rep_index_shard = in_shard
         self._sumsq = torch.zeros(4, dtype=torch.float32, device=device)   # [sumsq, replicated sumsq, 0, 0]
         # CUDA-graph mode: the step count lives on the device (a captured launch has frozen arguments)
@@ -132,6 +154,120 @@ class DistributedOptimizer:
         self._norm_out = torch.zeros(1, dtype=torch.float32, device=device)
         self._step_count = 0
         self.last_grad_norm: torch.Tensor | None = None
+        self._init_overlap()
+
+    # ------------------------------------------------------------------ buckets / overlap
+    NUM_BUCKETS = 6
+
+    def _make_buckets(self) -> list[tuple[int, int]]:
+        """Cut the flat buffer into at most NUM_BUCKETS ranges of roughly equal size at parameter
+        boundaries (rounded down to a multiple of 8 x DP size, so a boundary may fall a few
+        elements inside a parameter, which then belongs to both buckets)."""
+        align = 8 * self.dp_world_size
+        target = max(align, self.padded_numel // self.NUM_BUCKETS)
+        cuts, offset, last = [0], 0, 0
+        for p in self.params:
+            offset += p.numel()
+            c = offset // align * align
+            if c - last >= target and self.padded_numel - c >= target // 2:
+                cuts.append(c)
+                last = c
+        cuts.append(self.padded_numel)
+        return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+
+    def _init_overlap(self) -> None:
+        """Per-bucket bookkeeping for pushing a bucket's gradients while backward still runs.
+        Armed per step by ``zero_grad()`` when ``overlap_grad_reduce`` is set (the training engine
+        sets it: it guarantees exactly one backward pass between ``zero_grad()`` and ``step()``,
+        with every parameter used once). A bucket is pushed early only when every parameter in it
+        has reported its gradient final through its gradient sink; a parameter whose gradient
+        arrives through plain autograd (a bias) never reports, so its bucket waits for ``step()``."""
+        self.overlap_grad_reduce = False
+        self._overlap_armed = False
+        self._push_stream = None
+        if not self.use_fused_comm:
+            return
+        buckets = self._dp_comm.buckets
+        self._param_buckets: dict[int, list[int]] = {}
+        self._bucket_size = [0] * len(buckets)
+        for p, off in zip(self.params, self.param_offsets):
+            mine = [b for b, (a, e) in enumerate(buckets) if off < e and off + p.numel() > a]
+            self._param_buckets[id(p)] = mine
+            for b in mine:
+                self._bucket_size[b] += 1
+            p._grad_ready_cb = self._on_grad_ready
+            p._grad_parked_cb = self._on_grad_parked
+        self._pending = list(self._bucket_size)
+        self._parked = [0] * len(buckets)
+        self._pushed = [False] * len(buckets)
+        self._push_stream = torch.cuda.Stream(self.device, priority=-1)
+
+    def _reset_overlap(self) -> None:
+        if not self.use_fused_comm:
+            return
+        self._pending = list(self._bucket_size)
+        self._parked = [0] * len(self._bucket_size)
+        self._pushed = [False] * len(self._bucket_size)
+        self._overlap_armed = bool(self.overlap_grad_reduce)
+        for p in self.params:
+            p._gfs_parked = False
+            p._gfs_ready = False
+
+    def _on_grad_parked(self, p) -> None:
+        """A kernel that will write ``p``'s gradient has been queued for a batched launch. If a
+        bucket now waits for parked work only, launch that work."""
+        if not self._overlap_armed or p._gfs_parked or p._gfs_ready:
+            return
+        p._gfs_parked = True
+        flush = False
+        for b in self._param_buckets[id(p)]:
+            self._parked[b] += 1
+            flush = flush or self._parked[b] == self._pending[b]
+        if flush:
+            gemm_ops.flush_wgrad()
+            flush_dw_reductions()
+
+    def _on_grad_ready(self, p) -> None:
+        if not self._overlap_armed:
+            return
+        if p._gfs_ready:
+            if any(self._pushed[b] for b in self._param_buckets[id(p)]):
+                raise RuntimeError("a gradient was written after its bucket had been pushed to the other ranks "
+                                   "(parameter used twice in one backward pass, or two backward passes in one "
+                                   "step): set optimizer.overlap_grad_reduce = False for such models")
+            return
+        p._gfs_ready = True
+        for b in self._param_buckets[id(p)]:
+            if p._gfs_parked:
+                self._parked[b] -= 1
+            self._pending[b] -= 1
+            if self._pending[b] == 0:
+                self._push_bucket_async(b)
+
+    def _push_bucket_async(self, b: int) -> None:
+        """Bucket ``b`` is final on the current stream: push it on the side stream from here."""
+        if self._pushed[b]:
+            return
+        self._pushed[b] = True
+        ev = torch.cuda.Event()
+        ev.record()
+        self._push_stream.wait_event(ev)
+        with torch.cuda.stream(self._push_stream):
+            # a modest grid: the copy rides along with the backward kernels instead of displacing them
+            self._dp_comm.push_bucket(b, max_ctas=32)
+
+    def _finish_pushes(self) -> None:
+        """Push whatever the backward pass did not (everything when overlap is off) and make the
+        current stream wait for the side stream."""
+        forked = any(self._pushed)
+        for b in range(len(self._pushed)):
+            if not self._pushed[b]:
+                self._pushed[b] = True
+                self._dp_comm.push_bucket(b)
+        if forked:
+            torch.cuda.current_stream().wait_stream(self._push_stream)
+        self._overlap_armed = False
+        self._pushed = [False] * len(self._pushed)
 
     # ------------------------------------------------------------------ gradients
     def zero_grad(self, set_to_zero: bool = False):
@@ -139,6 +275,7 @@ class DistributedOptimizer:
         views into the flat buffer must survive)."""
         gemm_ops.flush_wgrad()   # nothing parked may land in the buffer after this point
         flush_dw_reductions()
+        self._reset_overlap()
         if self.use_fused_kernels and not set_to_zero:
             for p in self.params:
                 p._grad_fresh = True
@@ -187,7 +324,10 @@ class DistributedOptimizer:
         if self.graph_mode:
             self._step_dev.add_(1.0)
         self._materialise_unwritten()
-        self._sum_replicated_grads_over_tp()
+        if not self.use_fused_comm:
+            # (the fused DP path sums the replicated gradients over TP after its reduce-scatter, on
+            # the reduced shard: the two sums commute, and buckets can leave before step())
+            self._sum_replicated_grads_over_tp()
         if self.use_fused_comm:
             self._step_fused_comm()
         elif self.use_fused_kernels:
@@ -251,6 +391,7 @@ class DistributedOptimizer:
             dist.all_gather_into_tensor(self.param_buffer, out.clone(), group=self.dp_group)
 
     def _step_fused_comm(self):
+        self._finish_pushes()
         lr, beta1, beta2, eps, wd = self._hyper()
         st = self._adam_state()
         st["step"] += 1
@@ -279,20 +420,50 @@ class DistributedOptimizer:
         self.fp32_master_shard.grad = shard.to(torch.float32)
         self.optimizer.step()
         self.optimizer.zero_grad()
-        new_shard = self.fp32_master_shard.detach().to(self.dtype)
+        new_shard = self._to_reference_layout(self.fp32_master_shard.detach()).to(self.dtype)
         if self.dp_world_size > 1:
             dist.all_gather_into_tensor(self.param_buffer, new_shard.contiguous(), group=self.dp_group)
         else:
             self.param_buffer.copy_(new_shard)
 
     # ------------------------------------------------------------------ state
+    # -- the reference's shard is the contiguous range [r*shard, (r+1)*shard) of the flat buffer; with
+    #    the bucket-interleaved layout the same elements are spread over the DP ranks
+    def _to_reference_layout(self, t: torch.Tensor) -> torch.Tensor:
+        if not self.interleaved or t.numel() != self.shard_size:
+            return t
+        world = self.dp_world_size
+        every = torch.empty(world * self.shard_size, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(every, t.detach().contiguous(), group=self.dp_group)
+        every = every.view(world, self.shard_size)
+        full = torch.empty(self.padded_numel, dtype=t.dtype, device=t.device)
+        for r in range(world):
+            for a, b, o in self._dp_comm.shard_slices(r):
+                full[a:b] = every[r, o:o + (b - a)]
+        return full[self.shard_start:self.shard_end].clone()
+
+    def _from_reference_layout(self, t: torch.Tensor) -> torch.Tensor:
+        if not self.interleaved or t.numel() != self.shard_size:
+            return t
+        t = t.to(self.device)
+        full = torch.empty(self.padded_numel, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(full, t.detach().contiguous(), group=self.dp_group)
+        return self._dp_comm.gather_shard(full)
+
+    def _convert_state(self, sd: dict, fn) -> dict:
+        out = {"state": {}, "param_groups": sd["param_groups"]}
+        for k, st in sd["state"].items():
+            out["state"][k] = {n: (fn(v) if torch.is_tensor(v) and v.dim() == 1 else v) for n, v in st.items()}
+        return out
+
     def state_dict(self):
         """The inner AdamW state (step, exp_avg, exp_avg_sq of the flat shard + param groups),
-        as the reference returns (core/optimizer.py:106-108)."""
-        return self.optimizer.state_dict()
+        as the reference returns (core/optimizer.py:106-108), in the reference's shard layout
+        (a collective over the DP group when the bucket-interleaved layout is active)."""
+        return self._convert_state(self.optimizer.state_dict(), self._to_reference_layout)
 
     def load_state_dict(self, state_dict):
-        self.optimizer.load_state_dict(state_dict)
+        self.optimizer.load_state_dict(self._convert_state(state_dict, self._from_reference_layout))
         st = self.optimizer.state.get(self.fp32_master_shard, {})
         if "step" in st:
             self._step_count = int(float(st["step"]))
@@ -317,8 +488,8 @@ class DistributedOptimizer:
     def full_state_dict(self):
         """Everything needed to resume exactly: inner state + the fp32 master shard (which the
         reference's ``state_dict`` omits)."""
-        return {"optimizer": self.optimizer.state_dict(),
-                "fp32_master_shard": self.fp32_master_shard.detach().clone(),
+        return {"optimizer": self.state_dict(),
+                "fp32_master_shard": self._to_reference_layout(self.fp32_master_shard.detach()).clone(),
                 "step_count": self._step_count,
                 "shard": (self.shard_start, self.shard_end, self.padded_numel)}
 
@@ -326,11 +497,11 @@ class DistributedOptimizer:
         assert tuple(sd["shard"]) == (self.shard_start, self.shard_end, self.padded_numel), "sharding mismatch"
         self.load_state_dict(sd["optimizer"])
         with torch.no_grad():
-            self.fp32_master_shard.copy_(sd["fp32_master_shard"])
+            self.fp32_master_shard.copy_(self._from_reference_layout(sd["fp32_master_shard"]))
         self._step_count = int(sd["step_count"])
         self._sync_step_dev()
         # rebuild the low-precision parameters from the master weights
-        new_shard = self.fp32_master_shard.detach().to(self.dtype)
+        new_shard = self._to_reference_layout(self.fp32_master_shard.detach()).to(self.dtype)
         if self.dp_world_size > 1:
             dist.all_gather_into_tensor(self.param_buffer, new_shard.contiguous(), group=self.dp_group)
         else:

@@ -357,36 +357,77 @@ def barrier(kind: str = "tp") -> None:
 
 # --------------------------------------------------------------------------- data-parallel optimizer
 class DataParallelComm:
-    """Symmetric parameter / gradient buffers of the distributed optimizer and its two fused
-    kernels: (1) gradient reduce-scatter by peer loads + squared-norm partial, (2) global-norm
-    clip + AdamW + bf16 parameter all-gather by peer stores. No NCCL call, no host sync."""
+    """Buffers and kernels of the distributed optimizer's collectives (csrc/comm.cu), no NCCL call
+    and no host sync:
 
-    def __init__(self, padded_numel: int, shard_size: int, device: torch.device):
+    * ``push_bucket(b)``: as soon as the backward pass has finished bucket ``b`` of the flat
+      gradient buffer, every rank stores each peer's slice of it into that peer's staging buffer
+      over NVLink (the reduce-scatter's data movement, overlapped with the rest of backward; the
+      kernel never waits, so it cannot stall anything it shares the GPU with);
+    * ``sum_and_norm()``: the owner sums the staged contributions in rank order + squared norm;
+    * ``adam_and_gather()``: global-norm clip + AdamW on the fp32 shard + bf16 parameters stored
+      into every rank's parameter buffer.
+
+    ``buckets``: list of ``(start, end)`` ranges of the flat buffer, each a multiple of
+    ``8 * world`` long; rank ``r`` owns ``[start + r*len/world, start + (r+1)*len/world)`` of each
+    and its optimizer shard is the concatenation of those slices."""
+
+    def __init__(self, padded_numel: int, shard_size: int, device: torch.device, buckets=None):
         self.grp = symm.get_group("dp")
         g = self.grp
+        buckets = buckets or [(0, padded_numel)]
+        assert buckets[0][0] == 0 and buckets[-1][1] == padded_numel
+        nb = len(buckets)
+        self.buckets = buckets
+        flat0, slices, offs = [], [], [0]
+        for (a, b) in buckets:
+            assert (b - a) % (8 * g.world) == 0 and b > a
+            flat0.append(a)
+            slices.append((b - a) // g.world)
+            offs.append(offs[-1] + slices[-1])
+        assert offs[-1] == shard_size
+        self.nb, self.flat0, self.slices, self.offs = nb, flat0, slices, offs
+        L = ctypes.c_longlong
+        self._c_flat0, self._c_slice, self._c_off = (L * nb)(*flat0), (L * nb)(*slices), (L * (nb + 1))(*offs)
         self._param = g.alloc("dp:params", padded_numel, torch.bfloat16, zero=True)
-        self._grad = g.alloc("dp:grads", padded_numel, torch.bfloat16, zero=True)
+        self._stage = g.alloc("dp:stage", g.world * shard_size, torch.bfloat16, zero=True)
         self._norm = g.alloc("dp:norm", 16, torch.float32, zero=True)
         self.param_buffer = self._param.tensor
-        self.grad_buffer = self._grad.tensor
+        self.grad_buffer = torch.zeros(padded_numel, dtype=torch.bfloat16, device=device)   # read locally only
         self.shard_size = shard_size
-        self.shard_start = shard_size * g.rank
         self.reduced = torch.zeros(shard_size, dtype=torch.bfloat16, device=device)
         self.norm_out = torch.zeros(1, dtype=torch.float32, device=device)
         self.scratch = torch.zeros(_lib.lib().gfs_dp_reduce_norm_scratch_floats(), dtype=torch.float32,
                                    device=device)
-        self.site_ready = g.site("dp:ready")
+        self.site_push = g.site("dp:push")
         self.site_norm = g.site("dp:norm")
         self.site_param = g.site("dp:param")
 
-    def reduce_and_norm(self) -> None:
+    # ---- layout helpers ----
+    def shard_slices(self, rank: int | None = None):
+        """``(flat_start, flat_end, shard_start)`` of every slice owned by ``rank`` (default: this rank)."""
+        r = self.grp.rank if rank is None else rank
+        return [(f + r * s, f + (r + 1) * s, o) for f, s, o in zip(self.flat0, self.slices, self.offs)]
+
+    def gather_shard(self, flat: torch.Tensor, rank: int | None = None) -> torch.Tensor:
+        """This rank's shard of a flat-buffer-shaped tensor (copy, in shard order)."""
+        return torch.cat([flat[a:b] for a, b, _ in self.shard_slices(rank)])
+
+    def push_bucket(self, b: int, max_ctas: int = 0) -> None:
         g = self.grp
-        rc = _lib.lib().gfs_dp_reduce_norm(
-            self._grad.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), self.shard_start,
-            self.shard_size, g.world, g.rank, self.site_ready.slot0, ctypes.byref(self.site_ready.target),
-            self.site_norm.slot0, ctypes.byref(self.site_norm.target), self.scratch.data_ptr(), WAIT_NS,
+        rc = _lib.lib().gfs_dp_push_grads(
+            self.grad_buffer.data_ptr(), self._stage.ptrs, g.flag_ptrs, self.nb, self._c_flat0, self._c_slice,
+            self._c_off, b, g.world, g.rank, self.site_push.slot0, ctypes.byref(self.site_push.target), max_ctas,
             _lib.stream_ptr())
-        _lib.check(rc, "gfs_dp_reduce_norm")
+        _lib.check(rc, "gfs_dp_push_grads")
+
+    def sum_and_norm(self) -> None:
+        g = self.grp
+        rc = _lib.lib().gfs_dp_sum_norm(
+            self._stage.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), self.shard_size, g.world, g.rank,
+            self.site_push.slot0, self.site_push.target.value, self.site_norm.slot0,
+            ctypes.byref(self.site_norm.target), self.scratch.data_ptr(), WAIT_NS, _lib.stream_ptr())
+        _lib.check(rc, "gfs_dp_sum_norm")
 
     def adam_and_gather(self, master, exp_avg, exp_avg_sq, *, step, lr, beta1, beta2, eps, weight_decay, clip,
                         grad_scale, extern_sumsq=None, step_dev=None) -> None:
@@ -395,16 +436,28 @@ class DataParallelComm:
         bc2_sqrt = math.sqrt(1.0 - beta2 ** step)
         rc = _lib.lib().gfs_dp_adam_gather(
             self._param.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), master.data_ptr(),
-            exp_avg.data_ptr(), exp_avg_sq.data_ptr(), self.shard_start, self.shard_size, g.world, g.rank,
-            self.site_norm.slot0, self.site_norm.target.value, self.site_param.slot0,
+            exp_avg.data_ptr(), exp_avg_sq.data_ptr(), self.nb, self._c_flat0, self._c_slice, self._c_off, g.world,
+            g.rank, self.site_norm.slot0, self.site_norm.target.value, self.site_param.slot0,
             ctypes.byref(self.site_param.target), _lib.ptr(extern_sumsq), self.norm_out.data_ptr(),
             lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, clip, grad_scale, _lib.ptr(step_dev), WAIT_NS,
             _lib.stream_ptr())
         _lib.check(rc, "gfs_dp_adam_gather")
 
     def step(self, opt, state, *, step, lr, beta1, beta2, eps, weight_decay, clip, grad_scale) -> None:
+        """Everything after the pushes (the caller has pushed every bucket, on this stream or on a
+        stream this one has waited for)."""
         with _lib.nvtx("fused:dp_reduce_scatter_norm"):
-            self.reduce_and_norm()
+            self.sum_and_norm()
+        if opt._rep_index_shard is not None and not opt.reference_quirks and opt._rep_index_shard.numel():
+            # gradients of parameters replicated over TP (norm weights, row-parallel biases): sum this
+            # shard's share of them over the TP group (commutes with the DP sum done above)
+            if opt._rep_index_shard.numel() % 8 == 0:
+                sum_over_tp_inplace(self.reduced, opt._rep_index_shard)
+            else:
+                import torch.distributed as dist
+                vals = self.reduced.index_select(0, opt._rep_index_shard)
+                dist.all_reduce(vals, group=ps.get_tensor_model_parallel_group())
+                self.reduced.index_copy_(0, opt._rep_index_shard, vals)
         extern = None
         if opt.tp_world_size > 1 and not opt.reference_quirks and clip > 0:
             # global norm over TP x DP with replicated parameters counted once

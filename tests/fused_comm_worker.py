@@ -193,6 +193,7 @@ def main():
     ps.initialize_parallel_state(1)
     traj = {}
     finals = {}
+    states = {}
     for impl in ("nccl", "fused"):
         ps.set_comm_impl(impl)
         eng = TrainEngine(cfg, lr=1e-3, seed=3)
@@ -202,6 +203,13 @@ def main():
             losses.append(float(eng.train_step(tt[:, :-1].contiguous().to(dev), tt[:, 1:].contiguous().to(dev))))
         traj[impl] = losses
         finals[impl] = eng.optimizer.param_buffer.float().clone()
+        # optimizer state in the reference's layout (contiguous shard per DP rank), whatever the
+        # layout in use; and a save/load round trip must leave the master weights unchanged
+        osd = eng.optimizer.state_dict()["state"][0]
+        states[impl] = (osd["exp_avg"].float().clone(), osd["exp_avg_sq"].float().clone())
+        before = eng.optimizer.fp32_master_shard.detach().clone()
+        eng.optimizer.load_full_state_dict(eng.optimizer.full_state_dict())
+        assert torch.equal(before, eng.optimizer.fp32_master_shard.detach()), f"{impl}: state round trip"
         torch.cuda.synchronize()
         _lib.raise_on_status()
         # replicas must agree after the parameter all-gather
@@ -214,7 +222,9 @@ def main():
     for a, b in zip(traj["fused"], traj["nccl"]):
         assert abs(a - b) < 2e-2, traj
     close(finals["fused"], finals["nccl"], "DP final parameters", 2e-3)
-    log("DP training ok")
+    close(states["fused"][0], states["nccl"][0], "AdamW exp_avg in the reference layout", 2e-2)
+    close(states["fused"][1], states["nccl"][1], "AdamW exp_avg_sq in the reference layout", 2e-2)
+    log("DP training ok (bucketed gradient push overlapped with backward; state_dict layout converted)")
     eng = TrainEngine(cfg, lr=1e-3, seed=3, cuda_graph=True, graph_warmup=2)
     graphed = []
     for t in data:

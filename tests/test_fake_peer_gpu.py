@@ -156,8 +156,9 @@ def test_embedding_scatter(tp2, cuda_device):
 
 
 def test_data_parallel_optimizer_kernels(cuda_device):
-    """Gradient reduce-scatter by peer loads + norm, then clip + AdamW + parameter all-gather by peer
-    stores, as DP rank 0 of 2, against torch.optim.AdamW on the summed gradient."""
+    """Per-bucket gradient push, sum of the staged contributions + norm, then clip + AdamW +
+    parameter all-gather by peer stores, as DP rank 0 of 2 with two buckets (so the shard is the
+    concatenation of one slice per bucket), against torch.optim.AdamW on the summed gradient."""
     from gpt_from_scratch_b200.parallel import fused_comm
     from gpt_from_scratch_b200.parallel import parallel_state as ps
     from gpt_from_scratch_b200.parallel.fake_peer import fake_peers
@@ -168,20 +169,26 @@ def test_data_parallel_optimizer_kernels(cuda_device):
         grp = groups["dp"]
         g = torch.Generator(device="cuda").manual_seed(7)
         n, shard = 40960, 20480
-        dpc = fused_comm.DataParallelComm(n, shard, cuda_device)
+        cut, s0, s1 = 16384, 8192, 12288                 # bucket 0 = [0, cut), slices of s0; bucket 1: slices of s1
+        dpc = fused_comm.DataParallelComm(n, shard, cuda_device, buckets=[(0, cut), (cut, n)])
+        own = lambda t, r: torch.cat([t[r * s0:(r + 1) * s0], t[cut + r * s1:cut + (r + 1) * s1]])  # noqa: E731
         g0 = (torch.randn(n, device=cuda_device, generator=g) * 0.05).bfloat16()
         g1 = (torch.randn(n, device=cuda_device, generator=g) * 0.05).bfloat16()
         dpc.grad_buffer.copy_(g0)
-        grp.rank_tensors(dpc._grad)[1].copy_(g1)
+        grp.rank_tensors(dpc._stage)[0].view(2, shard)[1] = own(g1, 0)       # what rank 1 pushed to us
         p0 = torch.randn(shard, device=cuda_device, generator=g)
         master, m, v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
         other_sumsq = 3.25                                   # what rank 1 would publish for its shard
         grp.rank_tensors(dpc._norm)[0][1] = other_sumsq
-        dpc.reduce_and_norm()
+        dpc.push_bucket(1, max_ctas=8)
+        dpc.push_bucket(0)
+        dpc.sum_and_norm()
         dpc.adam_and_gather(master, m, v, step=1, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
                             clip=1.0, grad_scale=1.0)
         torch.cuda.synchronize()
-        red = (g0[:shard].float() + g1[:shard].float()).bfloat16()
+        # our slices of rank 1's buckets went to ITS staging buffer, source slot 0
+        assert torch.equal(grp.rank_tensors(dpc._stage)[1].view(2, shard)[0], own(g0, 1))
+        red = (own(g0, 0).float() + own(g1, 0).float()).bfloat16()
         assert torch.equal(dpc.reduced, red)
         norm = (red.float().pow(2).sum() + other_sumsq).sqrt()
         assert abs(float(dpc.norm_out) - float(norm)) / float(norm) < 1e-4
@@ -190,9 +197,10 @@ def test_data_parallel_optimizer_kernels(cuda_device):
         ref.grad = red.float() * (1.0 / (float(norm) + 1e-6) if norm > 1.0 else 1.0)
         opt.step()
         assert (master - ref.detach()).abs().max() < 2e-6
-        # all-gather by peer stores: our shard landed in both parameter buffers
-        assert torch.equal(dpc.param_buffer[:shard], master.bfloat16())
-        assert torch.equal(grp.rank_tensors(dpc._param)[1][:shard], master.bfloat16())
+        # all-gather by peer stores: our shard landed, slice by slice, in both parameter buffers
+        for buf in (dpc.param_buffer, grp.rank_tensors(dpc._param)[1]):
+            assert torch.equal(own(buf, 0), master.bfloat16())
+            assert float(own(buf, 1).abs().sum()) == 0.0      # rank 1's slices untouched
 
 
 @pytest.mark.expects_status
