@@ -145,8 +145,9 @@ __global__ void ce_exchange_kernel(PeerTable t, const float* __restrict__ stats,
 //
 // so the gradient reduction of a bucket can start as soon as the backward pass has produced it,
 // with equal work for every rank. Three kernels:
-//   dp_push_grads   (per bucket, during backward, never waits): every rank stores the peers'
+//   dp_push_grads   (per bucket, during backward, never waits): every rank copies the peers'
 //                   slices of its local gradients into the owners' staging buffers over NVLink
+//                   (copy engines) and signals
 //   dp_sum_norm     (once, at the step): the owner waits for all pushes, sums the staged
 //                   contributions in rank order (fp32, rounded to bf16 like a bf16 reduce-scatter)
 //                   and publishes the squared norm of its shard to every rank
@@ -160,36 +161,12 @@ struct BucketTable {
   long long off[MAX_BUCKETS + 1];  // first element of bucket b's slice in a shard; off[nb] = shard size
 };
 
-// staging buffer of rank r: [world (source)][shard] bf16
-__global__ void __launch_bounds__(256)
-dp_push_grads_kernel(PeerTable stage, const __nv_bfloat16* __restrict__ grads, long long flat0, long long slice,
-                     long long off, long long shard, int world, int rank, int slot) {
-  const long long vps = slice >> 3;                 // 16-byte vectors per slice
-  const long long total = vps * world;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  constexpr int U = 4;                              // vectors in flight per thread
-  for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < total; v0 += U * stride) {
-    uint4 val[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * stride;
-      if (v < total) {
-        const int dst = static_cast<int>((rank + 1 + v / vps) % world);      // peers first, own slice last
-        val[u] = *reinterpret_cast<const uint4*>(grads + flat0 + dst * slice + ((v % vps) << 3));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * stride;
-      if (v < total) {
-        const int dst = static_cast<int>((rank + 1 + v / vps) % world);
-        __nv_bfloat16* to = static_cast<__nv_bfloat16*>(stage.buf[dst]) + rank * shard + off + ((v % vps) << 3);
-        *reinterpret_cast<uint4*>(to) = val[u];
-      }
-    }
-  }
+// staging buffer of rank r: [world (source)][shard] bf16. The pushes themselves are copy-engine
+// transfers (cudaMemcpyAsync over NVLink, issued by gfs_dp_push_grads): they overlap the backward
+// pass without taking SMs from its persistent kernels, which are sized to the whole GPU. This
+// kernel, ordered after a bucket's copies on the same stream, tells every owner they have landed.
+__global__ void dp_push_signal_kernel(PeerTable stage, int world, int rank, int slot) {
   __threadfence_system();
-  __syncthreads();
   if (threadIdx.x < world) red_release_sys_add_u32(stage.flags[threadIdx.x] + slot + rank, 1u);
 }
 
@@ -208,7 +185,7 @@ dp_sum_norm_kernel(PeerTable stage, PeerTable norm, __nv_bfloat16* __restrict__ 
   float acc = 0.f;
   const long long nvec = shard >> 3;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  constexpr int U = 2;
+  constexpr int U = (WORLD > 0 && WORLD <= 4) ? 4 : 2;     // U x world 16-byte loads in flight per thread
   for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += U * stride) {
     uint4 in[U][WORLD > 0 ? WORLD : MAX_PEERS];
 #pragma unroll
@@ -448,23 +425,29 @@ static int fill_buckets(BucketTable& bt, int nb, const long long* flat0, const l
 }
 
 // Pushes bucket `b` of the local gradient buffer: slice r goes to rank r's staging buffer
-// (peer_stage[r] = rank r's [world][shard] bf16 buffer), at [this rank][off[b] ...). Never waits;
-// may run on a side stream while the backward pass continues. max_ctas > 0 limits the grid.
-// *target_inout: cumulative number of signals each owner must see from each source.
+// (peer_stage[r] = rank r's [world][shard] bf16 buffer), at [this rank][off[b] ...), by one
+// copy-engine transfer per destination (peers first), followed by a one-warp kernel that signals
+// the owners. Never waits; meant for a side stream while the backward pass continues.
+// *target_inout: cumulative number of signals each owner must see from each source (+1 per call).
 int gfs_dp_push_grads(const void* grads, const unsigned long long* peer_stage, const unsigned long long* peer_flags,
                       int nb, const long long* flat0, const long long* slice, const long long* off, int b, int world,
-                      int rank, int slot_push, unsigned int* target_inout, int max_ctas, void* stream) {
+                      int rank, int slot_push, unsigned int* target_inout, void* stream_) {
   PeerTable st;
   BucketTable bt;
   if (fill_table(st, peer_stage, peer_flags, world) || fill_buckets(bt, nb, flat0, slice, off)) return -1;
   if (b < 0 || b >= nb) return -1;
-  const long long vecs = (bt.slice[b] >> 3) * world;
-  int grid = resident_grid(static_cast<int>(std::min<long long>((vecs + 4 * 256 - 1) / (4 * 256), 1 << 20)));
-  if (max_ctas > 0) grid = std::min(grid, max_ctas);
-  *target_inout += static_cast<unsigned int>(grid);
-  dp_push_grads_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      st, static_cast<const __nv_bfloat16*>(grads), bt.flat0[b], bt.slice[b], bt.off[b], bt.off[nb], world, rank,
-      slot_push);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(grads);
+  const size_t bytes = static_cast<size_t>(bt.slice[b]) * sizeof(__nv_bfloat16);
+  for (int q = 0; q < world; ++q) {
+    const int dst = (rank + 1 + q) % world;
+    __nv_bfloat16* to = static_cast<__nv_bfloat16*>(st.buf[dst]) + rank * bt.off[nb] + bt.off[b];
+    if (cudaMemcpyAsync(to, g + bt.flat0[b] + dst * bt.slice[b], bytes, cudaMemcpyDeviceToDevice, stream) !=
+        cudaSuccess)
+      return -12;
+  }
+  *target_inout += 1u;
+  dp_push_signal_kernel<<<1, 32, 0, stream>>>(st, world, rank, slot_push);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -1017,9 +1017,17 @@ static int gemm2_comm_impl(int mode, const void* a, int lda, const void* B, int 
                            const void* residual, int ldr, int M, int N, int K, int b_mn_major, int world, int rank,
                            const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
                            unsigned int* target_inout, const void* rope_cos, const void* rope_sin, int rope_cols,
-                           int rope_d, int rope_b, long long wait_ns, void* ce_partials, void* stream_) {
+                           int rope_d, int rope_b, long long wait_ns, void* ce_partials, void* stream_,
+                           int swi_mode = 0, void* swi_extra = nullptr, int swi_ld = 0) {
+  // swi_mode 1 / 2 (all-gather only): the SwiGLU epilogues of gfs_gemm2_bf16_swiglu. Mode 1: N = 2I
+  // columns of the [gate | up] projection, out = gu [M, 2I], swi_extra = act [M, I]. Mode 2: N = I
+  // columns of d_act, B stored [K, I], out = d_gu [M, 2I], swi_extra = gu [M, 2I].
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (mode != COMM_ALLGATHER && mode != COMM_REDUCE_SCATTER) return -1;
+  if (swi_mode != 0 && (mode != COMM_ALLGATHER || ce_partials != nullptr || rope_cos != nullptr || residual ||
+                        swi_extra == nullptr || (swi_ld & 7) || (reinterpret_cast<uintptr_t>(swi_extra) & 15) ||
+                        b_mn_major != (swi_mode == 2) || (swi_mode == 1 && (N & 15))))
+    return -1;
   if (ce_partials != nullptr && (mode != COMM_ALLGATHER || b_mn_major || rope_cos != nullptr)) return -1;
   if (world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return -1;
   if (M <= 0 || N <= 0 || K <= 0 || (M % world) != 0) return -1;
@@ -1071,8 +1079,20 @@ static int gemm2_comm_impl(int mode, const void* a, int lda, const void* B, int 
   const CUtensorMap* tb = b_mn_major ? gfs_host::tmap_2d_cached(B, K, N, ldb, 64, 64)
                                      : gfs_host::tmap_2d_cached(B, N, K, ldb, BNH, 64);
   if (ta == nullptr || tb == nullptr) return -3;
+  if (swi_mode == 1) {
+    p.swi_I = N / 2;
+    p.tiles_n = (p.swi_I + BN / 2 - 1) / (BN / 2);
+    p.swi_ld = swi_ld;
+    p.swi_act = static_cast<__nv_bfloat16*>(swi_extra);
+  } else if (swi_mode == 2) {
+    p.swi_I = N;
+    p.swi_ld = swi_ld;
+    p.swi_gu = static_cast<const __nv_bfloat16*>(swi_extra);
+  }
   *target_inout += increment;
   c.target = *target_inout;
+  if (swi_mode == 1) return launch2<false, false, COMM_ALLGATHER, 1>(ta, tb, p, grid, stream);
+  if (swi_mode == 2) return launch2<false, true, COMM_ALLGATHER, 2>(ta, tb, p, grid, stream);
   if (ce_partials != nullptr) {
     p.ce_partials = static_cast<float2*>(ce_partials);
     return launch2<false, false, COMM_ALLGATHER, 3>(ta, tb, p, grid, stream);
@@ -1092,6 +1112,24 @@ int gfs_gemm2_bf16_comm(int mode, const void* a, int lda, const void* B, int ldb
   return gemm2_comm_impl(mode, a, lda, B, ldb, out, ldo, residual, ldr, M, N, K, b_mn_major, world, rank, peer_bufs,
                          peer_flags, target_inout, rope_cos, rope_sin, rope_cols, rope_d, rope_b, wait_ns, nullptr,
                          stream_);
+}
+
+// Tensor-parallel SwiGLU MLP under sequence parallelism: the all-gather GEMMs with the SwiGLU
+// epilogues of gfs_gemm2_bf16_swiglu.
+//   mode 1: a = this rank's shard of x [M/world, K], B = w_gu [2I, K];  out = gu [M, 2I] (pitch ldo),
+//           extra = act [M, I] = silu(gate) * up (pitch ld_extra)
+//   mode 2: a = this rank's shard of dOut [M/world, K], B = w_down stored [K, I]; out = d_gu [M, 2I],
+//           extra = gu [M, 2I] (the forward's projection)
+// peer_bufs[p] = rank p's gathered [M, K] buffer. Returns -20 like gfs_gemm2_bf16_comm.
+int gfs_gemm2_bf16_comm_swiglu(int swi_mode, const void* a, int lda, const void* B, int ldb, void* out, int ldo,
+                               void* extra, int ld_extra, int M, int I, int K, int world, int rank,
+                               const unsigned long long* peer_bufs, const unsigned long long* peer_flags,
+                               unsigned int* target_inout, long long wait_ns, void* stream_) {
+  if (swi_mode != 1 && swi_mode != 2) return -1;
+  if ((I & 7) || I < 256) return (I & 7) ? -1 : -20;
+  return gemm2_comm_impl(COMM_ALLGATHER, a, lda, B, ldb, out, ldo, nullptr, 0, M, swi_mode == 1 ? 2 * I : I, K,
+                         swi_mode == 2 ? 1 : 0, world, rank, peer_bufs, peer_flags, target_inout, nullptr, nullptr, 0, 0,
+                         1, wait_ns, nullptr, stream_, swi_mode, extra, ld_extra);
 }
 
 // Vocabulary-parallel LM head under sequence parallelism: the all-gather GEMM

@@ -41,6 +41,11 @@ class ParallelMLP(nn.Module):
                 if residual is not None:
                     out = out + residual
             return out
+        if fused_comm_active and self.gate_up_proj.bias is None and self.down_proj.bias is None:
+            from ..parallel import fused_comm
+            if fused_comm.fused_mlp_eligible(hidden_states, w_gu, w_down):
+                # gather -> gate|up GEMM + SwiGLU epilogue -> down GEMM -> reduce-scatter (+ residual)
+                return fused_comm.swiglu_mlp(hidden_states, w_gu, w_down, residual)
         gu = self.gate_up_proj(hidden_states)              # [S, B, 2I/P]
         S, B, W = gu.shape
         act = swiglu(gu.reshape(S * B, W)).view(S, B, W // 2)

@@ -93,12 +93,14 @@ def _declare(lib: ctypes.CDLL) -> None:
                                  ctypes.c_longlong, vp], i),
         "gfs_gemm2_bf16_allgather_ce": ([vp, i, vp, i, vp, i, vp, i, i, i, i, i, ulp, ulp, uip, ctypes.c_longlong,
                                          vp], i),
+        "gfs_gemm2_bf16_comm_swiglu": ([i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, ulp, ulp, uip,
+                                        ctypes.c_longlong, vp], i),
         "gfs_symm_barrier": ([ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_allgather": ([vp, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_embedding_scatter": ([vp, vp, i, i, i, i, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_ce_exchange": ([vp, vp, vp, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_dp_reduce_norm_scratch_floats": ([], i),
-        "gfs_dp_push_grads": ([vp, ulp, ulp, i, lp, lp, lp, i, i, i, i, uip, i, vp], i),
+        "gfs_dp_push_grads": ([vp, ulp, ulp, i, lp, lp, lp, i, i, i, i, uip, vp], i),
         "gfs_dp_sum_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, i, i, i, ctypes.c_uint, i, uip, vp,
                              ctypes.c_longlong, vp], i),
         "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, i, lp, lp, lp, i, i, i, ctypes.c_uint, i, uip, vp, vp,

@@ -219,6 +219,12 @@ class _WgradQueue:
         if len(self.items) == self.MAX_GROUP or self.tiles >= _PAIR_MIN_TILES:
             self.flush()
 
+    def uses(self, tensor: torch.Tensor) -> bool:
+        """True if a parked problem reads from ``tensor``'s memory."""
+        lo = tensor.data_ptr()
+        hi = lo + tensor.numel() * tensor.element_size()
+        return any(lo <= it[k].data_ptr() < hi for it in self.items for k in (0, 1))
+
     def flush(self) -> None:
         items, self.items, self.tiles = self.items, [], 0
         if not items:
@@ -250,6 +256,13 @@ _WGRAD_GROUPING = os.environ.get("GFS_WGRAD_GROUPING", "1") != "0"
 def flush_wgrad() -> None:
     """Launch every parked weight-gradient GEMM (no-op when nothing is parked)."""
     _wgrad_queue.flush()
+
+
+def flush_wgrad_if_uses(tensor: torch.Tensor) -> None:
+    """Launch the parked weight-gradient GEMMs if one of them still reads ``tensor`` (call before a
+    reused buffer is overwritten)."""
+    if _wgrad_queue.items and _wgrad_queue.uses(tensor):
+        _wgrad_queue.flush()
 
 
 def linear_wgrad_to_sink(dy2d: torch.Tensor, x2d: torch.Tensor, sink) -> None:

@@ -253,8 +253,7 @@ class DistributedOptimizer:
         ev.record()
         self._push_stream.wait_event(ev)
         with torch.cuda.stream(self._push_stream):
-            # a modest grid: the copy rides along with the backward kernels instead of displacing them
-            self._dp_comm.push_bucket(b, max_ctas=32)
+            self._dp_comm.push_bucket(b)         # copy-engine transfers + a one-warp signal kernel
 
     def _finish_pushes(self) -> None:
         """Push whatever the backward pass did not (everything when overlap is off) and make the

@@ -168,8 +168,7 @@ class _AllGatherLinear(torch.autograd.Function):
         sink = ctx.sink
         dw = None
         if sink is not None:
-            gemm_ops.linear_wgrad(dy2, x_full, out=sink.target(), accumulate=sink.consume_accumulate())
-            sink.done()
+            gemm_ops.linear_wgrad_to_sink(dy2, x_full, sink)     # small problems join the layer's grouped launch
         else:
             dw = gemm_ops.linear_wgrad(dy2, x_full)
         return dx.view(in_shape), dw, None, None, None, None
@@ -225,14 +224,14 @@ class _LinearReduceScatter(torch.autograd.Function):
         # dX = gather_S(dOut) @ W: all-gather fused into the dgrad GEMM; the gathered dOut is
         # then reused by the wgrad GEMM (gathered once, used twice)
         gathered, site = grp.pooled("agb", M * N, torch.bfloat16)
+        gemm_ops.flush_wgrad_if_uses(gathered.tensor)    # a parked weight gradient may still read this buffer
         dx = torch.empty((M, Kp), dtype=torch.bfloat16, device=d2.device)
         _gemm_comm(MODE_AG, d2, weight, dx, None, M, Kp, N, True, grp, gathered, site)
         dy_full = gathered.tensor.view(M, N)
         sink = ctx.sink
         dw = None
         if sink is not None:
-            gemm_ops.linear_wgrad(dy_full, x2, out=sink.target(), accumulate=sink.consume_accumulate())
-            sink.done()
+            gemm_ops.linear_wgrad_to_sink(dy_full, x2, sink)
         else:
             dw = gemm_ops.linear_wgrad(dy_full, x2)
         return dx.view(in_shape), dw, (dout if ctx.has_res else None), None
@@ -249,6 +248,102 @@ def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, residual: torch
         out = mappings.reduce_scatter_to_sequence_parallel_region(linear_with_sink(x, weight))
         return out + residual if residual is not None else out
     return _LinearReduceScatter.apply(x, weight, residual, GradSink.of(weight))
+
+
+# --------------------------------------------------------------------------- SwiGLU MLP
+def _swiglu_comm(swi_mode, a, b, out, extra, M, I, K, grp, buf, site) -> None:
+    with _lib.nvtx("fused:allgather_gemm_swiglu_fwd" if swi_mode == 1 else "fused:allgather_gemm_swiglu_bwd"):
+        rc = _lib.lib().gfs_gemm2_bf16_comm_swiglu(
+            swi_mode, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
+            extra.data_ptr(), extra.stride(0), M, I, K, grp.world, grp.rank, buf.ptrs, _site_flag_ptrs(grp, site),
+            ctypes.byref(site.target), WAIT_NS, _lib.stream_ptr())
+    _lib.check(rc, "gfs_gemm2_bf16_comm_swiglu")
+
+
+class _FusedCommMLP(torch.autograd.Function):
+    """Tensor-parallel SwiGLU MLP on the sequence shard: all-gather -> gate|up GEMM with
+    ``silu(gate) * up`` in its epilogue -> down GEMM -> reduce-scatter (+ residual). Backward:
+    all-gather of dOut -> dgrad of the down projection whose epilogue applies the SwiGLU backward
+    (writes d_gate | d_up), then the gate|up dgrad with its reduce-scatter; the two gathered
+    buffers feed the weight gradients. No standalone activation kernel in either direction."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w_gu, w_down, residual, sink_gu, sink_down, site_key):
+        grp = symm.get_group("tp")
+        H = x_shard.shape[-1]
+        I = w_gu.shape[0] // 2
+        x2 = _as2d(x_shard, H)
+        Ms = x2.shape[0]
+        M = Ms * grp.world
+        gathered = grp.alloc(("ag", site_key), M * H, torch.bfloat16)     # lives until backward
+        site = grp.site(("ag", site_key))
+        gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=x2.device)
+        act = torch.empty((M, I), dtype=torch.bfloat16, device=x2.device)
+        _swiglu_comm(1, x2, w_gu, gu, act, M, I, H, grp, gathered, site)
+        stage, site_rs = grp.pooled("rs", M * H, torch.bfloat16)
+        out = torch.empty((Ms, H), dtype=torch.bfloat16, device=x2.device)
+        res2 = _as2d(residual, H) if residual is not None else None
+        _gemm_comm(MODE_RS, act, w_down, out, res2, M, H, I, False, grp, stage, site_rs)
+        ctx.save_for_backward(gu, act, w_gu, w_down)
+        ctx.gathered = gathered
+        ctx.sinks = (sink_gu, sink_down)
+        ctx.has_res = residual is not None
+        ctx.dims = (M, Ms, H, I, x_shard.shape)
+        return out.view(x_shard.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        gu, act, w_gu, w_down = ctx.saved_tensors
+        sink_gu, sink_down = ctx.sinks
+        grp = symm.get_group("tp")
+        M, Ms, H, I, in_shape = ctx.dims
+        d2 = _as2d(dout, H)
+        # d_gu = swiglu'(gather_S(dOut) @ W_down, gu): all-gather fused into the dgrad GEMM, SwiGLU
+        # backward in its epilogue; the gathered dOut then feeds the down projection's wgrad
+        gathered_d, site_d = grp.pooled("agb", M * H, torch.bfloat16)
+        gemm_ops.flush_wgrad_if_uses(gathered_d.tensor)
+        dgu = torch.empty_like(gu)
+        _swiglu_comm(2, d2, w_down, dgu, gu, M, I, H, grp, gathered_d, site_d)
+        dy_full = gathered_d.tensor.view(M, H)
+        dw_down = dw_gu = None
+        if sink_down is not None:
+            gemm_ops.linear_wgrad_to_sink(dy_full, act, sink_down)
+        else:
+            dw_down = gemm_ops.linear_wgrad(dy_full, act)
+        # dX = reduce_scatter(d_gu @ W_gu)
+        stage, site_rs = grp.pooled("rs", M * H, torch.bfloat16)
+        dx = torch.empty((Ms, H), dtype=torch.bfloat16, device=d2.device)
+        _gemm_comm(MODE_RS, dgu, w_gu, dx, None, M, H, 2 * I, True, grp, stage, site_rs)
+        x_full = ctx.gathered.tensor.view(M, H)
+        if sink_gu is not None:
+            gemm_ops.linear_wgrad_to_sink(dgu, x_full, sink_gu)
+        else:
+            dw_gu = gemm_ops.linear_wgrad(dgu, x_full)
+        return dx.view(in_shape), dw_gu, dw_down, (dout if ctx.has_res else None), None, None, None
+
+
+def fused_mlp_eligible(x_shard: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """The SwiGLU epilogues exist on the CTA-pair kernel only: rows per rank a multiple of 256 and
+    enough tiles for it in both directions."""
+    if not (x_shard.is_cuda and x_shard.dtype == w_gu.dtype == w_down.dtype == torch.bfloat16 and
+            gemm_ops._PAIR_ENABLED):
+        return False
+    world = ps.get_tensor_model_parallel_world_size()
+    H = x_shard.shape[-1]
+    I = w_gu.shape[0] // 2
+    Ms = x_shard.numel() // H
+    M = Ms * world
+    if Ms % 256 or H % 8 or I % 8 or H < 256 or I < 256 or w_gu.stride(1) != 1 or w_down.stride(1) != 1:
+        return False
+    tiles_fwd = (M // 256) * ((I + 127) // 128)
+    tiles_bwd = (M // 256) * ((I + 255) // 256)
+    return min(tiles_fwd, tiles_bwd) >= gemm_ops._PAIR_MIN_TILES
+
+
+def swiglu_mlp(x_shard: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, residual=None) -> torch.Tensor:
+    """``reduce_scatter_S(swiglu(gather_S(x) @ w_gu^T) @ w_down^T) (+ residual)`` in two fused kernels."""
+    return _FusedCommMLP.apply(x_shard, w_gu, w_down, residual, GradSink.of(w_gu), GradSink.of(w_down),
+                               _weight_site_key(w_gu))
 
 
 # --------------------------------------------------------------------------- generic all-gather
@@ -361,9 +456,10 @@ class DataParallelComm:
     and no host sync:
 
     * ``push_bucket(b)``: as soon as the backward pass has finished bucket ``b`` of the flat
-      gradient buffer, every rank stores each peer's slice of it into that peer's staging buffer
-      over NVLink (the reduce-scatter's data movement, overlapped with the rest of backward; the
-      kernel never waits, so it cannot stall anything it shares the GPU with);
+      gradient buffer, every rank copies each peer's slice of it into that peer's staging buffer
+      over NVLink with the copy engines (the reduce-scatter's data movement, overlapped with the
+      rest of backward without taking SMs from it; nothing in it waits, so it cannot stall anything
+      it shares the GPU with), then signals the owners;
     * ``sum_and_norm()``: the owner sums the staged contributions in rank order + squared norm;
     * ``adam_and_gather()``: global-norm clip + AdamW on the fp32 shard + bf16 parameters stored
       into every rank's parameter buffer.
@@ -413,11 +509,11 @@ class DataParallelComm:
         """This rank's shard of a flat-buffer-shaped tensor (copy, in shard order)."""
         return torch.cat([flat[a:b] for a, b, _ in self.shard_slices(rank)])
 
-    def push_bucket(self, b: int, max_ctas: int = 0) -> None:
+    def push_bucket(self, b: int) -> None:
         g = self.grp
         rc = _lib.lib().gfs_dp_push_grads(
             self.grad_buffer.data_ptr(), self._stage.ptrs, g.flag_ptrs, self.nb, self._c_flat0, self._c_slice,
-            self._c_off, b, g.world, g.rank, self.site_push.slot0, ctypes.byref(self.site_push.target), max_ctas,
+            self._c_off, b, g.world, g.rank, self.site_push.slot0, ctypes.byref(self.site_push.target),
             _lib.stream_ptr())
         _lib.check(rc, "gfs_dp_push_grads")
 

@@ -93,6 +93,48 @@ def test_gemm_reduce_scatter_and_its_backward(tp2, cuda_device, Ms, Kp, N, pair,
     assert _rel(w.grad, dfull.t() @ x.detach().float()) < 1e-2
 
 
+def test_swiglu_mlp_under_fused_comm(tp2, cuda_device):
+    """gather -> gate|up GEMM with the SwiGLU epilogue -> down GEMM -> reduce-scatter (+ residual), and
+    its backward (SwiGLU backward in the epilogue of the all-gather-fed dgrad), against fp32."""
+    from gpt_from_scratch_b200.ops import gemm as gemm_ops
+    from gpt_from_scratch_b200.parallel import fused_comm
+    grp = tp2["tp"]
+    g = torch.Generator(device="cuda").manual_seed(21)
+    Ms, H, I = 256, 256, 384                   # I = this rank's share of the intermediate size
+    M = 2 * Ms
+    x0 = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16().requires_grad_()
+    x1 = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16()
+    w_gu = (torch.randn(2 * I, H, device=cuda_device, generator=g) * 0.08).bfloat16().requires_grad_()
+    w_dn = (torch.randn(H, I, device=cuda_device, generator=g) * 0.08).bfloat16().requires_grad_()
+    res = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16()
+    part1 = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16()    # rank 1's partial of our output rows
+    dout0 = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16()
+    dout1 = torch.randn(Ms, H, device=cuda_device, generator=g).bfloat16()
+    gathered = grp.alloc(("ag", fused_comm._weight_site_key(w_gu)), M * H, torch.bfloat16)
+    gathered.tensor.view(M, H)[Ms:] = x1
+    stage, _ = grp.pooled("rs", M * H, torch.bfloat16)
+    agb, _ = grp.pooled("agb", M * H, torch.bfloat16)
+    agb.tensor.view(M, H)[Ms:] = dout1
+    with gemm_ops.pair_min_tiles(1):
+        assert fused_comm.fused_mlp_eligible(x0, w_gu, w_dn)
+        stage.tensor.view(2, Ms, H)[1] = part1
+        y = fused_comm.swiglu_mlp(x0, w_gu, w_dn, res)
+        torch.cuda.synchronize()
+        stage.tensor.view(2, Ms, H)[1] = 0          # the backward's reduce-scatter reuses the staging buffer
+        y.backward(dout0)
+    torch.cuda.synchronize()
+    xf = torch.cat([x0.detach(), x1]).float().requires_grad_()
+    wg, wd = w_gu.detach().float().requires_grad_(), w_dn.detach().float().requires_grad_()
+    gu = (xf @ wg.t())
+    act = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    full = act @ wd.t()
+    assert _rel(y, full[:Ms] + part1.float() + res.float()) < 1.5e-2
+    full.backward(torch.cat([dout0, dout1]).float())
+    assert _rel(x0.grad, xf.grad[:Ms]) < 2e-2
+    assert _rel(w_gu.grad, wg.grad) < 2e-2
+    assert _rel(w_dn.grad, wd.grad) < 2e-2
+
+
 def test_lm_head_statistics_and_cross_entropy_exchange(tp2, cuda_device):
     """All-gather GEMM with the softmax statistics in its epilogue, then the exchange of (max,
     sum-exp, target logit) with the other vocabulary shard and the combine."""
@@ -180,7 +222,7 @@ def test_data_parallel_optimizer_kernels(cuda_device):
         master, m, v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
         other_sumsq = 3.25                                   # what rank 1 would publish for its shard
         grp.rank_tensors(dpc._norm)[0][1] = other_sumsq
-        dpc.push_bucket(1, max_ctas=8)
+        dpc.push_bucket(1)
         dpc.push_bucket(0)
         dpc.sum_and_norm()
         dpc.adam_and_gather(master, m, v, step=1, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
