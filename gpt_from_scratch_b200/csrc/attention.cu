@@ -436,13 +436,12 @@ constexpr int FWD64_SMEM = 2 * 16384 + FWD64_KS * 32768 + 256;
 // instead of once per item (at sequence length 1024 they were ~45 % of the kernel's time).
 // All barrier parities therefore run on counters that continue across items.
 //
-// OTMEM: the output accumulates in tensor memory (P V issued with accumulate) instead of being
+// The output accumulates in tensor memory (P V issued with accumulate) instead of being
 // folded into registers after every key block, and the running maximum is only raised when it
 // grows by more than 2^8 (any consistent offset gives the same softmax; the stale one keeps
 // exp2 arguments <= 8). Raising it rescales the accumulator in tensor memory, which after the
 // first blocks is rare. This frees the 64 accumulator registers per thread, so a block's 128
 // scores are loaded once and stay in registers for both the maximum and the exponentials.
-template <bool OTMEM>
 __global__ void __launch_bounds__(FWD64_THREADS, 1)
 flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const FwdParams p, int n_pairs, int n_items) {
@@ -561,7 +560,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       int g0 = 0;            // ring position of this item's first key block
       int cx[2] = {0, 0};    // blocks processed so far per query tile (barrier phase counters)
-      int it[2] = {0, 0};    // OTMEM: items in which the tile had blocks (phase of o_empty)
+      int it[2] = {0, 0};    // items in which the tile had blocks (phase of o_empty)
       for (int rnd = 0; rnd * G < n_items; ++rnd) {
         const int w = snake(rnd);
         if (w >= n_items) break;
@@ -623,16 +622,12 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
               const int c = cx[x] + j;
               const int g = g0 + j;
               if (mbar_try_wait(&p_full[x], c & 1) && mbar_try_wait(&v_full[g % KS], (g / KS) & 1)) {
-                if (OTMEM) {
-                  // the accumulator is overwritten once per item: wait until the softmax warps
-                  // have read the previous item's result out of it
-                  if (j == 0) mbar_wait(&o_empty[x], (it[x] & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
-                } else {
-                  mbar_wait(&o_empty[x], (c & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
-                }
+                // the accumulator is overwritten once per item: wait until the softmax warps
+                // have read the previous item's result out of it
+                if (j == 0) mbar_wait(&o_empty[x], (it[x] & 1) ^ 1u, wctx, STATUS_TIMEOUT_SOFTMAX);
                 tc_fence_after();
                 mma_tmn<8>(tmem_base + OP_COL + x * 64, tmem_base + P_COL + x * 64, smem_u32(Vs + (g % KS) * 16384),
-                           0, idesc_o, OTMEM && j > 0);
+                           0, idesc_o, j > 0);
                 umma_commit_e(&o_full[x]);
                 pv_iss[x] = j + 1;
                 if (pv_iss[ot] > j || j >= n_x[ot]) umma_commit_e(&v_empty[g % KS]);
@@ -676,7 +671,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const uint32_t p_addr = tmem_base + lane_base + P_COL + x * 64;
     const float sl2 = p.scale * LOG2E_F;
     int cdone = 0;  // blocks of this tile processed in earlier items
-    if constexpr (OTMEM) {
+    {
       for (int rnd = 0; rnd * G < n_items; ++rnd) {
         const int w = snake(rnd);
         if (w >= n_items) break;
@@ -868,165 +863,6 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           }
         }
         cdone += n_mine;
-      }
-    } else
-    for (int rnd = 0; rnd * G < n_items; ++rnd) {
-      const int w = snake(rnd);
-      if (w >= n_items) break;
-      int qp, bh, na, nbk;
-      decode(w, qp, bh, na, nbk);
-      const int b = bh / p.nh, h = bh % p.nh;
-      const int qtx = 2 * qp + x;
-      const int row_g = qtx * 128 + r;
-      const int n_mine = x == 0 ? na : nbk;
-      float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-      float o[D];
-#pragma unroll
-      for (int i = 0; i < D; ++i) o[i] = 0.f;
-
-      auto fold_pv = [&](int c, float alpha) {
-        mbar_wait(&o_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
-        tc_fence_after();
-        uint32_t wa[32], wb[32];
-        tmem_ld_32x32(o_addr, wa);
-        tmem_ld_32x32(o_addr + 32, wb);
-        tmem_ld_wait_for(wa);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) o[e] = fmaf(o[e], alpha, __uint_as_float(wa[e]));
-        tmem_ld_wait_for(wb);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) o[32 + e] = fmaf(o[32 + e], alpha, __uint_as_float(wb[e]));
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_empty[x]);
-      };
-
-      for (int j = 0; j < n_mine; ++j) {
-        const int c = cdone + j;
-        const bool need_mask = (p.causal && j == qtx) || ((j + 1) * 128 > p.S);
-        mbar_wait(&s_full[x], c & 1, wctx, STATUS_TIMEOUT_SOFTMAX);
-        tc_fence_after();
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-        uint32_t va[32], vb[32];
-        // per 32-column chunk: alive / mixed / dead for this warp's 32 rows (dead chunks cost no
-        // exponentials: on the diagonal block that is 3/8 of the work)
-        const int row_lo = qtx * 128 + quarter * 32;
-        auto kind_of = [&](int cc) {
-          return need_mask ? mask_class<false>(row_lo, row_lo + 31, j * 128 + cc, j * 128 + cc + 31, p.causal != 0, p.S)
-                           : 0;
-        };
-        auto max_chunk = [&](const uint32_t (&v)[32], int cc) {
-          const int kind = kind_of(cc);
-          if (kind == 2) return;
-          if (kind == 1) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int col_g = j * 128 + cc + e;
-              const bool dead = (p.causal && col_g > row_g) || col_g >= p.S;
-              mx0 = fmaxf(mx0, dead ? -INFINITY : __uint_as_float(v[e]));
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              mx0 = fmaxf(mx0, __uint_as_float(v[e]));
-              mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
-            }
-          }
-        };
-        tmem_ld_32x32(s_addr + 0, va);
-        tmem_ld_wait_for(va);
-        tmem_ld_32x32(s_addr + 32, vb);
-        max_chunk(va, 0);
-        tmem_ld_wait_for(vb);
-        tmem_ld_32x32(s_addr + 64, va);
-        max_chunk(vb, 32);
-        tmem_ld_wait_for(va);
-        tmem_ld_32x32(s_addr + 96, vb);
-        max_chunk(va, 64);
-        tmem_ld_wait_for(vb);
-        tmem_ld_32x32(s_addr + 0, va);  // first chunk of pass 2
-        max_chunk(vb, 96);
-        const float m_new = fmaxf(m, fmaxf(mx0, mx1));
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = fast_exp2((m - m_use) * sl2);
-        const float moff = m_use * sl2;
-        // the previous block's P V must have finished before P is overwritten; fold it in now
-        if (j > 0) fold_pv(c - 1, alpha_prev);
-        float rs0 = 0.f, rs1 = 0.f;
-        auto prob_chunk_impl = [&](auto mask_tag, const uint32_t (&v)[32], int cc) {
-          constexpr bool MASKED = decltype(mask_tag)::value;
-          uint32_t packed[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
-            float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
-            if constexpr (MASKED) {
-              const int col_g = j * 128 + cc + e;
-              const bool dead0 = (p.causal && col_g > row_g) || col_g >= p.S;
-              const bool dead1 = (p.causal && col_g + 1 > row_g) || col_g + 1 >= p.S;
-              x0 = dead0 ? 0.f : x0;
-              x1 = dead1 ? 0.f : x1;
-            }
-            rs0 += x0;
-            rs1 += x1;
-            packed[e >> 1] = pack_bf16x2(x0, x1);
-          }
-          tmem_st_32x16(p_addr + (cc >> 1), packed);
-        };
-        auto prob_chunk = [&](const uint32_t (&v)[32], int cc) {
-          const int kind = kind_of(cc);
-          if (kind == 2) {
-            uint32_t zeros[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) zeros[e] = 0u;
-            tmem_st_32x16(p_addr + (cc >> 1), zeros);
-          } else if (kind == 1) {
-            prob_chunk_impl(std::true_type{}, v, cc);
-          } else {
-            prob_chunk_impl(std::false_type{}, v, cc);
-          }
-        };
-        tmem_ld_wait_for(va);
-        tmem_ld_32x32(s_addr + 32, vb);
-        prob_chunk(va, 0);
-        tmem_ld_wait_for(vb);
-        tmem_ld_32x32(s_addr + 64, va);
-        prob_chunk(vb, 32);
-        tmem_ld_wait_for(va);
-        tmem_ld_32x32(s_addr + 96, vb);
-        prob_chunk(va, 64);
-        tmem_ld_wait_for(vb);
-        prob_chunk(vb, 96);
-        l = l * alpha + (rs0 + rs1);
-        m = m_new;
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&s_free[x]);   // this variant reads the scores twice: free only now
-          mbar_arrive(&p_full[x]);
-        }
-        alpha_prev = alpha;
-      }
-      if (n_mine > 0) fold_pv(cdone + n_mine - 1, alpha_prev);
-      cdone += n_mine;
-
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      if (row_g < p.S && n_mine > 0) {
-        __nv_bfloat16* dst = p.O + row_g * p.o_ss + b * p.o_bs + h * p.o_hs;
-#pragma unroll
-        for (int cc = 0; cc < D; cc += 8) {
-          uint4 wv;
-          wv.x = pack_bf16x2(o[cc + 0] * inv_l, o[cc + 1] * inv_l);
-          wv.y = pack_bf16x2(o[cc + 2] * inv_l, o[cc + 3] * inv_l);
-          wv.z = pack_bf16x2(o[cc + 4] * inv_l, o[cc + 5] * inv_l);
-          wv.w = pack_bf16x2(o[cc + 6] * inv_l, o[cc + 7] * inv_l);
-          *reinterpret_cast<uint4*>(dst + cc) = wv;
-        }
-      }
-      if (row_g < p.S_pad && n_mine > 0) {
-        const float mm = (m == -INFINITY) ? 0.f : m;
-        p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] = mm * p.scale + logf(fmaxf(l, 1e-37f));
       }
     }
   }
@@ -1546,25 +1382,14 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   const dim3 grid((S + 127) / 128, B * nh);
   static bool set64 = false, set128 = false;
   if (D == 64) {
-    const int smem = 16384 * 5 + 1 * 32768 + 256;   // single-buffered: two CTAs per SM
-    (void)smem;
     if (!set64) {
-      if (set_smem(flash_fwd64_kernel<false>, FWD64_SMEM) || set_smem(flash_fwd64_kernel<true>, FWD64_SMEM))
-        return -10;
+      if (set_smem(flash_fwd64_kernel, FWD64_SMEM)) return -10;
       set64 = true;
     }
-    // GFS_ATTN_FWD_OTMEM=0 selects the variant that folds the output into registers per key block
-    static const bool otmem = [] {
-      const char* e = std::getenv("GFS_ATTN_FWD_OTMEM");
-      return !(e && e[0] == '0');
-    }();
     const int n_pairs = (static_cast<int>(grid.x) + 1) / 2;
     const int n_items = n_pairs * B * nh;
     const int ctas = std::min(n_items, gfs_host::sm_count());
-    if (otmem)
-      flash_fwd64_kernel<true><<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
-    else
-      flash_fwd64_kernel<false><<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
+    flash_fwd64_kernel<<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
   } else {
     const int smem = 32768 * 5 + 2 * 32768 + 256;
     if (!set128) { if (set_smem(flash_fwd_kernel<128, 2>, smem)) return -10; set128 = true; }

@@ -39,8 +39,7 @@ struct PeerTable {
 __device__ __forceinline__ void cta_signal_all_and_wait(const PeerTable& t, int world, int rank, int slot0,
                                                         uint32_t target, unsigned long long wait_ns,
                                                         uint32_t* status) {
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // orders every thread's stores before the releases below (which are cumulative)
   if (threadIdx.x < world) red_release_sys_add_u32(t.flags[threadIdx.x] + slot0 + rank, 1u);
   if (threadIdx.x < world)
     wait_flag_reached(t.flags[rank] + slot0 + threadIdx.x, target, wait_ns, status,
@@ -166,59 +165,68 @@ struct BucketTable {
 // pass without taking SMs from its persistent kernels, which are sized to the whole GPU. This
 // kernel, ordered after a bucket's copies on the same stream, tells every owner they have landed.
 __global__ void dp_push_signal_kernel(PeerTable stage, int world, int rank, int slot) {
-  __threadfence_system();
   if (threadIdx.x < world) red_release_sys_add_u32(stage.flags[threadIdx.x] + slot + rank, 1u);
 }
 
 template <int WORLD>
 __global__ void __launch_bounds__(256)
-dp_sum_norm_kernel(PeerTable stage, PeerTable norm, __nv_bfloat16* __restrict__ reduced, long long shard, int world_rt,
-                   int rank, int slot_push, uint32_t target_push, int slot_norm, float* __restrict__ partials,
-                   unsigned int* __restrict__ ticket, unsigned long long wait_ns, uint32_t* status) {
+dp_sum_norm_kernel(PeerTable stage, PeerTable norm, const __nv_bfloat16* __restrict__ grads, BucketTable bt,
+                   __nv_bfloat16* __restrict__ reduced, int world_rt, int rank, int slot_push, uint32_t target_push,
+                   int slot_norm, float* __restrict__ partials, unsigned int* __restrict__ ticket,
+                   unsigned long long wait_ns, uint32_t* status) {
   const int world = WORLD > 0 ? WORLD : world_rt;
-  // every source's pushes of all buckets must have landed in our staging buffer
-  if (threadIdx.x < world)
+  constexpr int WMAX = WORLD > 0 ? WORLD : MAX_PEERS;
+  // every peer's pushes of all buckets must have landed in our staging buffer (this rank's own
+  // contribution is read straight from its gradient buffer: nothing is staged for it)
+  if (threadIdx.x < world && threadIdx.x != rank)
     wait_flag_reached(stage.flags[rank] + slot_push + threadIdx.x, target_push, wait_ns, status,
                       0xD1000000u | (threadIdx.x << 4) | rank);
   __syncthreads();
   const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(stage.buf[rank]);
+  const long long shard = bt.off[bt.nb];
   float acc = 0.f;
-  const long long nvec = shard >> 3;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   constexpr int U = (WORLD > 0 && WORLD <= 4) ? 4 : 2;     // U x world 16-byte loads in flight per thread
-  for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += U * stride) {
-    uint4 in[U][WORLD > 0 ? WORLD : MAX_PEERS];
+  for (int b = 0; b < bt.nb; ++b) {
+    const long long e_lo = bt.off[b];
+    const long long nvec = (bt.off[b + 1] - e_lo) >> 3;
+    const __nv_bfloat16* own = grads + bt.flat0[b] + rank * bt.slice[b];      // our slice of bucket b
+    for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += U * stride) {
+      uint4 in[U][WMAX];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * stride;
-      if (v < nvec) {
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < nvec) {
 #pragma unroll
-        for (int r = 0; r < (WORLD > 0 ? WORLD : MAX_PEERS); ++r)
-          if (r < world) in[u][r] = *reinterpret_cast<const uint4*>(mine + r * shard + (v << 3));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * stride;
-      if (v >= nvec) continue;
-      float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int r = 0; r < (WORLD > 0 ? WORLD : MAX_PEERS); ++r) {
-        if (r < world) {
-          const float2 a = unpack_bf16x2(in[u][r].x), b = unpack_bf16x2(in[u][r].y), c = unpack_bf16x2(in[u][r].z),
-                       d = unpack_bf16x2(in[u][r].w);
-          sum[0] += a.x; sum[1] += a.y; sum[2] += b.x; sum[3] += b.y;
-          sum[4] += c.x; sum[5] += c.y; sum[6] += d.x; sum[7] += d.y;
+          for (int r = 0; r < WMAX; ++r)
+            if (r < world)
+              in[u][r] = (r == rank) ? *reinterpret_cast<const uint4*>(own + (v << 3))
+                                     : *reinterpret_cast<const uint4*>(mine + r * shard + e_lo + (v << 3));
         }
       }
-      uint4 o;
-      o.x = pack_bf16x2(sum[0], sum[1]);
-      o.y = pack_bf16x2(sum[2], sum[3]);
-      o.z = pack_bf16x2(sum[4], sum[5]);
-      o.w = pack_bf16x2(sum[6], sum[7]);
-      *reinterpret_cast<uint4*>(reduced + (v << 3)) = o;
-      const float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), d = unpack_bf16x2(o.w);
-      acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * stride;
+        if (v >= nvec) continue;
+        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int r = 0; r < WMAX; ++r) {
+          if (r < world) {
+            const float2 a = unpack_bf16x2(in[u][r].x), b2 = unpack_bf16x2(in[u][r].y),
+                         c = unpack_bf16x2(in[u][r].z), d = unpack_bf16x2(in[u][r].w);
+            sum[0] += a.x; sum[1] += a.y; sum[2] += b2.x; sum[3] += b2.y;
+            sum[4] += c.x; sum[5] += c.y; sum[6] += d.x; sum[7] += d.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(sum[0], sum[1]);
+        o.y = pack_bf16x2(sum[2], sum[3]);
+        o.z = pack_bf16x2(sum[4], sum[5]);
+        o.w = pack_bf16x2(sum[6], sum[7]);
+        *reinterpret_cast<uint4*>(reduced + e_lo + (v << 3)) = o;
+        const float2 a = unpack_bf16x2(o.x), b2 = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), d = unpack_bf16x2(o.w);
+        acc += a.x * a.x + a.y * a.y + b2.x * b2.x + b2.y * b2.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+      }
     }
   }
   __shared__ float sm[8];
@@ -249,13 +257,15 @@ dp_sum_norm_kernel(PeerTable stage, PeerTable norm, __nv_bfloat16* __restrict__ 
 
 // Phase 2: wait for every rank's squared-norm, clip, AdamW on the fp32 master shard, and
 // write the bf16 parameters into every rank's parameter buffer (all-gather by 16-byte peer
-// stores; the bucket table maps a shard position to its place in the flat buffer). Ends with a
+// stores, or one multicast store per vector when the buffers have a multicast address; the
+// bucket table maps a shard position to its place in the flat buffer). Ends with a
 // signal/wait so that when the kernel completes, this rank's own parameter buffer has
 // received all shards.
 __global__ void __launch_bounds__(256)
 dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __restrict__ reduced,
                       float* __restrict__ master, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
-                      BucketTable bt, int world, int rank, int slot_norm, uint32_t target_norm,
+                      BucketTable bt, __nv_bfloat16* __restrict__ mc_params, int world, int rank, int slot_norm,
+                      uint32_t target_norm,
                       int slot_param, uint32_t target_param, const float* __restrict__ extern_sumsq,
                       float* __restrict__ norm_out, AdamArgs a, unsigned long long wait_ns, uint32_t* status) {
   __shared__ float s_coef;
@@ -324,9 +334,13 @@ dp_adam_gather_kernel(PeerTable params, PeerTable norm, const __nv_bfloat16* __r
     int b = 0;
     while (b + 1 < bt.nb && e0 >= bt.off[b + 1]) ++b;
     const long long flat = bt.flat0[b] + rank * bt.slice[b] + (e0 - bt.off[b]);
-    for (int q = 0; q < world; ++q) {
-      const int r = (rank + 1 + q) % world;         // peers first: the remote stores leave early
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.buf[r]) + flat) = o;
+    if (mc_params != nullptr) {
+      multimem_st_v4(mc_params + flat, o);          // NVSwitch delivers it to every rank's buffer
+    } else {
+      for (int q = 0; q < world; ++q) {
+        const int r = (rank + 1 + q) % world;       // peers first: the remote stores leave early
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.buf[r]) + flat) = o;
+      }
     }
   }
   cta_signal_all_and_wait(params, world, rank, slot_param, target_param, wait_ns, status);
@@ -352,7 +366,8 @@ int resident_grid(int want) { return std::max(1, std::min(want, gfs_host::sm_cou
 extern "C" {
 
 // In every function: peer_bufs / peer_flags are host arrays of `world` device pointers (this
-// rank's entry included); slot0 is the first of `world` consecutive uint32 counters reserved
+// rank's entry included); buffer tables carry one more entry, [world]: the multicast address of
+// the same symmetric buffers (0 when there is none), used where a kernel says so; slot0 is the first of `world` consecutive uint32 counters reserved
 // for the call site inside each rank's flag array; *target_inout is the cumulative count and
 // is advanced by the call (identically on all ranks). Grids are sized so that all CTAs are
 // co-resident, because CTAs wait for signals produced by other GPUs' CTAs.
@@ -439,7 +454,7 @@ int gfs_dp_push_grads(const void* grads, const unsigned long long* peer_stage, c
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(grads);
   const size_t bytes = static_cast<size_t>(bt.slice[b]) * sizeof(__nv_bfloat16);
-  for (int q = 0; q < world; ++q) {
+  for (int q = 0; q + 1 < world; ++q) {          // peers only: the owner reads its own slice in place
     const int dst = (rank + 1 + q) % world;
     __nv_bfloat16* to = static_cast<__nv_bfloat16*>(st.buf[dst]) + rank * bt.off[nb] + bt.off[b];
     if (cudaMemcpyAsync(to, g + bt.flat0[b] + dst * bt.slice[b], bytes, cudaMemcpyDeviceToDevice, stream) !=
@@ -455,16 +470,19 @@ int gfs_dp_push_grads(const void* grads, const unsigned long long* peer_stage, c
 // gfs_dp_reduce_norm_scratch_floats() gives its size.
 int gfs_dp_reduce_norm_scratch_floats() { return gfs_host::sm_count() * 2 + 8; }
 
-// Sums the staged gradient contributions of all ranks into `reduced` (this rank's shard) once
-// every push has arrived (target_push = the value gfs_dp_push_grads left in its counter), and
+// Sums the gradient contributions of all ranks (the peers' from the staging buffer, this rank's
+// own from `grads`) into `reduced` (this rank's shard) once every push has arrived (target_push = the value gfs_dp_push_grads left in its counter), and
 // publishes the shard's squared norm to every rank (peer_norm_slots[r][rank], flag slot_norm).
-int gfs_dp_sum_norm(const unsigned long long* peer_stage, const unsigned long long* peer_flags,
-                    const unsigned long long* peer_norm_slots, void* reduced, long long shard_numel, int world,
-                    int rank, int slot_push, unsigned int target_push, int slot_norm, unsigned int* target_norm_inout,
-                    void* scratch, long long wait_ns, void* stream) {
+int gfs_dp_sum_norm(const void* grads, const unsigned long long* peer_stage, const unsigned long long* peer_flags,
+                    const unsigned long long* peer_norm_slots, void* reduced, int nb, const long long* flat0,
+                    const long long* slice, const long long* off, int world, int rank, int slot_push,
+                    unsigned int target_push, int slot_norm, unsigned int* target_norm_inout, void* scratch,
+                    long long wait_ns, void* stream) {
   PeerTable st, nm;
+  BucketTable bt;
   if (fill_table(st, peer_stage, peer_flags, world) || fill_table(nm, peer_norm_slots, peer_flags, world)) return -1;
-  if (shard_numel & 7) return -1;
+  if (fill_buckets(bt, nb, flat0, slice, off)) return -1;
+  const long long shard_numel = bt.off[nb];
   const int grid = resident_grid(static_cast<int>(((shard_numel >> 3) + 2 * 256 - 1) / (2 * 256)));
   *target_norm_inout += 1;
   float* partials = static_cast<float*>(scratch);
@@ -472,9 +490,9 @@ int gfs_dp_sum_norm(const unsigned long long* peer_stage, const unsigned long lo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   __nv_bfloat16* red = static_cast<__nv_bfloat16*>(reduced);
 #define GFS_SUM_NORM(W)                                                                                          \
-  dp_sum_norm_kernel<W><<<grid, 256, 0, s>>>(st, nm, red, shard_numel, world, rank, slot_push, target_push,      \
-                                             slot_norm, partials, ticket, limit_of(wait_ns),                     \
-                                             gfs_host::status_words())
+  dp_sum_norm_kernel<W><<<grid, 256, 0, s>>>(st, nm, static_cast<const __nv_bfloat16*>(grads), bt, red, world,   \
+                                             rank, slot_push, target_push, slot_norm, partials, ticket,          \
+                                             limit_of(wait_ns), gfs_host::status_words())
   if (world == 2) GFS_SUM_NORM(2);
   else if (world == 4) GFS_SUM_NORM(4);
   else if (world == 8) GFS_SUM_NORM(8);
@@ -506,7 +524,8 @@ int gfs_dp_adam_gather(const unsigned long long* peer_params, const unsigned lon
              bias_corr2_sqrt, clip, grad_scale, static_cast<const float*>(step_dev), beta1, beta2};
   dp_adam_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pr, nm, static_cast<const __nv_bfloat16*>(reduced), static_cast<float*>(master), static_cast<float*>(exp_avg),
-      static_cast<float*>(exp_avg_sq), bt, world, rank, slot_norm, target_norm, slot_param, *target_param_inout,
+      static_cast<float*>(exp_avg_sq), bt, reinterpret_cast<__nv_bfloat16*>(peer_params[world]), world, rank,
+      slot_norm, target_norm, slot_param, *target_param_inout,
       static_cast<const float*>(extern_sumsq), static_cast<float*>(norm_out), a, limit_of(wait_ns),
       gfs_host::status_words());
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

@@ -388,6 +388,18 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// One 16-byte store to a multicast address: NVSwitch writes it to the same offset of every rank's
+// copy of the symmetric buffer (this rank's own included), so an all-gather leaves the GPU once
+// instead of once per peer. Ordered like any other store by the fences / release that follow it.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -454,7 +466,39 @@ __device__ __forceinline__ void ag_push_rows(const Comm& c, int tid, int nthread
   const int r1 = min(c.rows_per_rank, r0 + rpc);
   const int vpr = c.ag_cols >> 3;
   const int nvec = (r1 - r0) * vpr;
-  for (int i = 0; i < c.world; ++i) {
+  if (c.mc_buf != nullptr) {
+    // multicast: one store per vector reaches every rank's gathered buffer through the switch
+    __nv_bfloat16* dst = c.mc_buf + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
+    for (int v = tid; v < nvec; v += nthreads * 4) {
+      uint4 tmp[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vv = v + u * nthreads;
+        if (vv < nvec) {
+          const int row = r0 + vv / vpr;
+          tmp[u] = *reinterpret_cast<const uint4*>(c.ag_src + static_cast<size_t>(row) * c.ag_ld + (vv % vpr) * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vv = v + u * nthreads;
+        if (vv < nvec) {
+          const int row = r0 + vv / vpr;
+          multimem_st_v4(dst + static_cast<size_t>(row) * c.ag_cols + (vv % vpr) * 8, tmp[u]);
+        }
+      }
+    }
+    // (no fence per thread: the barrier orders every thread's stores before the signalling threads'
+    // release, which is cumulative; a system-scope fence costs microseconds)
+    named_barrier_sync(bar_id, nthreads);
+    if (tid < c.world) red_release_sys_add_u32(c.peer_flags[tid] + c.rank, 1u);
+    return;
+  }
+  // The system-scope release that publishes the rows costs microseconds, so there is one for all
+  // destinations, not one per destination: store to every rank (peers first, the rows are re-read
+  // from cache), CTA barrier, then one thread per destination bumps its counter with release
+  // semantics (cumulative over the stores the barrier ordered before it).
+  for (int i = 1; i <= c.world; ++i) {
     const int peer = (c.rank + i) % c.world;
     __nv_bfloat16* dst = c.peer_buf[peer] + static_cast<size_t>(c.rank) * c.rows_per_rank * c.ag_cols;
     for (int v = tid; v < nvec; v += nthreads * 4) {
@@ -476,68 +520,89 @@ __device__ __forceinline__ void ag_push_rows(const Comm& c, int tid, int nthread
         }
       }
     }
-    __threadfence_system();
-    named_barrier_sync(bar_id, nthreads);
-    if (tid == 0) red_release_sys_add_u32(c.peer_flags[peer] + c.rank, 1u);
   }
+  named_barrier_sync(bar_id, nthreads);
+  if (tid < c.world) red_release_sys_add_u32(c.peer_flags[tid] + c.rank, 1u);
 }
 
 // Final step of a fused GEMM -> reduce-scatter: out[row, :] = sum over source ranks of the staged
 // bf16 partial rows (in rank order: deterministic) + optional residual, rounded once. `stage` is
 // this rank's staging area [world][rows][N]. The vectors (8 columns each) are dealt to
-// `nthreads_total` threads of the whole grid, of which the caller is number `tid_global`; four
-// independent vectors are in flight per thread so the pass runs at memory speed, not latency.
+// `nthreads_total` threads of the whole grid, of which the caller is number `tid_global`. All of a
+// step's loads (U vectors x WORLD sources + U residual vectors) are issued before the first sum, so
+// a thread has U * (WORLD + 1) independent 16-byte loads in flight and the pass runs at memory
+// speed; with the source loop left to run time the loads of one vector serialise (one memory
+// latency per source), which made this pass the longest part of the small reduce-scatter GEMMs.
+template <int WORLD, int U>
+__device__ __forceinline__ void rs_reduce_rows_t(const __nv_bfloat16* __restrict__ stage, int rows, int N,
+                                                 const __nv_bfloat16* __restrict__ res, int ld_res,
+                                                 __nv_bfloat16* __restrict__ out, int ld_out, uint32_t tid_global,
+                                                 uint32_t nthreads_total) {
+  const uint32_t vpr = static_cast<uint32_t>(N) >> 3;
+  const uint32_t total = static_cast<uint32_t>(rows) * vpr;       // < 2^32: rows * N / 8 of one row chunk
+  const size_t chunk_elems = static_cast<size_t>(rows) * N;
+  for (uint32_t v0 = tid_global; v0 < total; v0 += nthreads_total * U) {
+    uint4 in[U][WORLD];
+    uint4 rr[U];
+    uint32_t row[U], col[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t v = v0 + static_cast<uint32_t>(u) * nthreads_total;
+      const bool live = v < total;
+      row[u] = live ? v / vpr : 0u;
+      col[u] = live ? (v - row[u] * vpr) << 3 : 0u;
+      const __nv_bfloat16* src0 = stage + static_cast<size_t>(row[u]) * N + col[u];
+#pragma unroll
+      for (int s = 0; s < WORLD; ++s) in[u][s] = *reinterpret_cast<const uint4*>(src0 + s * chunk_elems);
+      rr[u] = (res != nullptr) ? *reinterpret_cast<const uint4*>(res + static_cast<size_t>(row[u]) * ld_res + col[u])
+                               : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v0 + static_cast<uint32_t>(u) * nthreads_total >= total) continue;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int s = 0; s < WORLD; ++s) {
+        const float2 a = unpack_bf16x2(in[u][s].x), b = unpack_bf16x2(in[u][s].y), c = unpack_bf16x2(in[u][s].z),
+                     d = unpack_bf16x2(in[u][s].w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+      const float2 a = unpack_bf16x2(rr[u].x), b = unpack_bf16x2(rr[u].y), c = unpack_bf16x2(rr[u].z),
+                   d = unpack_bf16x2(rr[u].w);
+      uint4 o;
+      o.x = pack_bf16x2(acc[0] + a.x, acc[1] + a.y);
+      o.y = pack_bf16x2(acc[2] + b.x, acc[3] + b.y);
+      o.z = pack_bf16x2(acc[4] + c.x, acc[5] + c.y);
+      o.w = pack_bf16x2(acc[6] + d.x, acc[7] + d.y);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row[u]) * ld_out + col[u]) = o;
+    }
+  }
+}
+
 __device__ __forceinline__ void rs_reduce_rows(const __nv_bfloat16* __restrict__ stage, int world, int rows, int N,
                                                const __nv_bfloat16* __restrict__ res, int ld_res,
                                                __nv_bfloat16* __restrict__ out, int ld_out, size_t tid_global,
                                                size_t nthreads_total) {
-  const int vpr = N >> 3;
-  const size_t total = static_cast<size_t>(rows) * vpr;
-  const size_t chunk_elems = static_cast<size_t>(rows) * N;
-  constexpr int U = 4;
-  for (size_t v0 = tid_global; v0 < total; v0 += nthreads_total * U) {
-    float acc[U][8];
-    uint4 rr[U];
-    size_t off_out[U];
-    bool live[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const size_t v = v0 + static_cast<size_t>(u) * nthreads_total;
-      live[u] = v < total;
-      const int row = live[u] ? static_cast<int>(v / vpr) : 0;
-      const int col = live[u] ? static_cast<int>(v % vpr) << 3 : 0;
-      off_out[u] = static_cast<size_t>(row) * ld_out + col;
-      rr[u] = make_uint4(0, 0, 0, 0);
-      if (live[u] && res != nullptr) rr[u] = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * ld_res + col);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
-      if (live[u]) {
-        const __nv_bfloat16* src0 = stage + static_cast<size_t>(row) * N + col;
-        for (int src = 0; src < world; ++src) {
-          const uint4 w = *reinterpret_cast<const uint4*>(src0 + src * chunk_elems);
-          const float2 a = unpack_bf16x2(w.x), b = unpack_bf16x2(w.y), c = unpack_bf16x2(w.z), d = unpack_bf16x2(w.w);
-          acc[u][0] += a.x; acc[u][1] += a.y; acc[u][2] += b.x; acc[u][3] += b.y;
-          acc[u][4] += c.x; acc[u][5] += c.y; acc[u][6] += d.x; acc[u][7] += d.y;
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!live[u]) continue;
-      const float2 a = unpack_bf16x2(rr[u].x), b = unpack_bf16x2(rr[u].y), c = unpack_bf16x2(rr[u].z),
-                   d = unpack_bf16x2(rr[u].w);
-      uint4 o;
-      o.x = pack_bf16x2(acc[u][0] + a.x, acc[u][1] + a.y);
-      o.y = pack_bf16x2(acc[u][2] + b.x, acc[u][3] + b.y);
-      o.z = pack_bf16x2(acc[u][4] + c.x, acc[u][5] + c.y);
-      o.w = pack_bf16x2(acc[u][6] + d.x, acc[u][7] + d.y);
-      *reinterpret_cast<uint4*>(out + off_out[u]) = o;
-    }
+  const uint32_t t = static_cast<uint32_t>(tid_global), n = static_cast<uint32_t>(nthreads_total);
+  switch (world) {
+    case 2: rs_reduce_rows_t<2, 4>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    case 3: rs_reduce_rows_t<3, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    case 4: rs_reduce_rows_t<4, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    case 5: rs_reduce_rows_t<5, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    case 6: rs_reduce_rows_t<6, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    case 7: rs_reduce_rows_t<7, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
+    default: rs_reduce_rows_t<8, 2>(stage, rows, N, res, ld_res, out, ld_out, t, n); break;
   }
 }
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Counted arrival without waiting: the warps that call bar.sync on the same barrier are released
+// once `nthreads` threads (arrivals + waiters) have reached it.
+__device__ __forceinline__ void named_barrier_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 }  // namespace gfs

@@ -478,6 +478,72 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, c
   }
 }
 
+// Embedding backward without a library sort: the token ids of one micro-batch (n <= 32768) are
+// sorted by ONE CTA in shared memory. Key = (local vocabulary row << shift) | dout row index, so
+// keys are unique and ascending order is "by row, then by position" - the order a stable sort
+// gives, hence the same bitwise result as summing in sorted order. Ids owned by other ranks get
+// the all-ones key and end up behind the valid ones. Bitonic network on npow2 keys.
+constexpr int SORT_THREADS = 1024;
+__global__ void __launch_bounds__(SORT_THREADS)
+embedding_sort_kernel(const long long* __restrict__ ids_bs, uint32_t* __restrict__ keys_out, int n, int npow2,
+                      int shift, int B, int S, int v0, int v1) {
+  extern __shared__ uint32_t sk[];
+  for (int i = threadIdx.x; i < npow2; i += SORT_THREADS) {
+    uint32_t key = 0xFFFFFFFFu;
+    if (i < n) {
+      const long long id = ids_bs[static_cast<size_t>(i % B) * S + i / B];   // dout row i = (s, b) = (i / B, i % B)
+      if (id >= v0 && id < v1) key = (static_cast<uint32_t>(id - v0) << shift) | static_cast<uint32_t>(i);
+    }
+    sk[i] = key;
+  }
+  __syncthreads();
+  for (int k = 2; k <= npow2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int c = threadIdx.x; c < (npow2 >> 1); c += SORT_THREADS) {
+        const int a = ((c & ~(j - 1)) << 1) | (c & (j - 1));
+        const int b = a | j;
+        const uint32_t x = sk[a], y = sk[b];
+        const bool ascending = (a & k) == 0;
+        if ((x > y) == ascending) {
+          sk[a] = y;
+          sk[b] = x;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < n; i += SORT_THREADS) keys_out[i] = sk[i];
+}
+
+// Segmented sum over the sorted keys: a warp owns one run of equal vocabulary rows and adds its
+// dout rows in key order (deterministic); dW rows are accumulated (bf16, fp32 sum).
+__global__ void embedding_bwd_keys_kernel(const uint32_t* __restrict__ keys, const __nv_bfloat16* __restrict__ dout,
+                                          __nv_bfloat16* __restrict__ dW, int n, int H, int shift) {
+  const int lane = threadIdx.x & 31;
+  const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= n) return;
+  const uint32_t key = keys[p];
+  if (key == 0xFFFFFFFFu) return;
+  const uint32_t row = key >> shift;
+  if (p > 0 && (keys[p - 1] >> shift) == row) return;  // not the start of a run
+  const uint32_t mask = (1u << shift) - 1u;
+  int q_end = p + 1;
+  while (q_end < n && keys[q_end] != 0xFFFFFFFFu && (keys[q_end] >> shift) == row) ++q_end;
+  __nv_bfloat16* dst = dW + static_cast<size_t>(row) * H;
+  const int nvec = H >> 3;
+  for (int v = lane; v < nvec; v += 32) {
+    float acc[8];
+    load8(dst + 8 * v, acc);
+    for (int q = p; q < q_end; ++q) {
+      float f[8];
+      load8(dout + static_cast<size_t>(keys[q] & mask) * H + 8 * v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    store8(dst + 8 * v, acc);
+  }
+}
+
 inline int grid_for(size_t work_items, int threads, int max_blocks_per_sm = 16) {
   const size_t blocks = (work_items + threads - 1) / threads;
   const size_t cap = static_cast<size_t>(gfs_host::sm_count()) * max_blocks_per_sm;
@@ -643,6 +709,37 @@ int gfs_embedding_bwd(const void* sorted_ids, const void* perm, const void* dout
   embedding_bwd_kernel<<<(n + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const long long*>(sorted_ids), static_cast<const long long*>(perm),
       static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dW), n, H, v0, v1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Embedding backward with the in-library sort: ids [B, S] (int64), dout [S, B, H], dW [v1 - v0, H]
+// accumulated. `keys` is scratch for n = S * B uint32. Returns -20 when the problem does not fit
+// the single-CTA sort (n > 32768 or the key does not fit 32 bits): the caller then sorts elsewhere
+// and uses gfs_embedding_bwd.
+int gfs_embedding_bwd_sorted(const void* ids_bs, const void* dout, void* dW, void* keys, int B, int S, int H, int v0,
+                             int v1, void* stream_) {
+  if (H & 7) return -1;
+  const long long n64 = static_cast<long long>(B) * S;
+  if (n64 == 0) return 0;
+  if (n64 > 32768) return -20;
+  const int n = static_cast<int>(n64);
+  int npow2 = 2, shift = 1;
+  while (npow2 < n) { npow2 <<= 1; ++shift; }
+  if ((static_cast<unsigned long long>(v1 - v0) << shift) >= 0xFFFFFFFFull) return -20;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(embedding_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4) !=
+        cudaSuccess)
+      return -10;
+    attr_set = true;
+  }
+  embedding_sort_kernel<<<1, SORT_THREADS, npow2 * sizeof(uint32_t), stream>>>(
+      static_cast<const long long*>(ids_bs), static_cast<uint32_t*>(keys), n, npow2, shift, B, S, v0, v1);
+  const int warps = 8;
+  embedding_bwd_keys_kernel<<<(n + warps - 1) / warps, warps * 32, 0, stream>>>(
+      static_cast<const uint32_t*>(keys), static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dW), n, H,
+      shift);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -71,6 +71,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_swiglu_bwd": ([vp, vp, vp, i, i, vp], i),
         "gfs_embedding_fwd": ([vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_embedding_bwd": ([vp, vp, vp, vp, i, i, i, i, vp], i),
+        "gfs_embedding_bwd_sorted": ([vp, vp, vp, vp, i, i, i, i, i, vp], i),
         "gfs_ce_fwd": ([vp, vp, vp, vp, vp, i, i, cl, i, i, vp], i),
         "gfs_ce_combine": ([vp, vp, vp, i, i, vp], i),
         "gfs_ce_bwd": ([vp, vp, vp, vp, i, i, cl, i, vp], i),
@@ -101,7 +102,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_ce_exchange": ([vp, vp, vp, i, ulp, ulp, i, i, i, uip, ctypes.c_longlong, vp], i),
         "gfs_dp_reduce_norm_scratch_floats": ([], i),
         "gfs_dp_push_grads": ([vp, ulp, ulp, i, lp, lp, lp, i, i, i, i, uip, vp], i),
-        "gfs_dp_sum_norm": ([ulp, ulp, ulp, vp, ctypes.c_longlong, i, i, i, ctypes.c_uint, i, uip, vp,
+        "gfs_dp_sum_norm": ([vp, ulp, ulp, ulp, vp, i, lp, lp, lp, i, i, i, ctypes.c_uint, i, uip, vp,
                              ctypes.c_longlong, vp], i),
         "gfs_dp_adam_gather": ([ulp, ulp, ulp, vp, vp, vp, vp, i, lp, lp, lp, i, i, i, ctypes.c_uint, i, uip, vp, vp,
                                 f, d, d, f, f, f, f, f, f, vp, ctypes.c_longlong, vp], i),

@@ -3,7 +3,8 @@
 Forward writes ``out[s, b, :] = W[id - v0]`` (zero when the id belongs to another rank)
 directly in sequence-first layout, replacing the reference's mask / clamp / F.embedding /
 masked_fill / transpose-copy chain (core/tensor_parallel/layers.py:120-133). Backward is a
-deterministic segmented sum over token ids sorted on the device.
+deterministic segmented sum over token ids sorted on the device (by a single-CTA bitonic sort of
+this library for up to 32768 tokens per micro-batch).
 """
 from __future__ import annotations
 
@@ -31,6 +32,15 @@ def embedding_bwd_native(ids_bs: torch.Tensor, dout_sbh: torch.Tensor, dweight: 
     H = dweight.shape[1]
     if not accumulate:
         dweight.zero_()
+    # up to 32768 tokens: sorted by one CTA of the library (no library sort, nothing allocated but a
+    # key buffer); larger batches fall back to torch.sort
+    keys = torch.empty(S * B, dtype=torch.int32, device=dweight.device)
+    rc = _lib.lib().gfs_embedding_bwd_sorted(ids_bs.data_ptr(), dout_sbh.data_ptr(), dweight.data_ptr(),
+                                             keys.data_ptr(), B, S, H, v0, v1, _lib.stream_ptr())
+    if rc != -20:
+        _lib.check(rc, "gfs_embedding_bwd_sorted")
+        _lib.add_launches(1)
+        return
     flat = ids_bs.t().reshape(-1)  # [S*B] in dout row order
     sorted_ids, perm = torch.sort(flat, stable=True)
     rc = _lib.lib().gfs_embedding_bwd(sorted_ids.data_ptr(), perm.data_ptr(), dout_sbh.data_ptr(),

@@ -38,6 +38,7 @@ Differences that are deliberate:
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -183,6 +184,7 @@ class DistributedOptimizer:
         has reported its gradient final through its gradient sink; a parameter whose gradient
         arrives through plain autograd (a bias) never reports, so its bucket waits for ``step()``."""
         self.overlap_grad_reduce = False
+        self._overlap_allowed = os.environ.get("GFS_DP_OVERLAP", "1") != "0"   # A/B switch
         self._overlap_armed = False
         self._push_stream = None
         if not self.use_fused_comm:
@@ -208,7 +210,7 @@ class DistributedOptimizer:
         self._pending = list(self._bucket_size)
         self._parked = [0] * len(self._bucket_size)
         self._pushed = [False] * len(self._bucket_size)
-        self._overlap_armed = bool(self.overlap_grad_reduce)
+        self._overlap_armed = bool(self.overlap_grad_reduce and self._overlap_allowed)
         for p in self.params:
             p._gfs_parked = False
             p._gfs_ready = False

@@ -45,6 +45,7 @@ class FakePeerGroup(symm.SymmGroup):
         self._sites = {}
         self._pools = {}
         self._next_slot = 0
+        self.has_multicast = False
         flags = self.alloc("__flags__", 2 * symm.NUM_FLAG_SLOTS, torch.int32, zero=True)
         self.flags = flags
         self.flag_ptrs = flags.ptrs
@@ -59,7 +60,7 @@ class FakePeerGroup(symm.SymmGroup):
         # one allocation per (fake) rank; all zero-filled so that what an absent rank "sent" is
         # well defined until a test writes something else
         per_rank = [torch.zeros(numel, dtype=dtype, device=self.device) for _ in range(self.world)]
-        ptrs = (ctypes.c_ulonglong * self.world)(*[t.data_ptr() for t in per_rank])
+        ptrs = (ctypes.c_ulonglong * (self.world + 1))(*[t.data_ptr() for t in per_rank], 0)   # no multicast
         buf = symm.SymmBuffer(per_rank[self.rank], ptrs, per_rank)     # handle = every rank's tensor
         self._buffers[key] = buf
         return buf

@@ -41,7 +41,7 @@ def _site_flag_ptrs(grp: symm.SymmGroup, site: symm.Site):
     cache = grp.__dict__.setdefault("_site_flag_ptrs", {})
     ptrs = cache.get(site.slot0)
     if ptrs is None:
-        ptrs = (ctypes.c_ulonglong * grp.world)(*[int(p) + 4 * site.slot0 for p in grp.flag_ptrs])
+        ptrs = (ctypes.c_ulonglong * grp.world)(*[int(grp.flag_ptrs[r]) + 4 * site.slot0 for r in range(grp.world)])
         cache[site.slot0] = ptrs
     return ptrs
 
@@ -91,6 +91,16 @@ def _weight_site_key(weight: torch.Tensor) -> int:
         _next_weight_key += 1
         weight._gfs_site_key = key
     return key
+
+
+def _check_generation(buf: symm.SymmBuffer, expected: int) -> None:
+    """The gathered input of a call site lives in ONE symmetric buffer per site, kept from the
+    forward to the backward for the weight gradient. A second forward through the same layer before
+    the first one's backward (e.g. two micro-batches forwarded, then both backwarded) overwrites it:
+    raise instead of computing a wrong gradient."""
+    if buf.generation != expected:
+        raise RuntimeError("fused tensor-parallel layers keep one gathered input per layer: run each forward's "
+                           "backward before the next forward through the same layer (or use --comm-impl nccl)")
 
 
 def _as2d(t: torch.Tensor, cols: int) -> torch.Tensor:
@@ -144,6 +154,8 @@ class _AllGatherLinear(torch.autograd.Function):
             _gemm_comm(MODE_AG, x2, weight, out, None, M, N, K, False, grp, gathered, site, rope)
         ctx.save_for_backward(weight)
         ctx.gathered = gathered
+        gathered.generation += 1
+        ctx.generation = gathered.generation
         ctx.sink = sink
         ctx.dims = (M, N, K, Ms, x_shard.shape)
         y = out.view(x_shard.shape[0] * grp.world, *x_shard.shape[1:-1], N)
@@ -159,6 +171,7 @@ class _AllGatherLinear(torch.autograd.Function):
         (weight,) = ctx.saved_tensors
         grp = symm.get_group("tp")
         M, N, K, Ms, in_shape = ctx.dims
+        _check_generation(ctx.gathered, ctx.generation)
         dy2 = _as2d(dy, N)
         # dX = reduce_scatter(dY @ W): GEMM with the reduce-scatter in its epilogue
         stage, site = grp.pooled("rs", M * K, torch.bfloat16)
@@ -286,6 +299,8 @@ class _FusedCommMLP(torch.autograd.Function):
         _gemm_comm(MODE_RS, act, w_down, out, res2, M, H, I, False, grp, stage, site_rs)
         ctx.save_for_backward(gu, act, w_gu, w_down)
         ctx.gathered = gathered
+        gathered.generation += 1
+        ctx.generation = gathered.generation
         ctx.sinks = (sink_gu, sink_down)
         ctx.has_res = residual is not None
         ctx.dims = (M, Ms, H, I, x_shard.shape)
@@ -297,6 +312,7 @@ class _FusedCommMLP(torch.autograd.Function):
         sink_gu, sink_down = ctx.sinks
         grp = symm.get_group("tp")
         M, Ms, H, I, in_shape = ctx.dims
+        _check_generation(ctx.gathered, ctx.generation)
         d2 = _as2d(dout, H)
         # d_gu = swiglu'(gather_S(dOut) @ W_down, gu): all-gather fused into the dgrad GEMM, SwiGLU
         # backward in its epilogue; the gathered dOut then feeds the down projection's wgrad
@@ -397,7 +413,9 @@ class _EmbeddingReduceScatter(torch.autograd.Function):
         _lib.check(rc, "gfs_embedding_scatter")
         ctx.save_for_backward(ids)
         ctx.meta = (v0, v1, sink, weight.shape, S, B, H)
-        return out.tensor.view(Ss, B, H)
+        # the result is layer 0's input and is saved for its backward, while the pooled symmetric
+        # buffer is written again by the next forward: hand out a private copy (a few MB per step)
+        return out.tensor.view(Ss, B, H).clone()
 
     @staticmethod
     def backward(ctx, dout):
@@ -520,8 +538,8 @@ class DataParallelComm:
     def sum_and_norm(self) -> None:
         g = self.grp
         rc = _lib.lib().gfs_dp_sum_norm(
-            self._stage.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(), self.shard_size, g.world, g.rank,
-            self.site_push.slot0, self.site_push.target.value, self.site_norm.slot0,
+            self.grad_buffer.data_ptr(), self._stage.ptrs, g.flag_ptrs, self._norm.ptrs, self.reduced.data_ptr(),
+            self.nb, self._c_flat0, self._c_slice, self._c_off, g.world, g.rank, self.site_push.slot0, self.site_push.target.value, self.site_norm.slot0,
             ctypes.byref(self.site_norm.target), self.scratch.data_ptr(), WAIT_NS, _lib.stream_ptr())
         _lib.check(rc, "gfs_dp_sum_norm")
 

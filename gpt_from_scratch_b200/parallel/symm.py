@@ -32,18 +32,21 @@ NUM_FLAG_SLOTS = 8192      # must equal gfs_flag_slots() of the native library (
 # sides, filled with a pattern; check_canaries() verifies them (the multi-GPU tests do so after
 # exercising every fused kernel). Stands in for a memory checker on peer stores.
 CANARIES = os.environ.get("GFS_SYMM_CANARIES", "0") == "1"
+# GFS_MULTIMEM=0: never hand kernels a multicast address (they then use per-peer stores)
+MULTIMEM = os.environ.get("GFS_MULTIMEM", "1") != "0"
 GUARD_BYTES = 256
 CANARY_BYTE = 0xA5
 _groups: dict = {}
 
 
 class SymmBuffer:
-    __slots__ = ("tensor", "ptrs", "handle")
+    __slots__ = ("tensor", "ptrs", "handle", "generation")
 
     def __init__(self, tensor, ptrs, handle):
         self.tensor = tensor
-        self.ptrs = ptrs          # ctypes array of `world` device pointers (this rank included)
+        self.ptrs = ptrs          # ctypes array: `world` device pointers (this rank included) + multicast address
         self.handle = handle
+        self.generation = 0       # bumped by every operator that overwrites the buffer (reuse check)
 
 
 class Site:
@@ -66,6 +69,7 @@ class SymmGroup:
         self._sites: dict = {}
         self._pools: dict = {}
         self._next_slot = 0
+        self.has_multicast = False
         # counters [0, NUM_FLAG_SLOTS) + their base words [NUM_FLAG_SLOTS, 2*NUM_FLAG_SLOTS)
         flags = self.alloc("__flags__", 2 * NUM_FLAG_SLOTS, torch.int32, zero=True)
         self.flags = flags
@@ -93,8 +97,13 @@ class SymmGroup:
             t.zero_()
         handle = symm_mem.rendezvous(raw, self.group)
         off = guard * dtype.itemsize
-        ptrs = (ctypes.c_ulonglong * self.world)(*[int(p) + off for p in handle.buffer_ptrs])
+        # entries [0, world): every rank's copy; entry [world]: the NVSwitch multicast address of the
+        # same allocation (a store to it lands in every copy), 0 when the fabric offers none
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0) if MULTIMEM else 0
+        ptrs = (ctypes.c_ulonglong * (self.world + 1))(*[int(p) + off for p in handle.buffer_ptrs],
+                                                       (mc + off) if mc else 0)
         assert int(ptrs[self.rank]) == t.data_ptr()
+        self.has_multicast = bool(mc)
         buf = SymmBuffer(t, ptrs, handle)
         self._buffers[key] = buf
         if guard:

@@ -245,6 +245,8 @@ def main():
         symm.check_all_canaries()
         log("canaries intact")
     dist.barrier()
+    from gpt_from_scratch_b200.parallel import symm as _symm
+    log("multicast (NVLS) stores in use:", {k: g.has_multicast for k, g in _symm._groups.items()})
     log("WORKER OK")
     dist.destroy_process_group()
 

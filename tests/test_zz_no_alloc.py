@@ -56,6 +56,41 @@ def test_static_scratch_gemm_matches_regular_entry_point(cuda_device):
         assert torch.equal(out_static, out_regular), f"call {call}: results differ from the regular entry point"
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,splits", [
+    (256, 96, 1024, True, True, 4),      # N <= 128: the 128-column tile variants
+    (200, 312, 1000, False, False, 2),   # K-major operands, K tail (1000 = 15 * 64 + 40), ragged M and N
+    (384, 256, 520, False, True, 3),     # mixed layouts, K tail
+    (136, 72, 2048, True, False, 8),     # small ragged output, deep contraction
+])
+def test_static_scratch_gemm_other_kernel_variants(cuda_device, M, N, K, a_mn, b_mn, splits):
+    """Layouts, tile widths and ragged sizes beyond the weight-gradient case above, each against the
+    regular entry point with the same split count; and the calls leave the amount of free device
+    memory exactly as they found it (nothing is allocated or freed behind the caller's back)."""
+    fn = _lib_handle()
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device=cuda_device, generator=g).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=cuda_device, generator=g).bfloat16()
+    out_regular = torch.empty(M, N, device=cuda_device, dtype=torch.bfloat16)
+    _reference_entry(a, b, out_regular, None, M, N, K, a_mn, b_mn, splits)
+    out_static = torch.empty(M, N, device=cuda_device, dtype=torch.bfloat16)
+    fn(a.data_ptr(), b.data_ptr(), out_static.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
+       out_static.stride(0), 0, int(a_mn), int(b_mn), 0, splits, stream)        # first call on the device: set-up
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        rc = fn(a.data_ptr(), b.data_ptr(), out_static.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
+                out_static.stride(0), 0, int(a_mn), int(b_mn), 0, splits, stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed free device memory"
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    ref = af @ bf
+    assert (out_static.float() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item() + 1e-3
+    assert torch.equal(out_static, out_regular)
+
+
 def test_static_scratch_gemm_rejects_oversized_problems(cuda_device):
     fn = _lib_handle()
     stream = torch.cuda.current_stream().cuda_stream
