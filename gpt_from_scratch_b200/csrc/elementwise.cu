@@ -712,15 +712,16 @@ int gfs_embedding_bwd(const void* sorted_ids, const void* perm, const void* dout
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// Embedding backward with the in-library sort: ids [B, S] (int64), dout [S, B, H], dW [v1 - v0, H]
-// accumulated. `keys` is scratch for n = S * B uint32. Returns -20 when the problem does not fit
-// the single-CTA sort (n > 32768 or the key does not fit 32 bits): the caller then sorts elsewhere
-// and uses gfs_embedding_bwd.
-int gfs_embedding_bwd_sorted(const void* ids_bs, const void* dout, void* dW, void* keys, int B, int S, int H, int v0,
-                             int v1, void* stream_) {
-  if (H & 7) return -1;
+// Embedding backward with the in-library sort, in two calls so that the sort (one CTA, tens of
+// microseconds, needs only the token ids) can run on a side stream during the forward pass:
+//   gfs_embedding_sort_keys  ids [B, S] (int64) -> keys [S * B] uint32, sorted; returns the key
+//                            shift (> 0), or -20 when the problem does not fit the single-CTA sort
+//                            (n > 32768 or the key does not fit 32 bits: the caller then sorts
+//                            elsewhere and uses gfs_embedding_bwd)
+//   gfs_embedding_bwd_keys   dW [v1 - v0, H] += segmented sum of dout [S, B, H] in key order
+int gfs_embedding_sort_keys(const void* ids_bs, void* keys, int B, int S, int v0, int v1, void* stream_) {
   const long long n64 = static_cast<long long>(B) * S;
-  if (n64 == 0) return 0;
+  if (n64 <= 0) return -1;
   if (n64 > 32768) return -20;
   const int n = static_cast<int>(n64);
   int npow2 = 2, shift = 1;
@@ -736,8 +737,14 @@ int gfs_embedding_bwd_sorted(const void* ids_bs, const void* dout, void* dW, voi
   }
   embedding_sort_kernel<<<1, SORT_THREADS, npow2 * sizeof(uint32_t), stream>>>(
       static_cast<const long long*>(ids_bs), static_cast<uint32_t*>(keys), n, npow2, shift, B, S, v0, v1);
+  return cudaGetLastError() == cudaSuccess ? shift : -11;
+}
+
+int gfs_embedding_bwd_keys(const void* keys, const void* dout, void* dW, int n, int H, int shift, void* stream_) {
+  if ((H & 7) || shift <= 0 || shift > 31) return -1;
+  if (n == 0) return 0;
   const int warps = 8;
-  embedding_bwd_keys_kernel<<<(n + warps - 1) / warps, warps * 32, 0, stream>>>(
+  embedding_bwd_keys_kernel<<<(n + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const uint32_t*>(keys), static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dW), n, H,
       shift);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

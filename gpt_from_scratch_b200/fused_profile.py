@@ -15,7 +15,12 @@ Operators: ``ag_gemm`` (all-gather -> QKV GEMM), ``gemm_rs`` (out-projection GEM
 reduce-scatter + residual), ``mlp`` (the SwiGLU MLP: both of the above with the activation in the
 epilogues, forward and backward), ``lm_head`` (all-gather -> LM-head GEMM with cross-entropy
 statistics, fold, exchange), ``embedding`` (lookup -> reduce-scatter), ``dp`` (gradient push,
-sum + norm, clip + AdamW + parameter all-gather). Each prints its CUDA-event time per launch.
+sum + norm, clip + AdamW + parameter all-gather). Each prints its CUDA-event time per launch
+(host launch overhead included: these are eager calls).
+
+``--trace`` (GEMM operators): instead of timing, run the operator once with the CTA-pair kernel's
+phase stamps switched on (``gfs_gemm2_set_trace``) and print, per phase, the SM-clock cycles since
+kernel entry over all CTAs (min / median / max) - where inside the kernel the time goes.
 """
 from __future__ import annotations
 
@@ -43,8 +48,45 @@ def _time(fn, iters: int) -> float:
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+TRACE_SLOTS = ["global_ns", "entry", "setup_done", "first_tma", "first_mma", "epi_begin", "epi_first", "epi_last",
+               "red_begin", "red_end", "push_done", "exit", "tiles"]
+
+
+def trace_once(fn) -> None:
+    """Run ``fn`` (one fused GEMM call) with the phase stamps on and print the per-phase table."""
+    import ctypes
+    from .ops import _lib
+    lib = _lib.lib()
+    lib.gfs_gemm2_set_trace.argtypes = [ctypes.c_void_p]
+    lib.gfs_gemm2_set_trace.restype = None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    n_cta = lib.gfs_sm_count()
+    buf = torch.zeros(n_cta * 16, dtype=torch.int64, device="cuda")
+    lib.gfs_gemm2_set_trace(buf.data_ptr())
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        lib.gfs_gemm2_set_trace(None)
+    t = buf.view(n_cta, 16).cpu()
+    t = t[t[:, 1] != 0]
+    print(f"CTAs {t.shape[0]}, kernel entry spread {int(t[:, 0].max() - t[:, 0].min())} ns, "
+          f"tiles per CTA pair up to {int(t[:, 12].max())} (stamps of the LAST traced launch of the call)")
+    print(f"{'phase':12s} {'min':>8s} {'median':>8s} {'max':>8s}   cycles since kernel entry")
+    for slot in (2, 3, 4, 5, 6, 7, 10, 8, 9, 11):
+        col = t[:, slot]
+        ok = col != 0
+        if int(ok.sum()) == 0:
+            continue
+        rel = (col[ok] - t[ok, 1]).float()
+        print(f"{TRACE_SLOTS[slot]:12s} {int(rel.min()):8d} {int(rel.median()):8d} {int(rel.max()):8d}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--trace", action="store_true", help="print the CTA-pair GEMM kernel's phase stamps instead")
     ap.add_argument("--op", required=True, choices=["ag_gemm", "gemm_rs", "mlp", "lm_head", "embedding", "dp"])
     ap.add_argument("--shape", choices=sorted(SHAPES), default="124m")
     ap.add_argument("--world", type=int, default=2)
@@ -68,10 +110,14 @@ def main() -> None:
     with fake_peers(P, 0):
         if a.op == "ag_gemm":
             x, w = rnd(Ms, H), rnd(3 * H // P, H, scale=0.05)
+            if a.trace:
+                return trace_once(lambda: fused_comm.allgather_linear(x, w))
             us = _time(lambda: fused_comm.allgather_linear(x, w), a.iters)
             flops = 2.0 * M * (3 * H // P) * H
         elif a.op == "gemm_rs":
             x, w, r = rnd(M, H // P), rnd(H, H // P, scale=0.05), rnd(Ms, H)
+            if a.trace:
+                return trace_once(lambda: fused_comm.linear_reduce_scatter(x, w, r))
             us = _time(lambda: fused_comm.linear_reduce_scatter(x, w, r), a.iters)
             flops = 2.0 * M * H * (H // P)
         elif a.op == "mlp":

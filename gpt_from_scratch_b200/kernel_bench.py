@@ -162,6 +162,13 @@ def build_cases(dev, small: bool):
     cases.append(("ce_bwd_inplace", lambda: ce_ops.ce_backward_inplace(logits, lse_ce, tgt, grows, 0), 0, 4 * M * V))
     # parameter count of the benchmark model: 12 layers x (QKV + out + gate_up + down) + untied
     # embedding and LM head at vocab 50304 + norms
+    # head_dim 128 at the two larger model shapes (per tensor-parallel rank): GPT-1.3B TP8
+    # (B 4, 2 heads, S 2048) and GPT-7B TP4 (B 1, 8 heads, S 4096)
+    for tag, (S2, B2, nh2) in (("1p3b_tp8", (2048, 4, 2)), ("7b_tp4", (4096, 1, 8))):
+        if small:
+            break
+        cases.extend(attention_cases(dev, rnd, S2, B2, nh2, 128, f"_d128_{tag}"))
+
     n = 190_532_352 if not small else 8 * 1024 * 1024
     grad = rnd(n)
     master = torch.randn(n, device=dev)
@@ -182,8 +189,87 @@ def build_cases(dev, small: bool):
     return cases
 
 
+def attention_cases(dev, rnd, S, B, nh, D, suffix):
+    qkv = rnd(S, B, 3, nh, D)
+    out = torch.empty(S, B, nh, D, device=dev, dtype=torch.bfloat16)
+    dout = rnd(S, B, nh, D)
+    dqkv = torch.empty_like(qkv)
+    scale = 1.0 / math.sqrt(D)
+    lse = flash_fwd_native(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out, True, scale)
+    att_flops = 4.0 * S * S * D * B * nh / 2
+    return [("flash_fwd" + suffix,
+             lambda: flash_fwd_native(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out, True, scale),
+             att_flops, 2 * 4 * S * B * nh * D),
+            ("flash_bwd" + suffix,
+             lambda: flash_bwd_native(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out, dout, lse, dqkv[:, :, 0],
+                                      dqkv[:, :, 1], dqkv[:, :, 2], True, scale),
+             2.5 * att_flops, 2 * 8 * S * B * nh * D)]
+
+
+def vs_reference(dev, timer, iters):
+    """Head to head with the reference's own Triton kernels (its ``apply_flash_attn`` forward +
+    backward and ``apply_rope_qk``, imported unmodified from ``baseline/_ref``) at the same shapes
+    and with the same timing method. The reference's kernels autotune on first use: the warm-up
+    launches absorb that. Its attention takes ``[B, nh, S, D]`` tensors and makes them contiguous
+    (core/myFlashAttn.py:206-208); contiguous inputs are passed so no copy is timed."""
+    import sys
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "core")):
+        print("reference not installed under baseline/_ref: nothing to compare against")
+        return
+    sys.path[:] = [ref_root] + [q for q in sys.path if os.path.abspath(q or ".") != REPO]
+    for name in [m for m in sys.modules if m == "core" or m.startswith("core.")]:
+        del sys.modules[name]
+    from core.myFlashAttn import apply_flash_attn as ref_attn
+    from core.rope_triton import apply_rope_qk as ref_rope
+    from .ops.attention import apply_flash_attn as our_attn
+    g = torch.Generator(device="cuda").manual_seed(1)
+    print(f"{'operator':40s} {'reference us':>13s} {'ours us':>9s} {'ratio':>6s}")
+    for tag, (B, nh, S, D) in (("gpt124m  B16 nh12 S1024 D64", (16, 12, 1024, 64)),
+                                ("gpt1.3b/TP8 B4 nh2 S2048 D128", (4, 2, 2048, 128)),
+                                ("gpt7b/TP4 B1 nh8 S4096 D128", (1, 8, 4096, 128))):
+        q, k, v = (torch.randn(B, nh, S, D, device=dev, generator=g).bfloat16().requires_grad_() for _ in range(3))
+        do = torch.randn(B, nh, S, D, device=dev, generator=g).bfloat16()
+        res = {}
+        for who, fn in (("ref", ref_attn), ("ours", our_attn)):
+            def fwd():
+                return fn(q, k, v, True)
+
+            def fwd_bwd():
+                fn(q, k, v, True).backward(do)
+            try:
+                t_f = timer.time_us(fwd, iters=iters, warmup=4)
+                t_fb = timer.time_us(fwd_bwd, iters=iters, warmup=4)
+                res[who] = (t_f, t_fb - t_f)
+            except Exception as e:  # noqa: BLE001 - a reference failure is a result to report
+                res[who] = f"{type(e).__name__}: {str(e)[:120]}"
+        for idx, what in ((0, "flash attention fwd"), (1, "flash attention bwd (fwd+bwd minus fwd)")):
+            r, o = res["ref"], res["ours"]
+            if isinstance(r, str) or isinstance(o, str):
+                print(f"{what + ' ' + tag:40s} reference: {r if isinstance(r, str) else r[idx]}  ours: "
+                      f"{o if isinstance(o, str) else o[idx]}")
+            else:
+                print(f"{(what + ' ' + tag)[:60]:60s} {r[idx]:9.1f} {o[idx]:9.1f} {r[idx] / o[idx]:6.2f}x")
+    # RoPE on q and k of the GPT-124M shape: the reference rotates [S, B, nh, D] views with two launches
+    from .ops.rope import rope_inplace_native
+    S, B, nh, D = 1024, 16, 12, 64
+    qkv = torch.randn(S, B, 3, nh, D, device=dev, generator=g).bfloat16()
+    pos = torch.arange(S, device=dev, dtype=torch.float32)
+    ang = pos[:, None] * (10000.0 ** (-torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    qv, kv = qkv[:, :, 0], qkv[:, :, 1]
+    cos_b, sin_b = cos.bfloat16(), sin.bfloat16()      # the reference rounds its tables to the activation dtype
+    t_ref = timer.time_us(lambda: ref_rope(qv, kv, cos_b, sin_b), iters=iters, warmup=4)
+    t_our = timer.time_us(lambda: rope_inplace_native(qkv, cos, sin, S, B, nh, D, parts=2, token_stride=3 * nh * D,
+                                                      backward=False), iters=iters, warmup=4)
+    print(f"{'rope q,k fwd gpt124m (ours: in place; in training folded into the QKV GEMM)':60s} "
+          f"{t_ref:9.1f} {t_our:9.1f} {t_ref / t_our:6.2f}x")
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--vs-reference", action="store_true",
+                    help="time the reference's Triton attention / RoPE (baseline/_ref) next to ours")
     ap.add_argument("--only", default=None)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
@@ -192,6 +278,9 @@ def main():
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     bw, fl, kind = peaks()
+    if args.vs_reference:
+        vs_reference(dev, Timer(dev), args.iters)
+        return
     cases = build_cases(dev, args.small)
     if args.only:
         cases = [c for c in cases if args.only in c[0]]

@@ -71,7 +71,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "gfs_swiglu_bwd": ([vp, vp, vp, i, i, vp], i),
         "gfs_embedding_fwd": ([vp, vp, vp, i, i, i, i, i, i, i, vp], i),
         "gfs_embedding_bwd": ([vp, vp, vp, vp, i, i, i, i, vp], i),
-        "gfs_embedding_bwd_sorted": ([vp, vp, vp, vp, i, i, i, i, i, vp], i),
+        "gfs_embedding_sort_keys": ([vp, vp, i, i, i, i, vp], i),
+        "gfs_embedding_bwd_keys": ([vp, vp, vp, i, i, i, vp], i),
         "gfs_ce_fwd": ([vp, vp, vp, vp, vp, i, i, cl, i, i, vp], i),
         "gfs_ce_combine": ([vp, vp, vp, i, i, vp], i),
         "gfs_ce_bwd": ([vp, vp, vp, vp, i, i, cl, i, vp], i),

@@ -28,7 +28,7 @@ import torch
 
 from ..ops import _lib
 from ..ops import gemm as gemm_ops
-from ..ops.embedding import embedding_bwd_native
+from ..ops.embedding import embedding_bwd_native, sort_ids_async
 from ..ops.grad_sink import GradSink
 from . import parallel_state as ps
 from . import symm
@@ -413,6 +413,7 @@ class _EmbeddingReduceScatter(torch.autograd.Function):
         _lib.check(rc, "gfs_embedding_scatter")
         ctx.save_for_backward(ids)
         ctx.meta = (v0, v1, sink, weight.shape, S, B, H)
+        ctx.sorted_ids = sort_ids_async(ids, v0, v1) if weight.requires_grad else None   # for the backward
         # the result is layer 0's input and is saved for its backward, while the pooled symmetric
         # buffer is written again by the next forward: hand out a private copy (a few MB per step)
         return out.tensor.view(Ss, B, H).clone()
@@ -423,11 +424,12 @@ class _EmbeddingReduceScatter(torch.autograd.Function):
         v0, v1, sink, wshape, S, B, H = ctx.meta
         full = allgather_rows(_as2d(dout, B * H), "embb").view(S, B, H)
         if sink is not None:
-            embedding_bwd_native(ids, full, sink.target(), v0, v1, accumulate=sink.consume_accumulate())
+            embedding_bwd_native(ids, full, sink.target(), v0, v1, accumulate=sink.consume_accumulate(),
+                                 sorted_ids=ctx.sorted_ids)
             sink.done()
             return None, None, None, None, None
         dw = torch.zeros(wshape, dtype=dout.dtype, device=dout.device)
-        embedding_bwd_native(ids, full, dw, v0, v1, accumulate=True)
+        embedding_bwd_native(ids, full, dw, v0, v1, accumulate=True, sorted_ids=ctx.sorted_ids)
         return None, dw, None, None, None
 
 

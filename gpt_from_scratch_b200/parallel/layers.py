@@ -20,7 +20,7 @@ import torch.nn as nn
 import torch.nn.init as init
 
 from ..ops import gemm as gemm_ops
-from ..ops.embedding import embedding_bwd_native, embedding_fwd_native
+from ..ops.embedding import embedding_bwd_native, embedding_fwd_native, sort_ids_async
 from ..ops.grad_sink import GradSink
 from . import mappings
 from . import parallel_state as ps
@@ -215,7 +215,10 @@ class _EmbeddingFn(torch.autograd.Function):
     def forward(ctx, ids, weight, v0, v1, sink):
         ctx.save_for_backward(ids)
         ctx.meta = (v0, v1, sink, weight.shape)
-        return embedding_fwd_native(ids, weight, v0, v1)
+        out = embedding_fwd_native(ids, weight, v0, v1)
+        # the backward needs the ids sorted: start that now, on a side stream
+        ctx.sorted_ids = sort_ids_async(ids, v0, v1) if weight.requires_grad else None
+        return out
 
     @staticmethod
     def backward(ctx, dout):
@@ -223,11 +226,12 @@ class _EmbeddingFn(torch.autograd.Function):
         v0, v1, sink, wshape = ctx.meta
         dout = dout.contiguous()
         if sink is not None:
-            embedding_bwd_native(ids, dout, sink.target(), v0, v1, accumulate=sink.consume_accumulate())
+            embedding_bwd_native(ids, dout, sink.target(), v0, v1, accumulate=sink.consume_accumulate(),
+                                 sorted_ids=ctx.sorted_ids)
             sink.done()
             return None, None, None, None, None
         dw = torch.zeros(wshape, dtype=dout.dtype, device=dout.device)
-        embedding_bwd_native(ids, dout, dw, v0, v1, accumulate=True)
+        embedding_bwd_native(ids, dout, dw, v0, v1, accumulate=True, sorted_ids=ctx.sorted_ids)
         return None, dw, None, None, None
 
 
