@@ -99,14 +99,39 @@ class TrainEngine:
     def train_step(self, inputs: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         if self.cuda_graph and self.steps_done >= self.graph_warmup:
             if self._graph is None:
-                self._capture(inputs, labels)
-            if tuple(inputs.shape) == self._graph_shape:
+                self._try_capture(inputs, labels)
+            if self._graph is not None and tuple(inputs.shape) == self._graph_shape:
                 return self._replay(inputs, labels)
         loss = self._eager_step(inputs, labels)
         self.steps_done += 1
         return loss
 
     # ------------------------------------------------------------------ CUDA graph
+    def _try_capture(self, inputs: torch.Tensor, labels: torch.Tensor) -> None:
+        """Capture the step; if the capture fails (an operator that cannot be captured on this
+        system), undo its host-side effects, say so once and keep the eager loop."""
+        import sys
+        from .ops import gemm as gemm_ops
+        from .ops import rmsnorm as rmsnorm_ops
+        steps_before = self.optimizer._step_count
+        try:
+            self._capture(inputs, labels)
+        except Exception as e:  # noqa: BLE001 - any capture failure means "run eagerly"
+            from .parallel import symm
+            self.cuda_graph = False
+            self._graph = None
+            symm.abort_graph_capture()
+            gemm_ops._wgrad_queue.items.clear()          # parked work refers to tensors of the failed capture
+            gemm_ops._wgrad_queue.tiles = 0
+            rmsnorm_ops._dw_queue.items.clear()
+            if self.optimizer._step_count != steps_before:   # the captured step never ran on the GPU
+                self.optimizer._step_count = steps_before
+                st = self.optimizer._adam_state()
+                st["step"].fill_(float(steps_before))
+            torch.cuda.synchronize(self.device)
+            print(f"[gpt_from_scratch_b200] CUDA-graph capture of the training step failed "
+                  f"({type(e).__name__}: {str(e)[:200]}); continuing with eager launches", file=sys.stderr)
+
     def _capture(self, inputs: torch.Tensor, labels: torch.Tensor) -> None:
         """Capture one whole step (all ranks do so at the same step). Nothing runs on the GPU here;
         the first replay executes the captured step."""

@@ -163,17 +163,26 @@ class DistributedOptimizer:
     def _make_buckets(self) -> list[tuple[int, int]]:
         """Cut the flat buffer into at most NUM_BUCKETS ranges of roughly equal size at parameter
         boundaries (rounded down to a multiple of 8 x DP size, so a boundary may fall a few
-        elements inside a parameter, which then belongs to both buckets)."""
+        elements inside a parameter, which then belongs to both buckets). The walk goes from the
+        END of the buffer, the order in which the backward pass produces the gradients, so the
+        first bucket to leave is the LM head alone and later buckets fill up in production order."""
         align = 8 * self.dp_world_size
         target = max(align, self.padded_numel // self.NUM_BUCKETS)
-        cuts, offset, last = [0], 0, 0
-        for p in self.params:
-            offset += p.numel()
+        cuts, last = [self.padded_numel], self.padded_numel
+        offset = sum(p.numel() for p in self.params)
+        for p in reversed(self.params):
+            offset -= p.numel()
             c = offset // align * align
-            if c - last >= target and self.padded_numel - c >= target // 2:
+            if last - c >= target and c >= target // 2:
                 cuts.append(c)
                 last = c
-        cuts.append(self.padded_numel)
+        # the first parameter (the embedding table: its gradient is the LAST one the backward pass
+        # produces) gets a bucket of its own when it is large, so what precedes it can leave earlier
+        first_end = self.params[0].numel() // align * align
+        if first_end >= target // 2 and first_end < last:
+            cuts.append(first_end)
+        cuts.append(0)
+        cuts = sorted(set(cuts))
         return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
 
     def _init_overlap(self) -> None:

@@ -188,6 +188,15 @@ def end_graph_capture() -> None:
         g.record_per_step()
 
 
+def abort_graph_capture() -> None:
+    """A capture failed after :func:`begin_graph_capture`: the launches it recorded never ran, so
+    the counts they added on the host are dropped (the base words already hold everything that
+    did run)."""
+    for g in _groups.values():
+        for s in g._sites.values():
+            s.target.value = 0
+
+
 def get_group(kind: str) -> SymmGroup:
     """``kind``: "tp", "dp" or "world" (all ranks of the job)."""
     from . import parallel_state as ps

@@ -327,3 +327,40 @@ def test_lazy_zero_grad_clears_slices_written_by_plain_autograd():
     opt.zero_grad()
     opt._materialise_unwritten()
     assert float(lin.bias.grad.abs().sum()) == 0.0
+
+
+def test_gradient_buckets_cover_the_flat_buffer_in_aligned_pieces():
+    """The bucket cut of the data-parallel gradient reduction: whole buffer covered once, every
+    bucket a multiple of 8 x DP size long (so each rank's slice is a whole number of 16-byte
+    vectors), boundaries at (rounded) parameter boundaries, and a bucket count that stays small."""
+    from gpt_from_scratch_b200.optimizer import DistributedOptimizer
+
+    class Stub:
+        NUM_BUCKETS = DistributedOptimizer.NUM_BUCKETS
+        _make_buckets = DistributedOptimizer._make_buckets
+
+    for dp, sizes in ((8, [50304 * 768] + [768, 2304 * 768, 768 * 768, 768, 6144 * 768, 768 * 3072] * 12 +
+                          [768, 50304 * 768]),
+                      (2, [1000, 24, 7, 4096, 333]),
+                      (4, [64])):
+        st = Stub()
+        st.dp_world_size = dp
+        st.params = [torch.empty(n) for n in sizes]
+        total = sum(sizes)
+        align = dp * 8
+        st.padded_numel = (total + align - 1) // align * align
+        buckets = st._make_buckets()
+        assert buckets[0][0] == 0 and buckets[-1][1] == st.padded_numel
+        assert all(a1 == b0 for (_, a1), (b0, _) in zip(buckets[:-1], buckets[1:]))
+        assert all((b - a) % align == 0 and b > a for a, b in buckets)
+        assert len(buckets) <= DistributedOptimizer.NUM_BUCKETS + 1
+    # the 124M model at DP8: the LM head, whose gradient the backward pass produces first, is a
+    # bucket of its own (it can leave at once)
+    st = Stub()
+    st.dp_world_size = 8
+    sizes = [50304 * 768] + [768, 2304 * 768, 768 * 768, 768, 6144 * 768, 768 * 3072] * 12 + [768, 50304 * 768]
+    st.params = [torch.empty(1).expand(n) for n in sizes]
+    st.padded_numel = sum(sizes)
+    b = st._make_buckets()
+    assert b[-1] == (sum(sizes) - 50304 * 768, sum(sizes)), b
+    assert b[0] == (0, 50304 * 768), b     # and the embedding table, produced last, another
