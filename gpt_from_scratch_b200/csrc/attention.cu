@@ -304,18 +304,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // pass 1: row maximum (TMEM loads double buffered against the arithmetic)
       float mx = -INFINITY;
       uint32_t va[32], vb[32];
-      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
+      // Diagonal / tail block: dead scores become -inf in the registers and the block runs the same
+      // max / exponential code as every other block (a separate masked copy of that code executes
+      // once per CTA from a cold instruction cache and cost more than two unmasked blocks).
+      auto mask_chunk = [&](uint32_t (&v)[32], int c) {
         if (need_mask) {
+          const int lim_c = p.causal ? row_g - j * 128 - c : 0x7fffffff;   // last live column of the chunk
+          const int lim = min(lim_c, p.S - 1 - j * 128 - c);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col_g = j * 128 + c + e;
-            const bool dead = (p.causal && col_g > row_g) || col_g >= p.S;
-            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(v[e]));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+          for (int e = 0; e < 32; ++e) v[e] = (e > lim) ? 0xff800000u : v[e];
         }
+      };
+      auto max_chunk = [&](uint32_t (&v)[32], int c) {
+        mask_chunk(v, c);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
       };
       tmem_ld_32x32(s_addr + 0, va);
       tmem_ld_wait_for(va);
@@ -338,20 +341,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
       float rs = 0.f;
       uint8_t* prow = Ps + st * P_BYTES + r * 128;
-      auto prob_chunk_impl = [&](auto mask_tag, const uint32_t (&v)[32], int c) {
-        constexpr bool MASKED = decltype(mask_tag)::value;
+      auto prob_chunk = [&](uint32_t (&v)[32], int c) {
+        mask_chunk(v, c);
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
-          float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
-          if constexpr (MASKED) {
-            const int col_g = j * 128 + c + e;
-            const bool dead0 = (p.causal && col_g > row_g) || col_g >= p.S;
-            const bool dead1 = (p.causal && col_g + 1 > row_g) || col_g + 1 >= p.S;
-            x0 = dead0 ? 0.f : x0;
-            x1 = dead1 ? 0.f : x1;
-          }
+          const float x0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl2, -moff));
+          const float x1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl2, -moff));
           rs += x0 + x1;
           packed[e >> 1] = pack_bf16x2(x0, x1);
         }
@@ -362,10 +358,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           const uint4 w = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
           *reinterpret_cast<uint4*>(blk + ((((chunk0 + q4) ^ (r & 7)) & 7) << 4)) = w;
         }
-      };
-      auto prob_chunk = [&](const uint32_t (&v)[32], int c) {
-        if (need_mask) prob_chunk_impl(std::true_type{}, v, c);
-        else prob_chunk_impl(std::false_type{}, v, c);
       };
       tmem_ld_wait_for(va);
       tmem_ld_32x32(s_addr + 32, vb);
@@ -858,6 +850,12 @@ __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __n
   }
   for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (row < total && sub == 0) dvec[(static_cast<size_t>(b) * nh + h) * S_pad + s] = acc;
+  // rows S .. S_pad-1 of every head: zeros (the backward multiplies them by probabilities that are 0)
+  const int pad = S_pad - S;
+  const long long pad_total = static_cast<long long>(pad) * B * nh;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pad_total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dvec[(i / pad) * S_pad + S + (i % pad)] = 0.f;
 }
 
 // ---------------------------------------------------------------------------
@@ -1129,8 +1127,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       uint8_t* m1row = M1 + sb * M_BYTES + r * 128;
       uint8_t* m2row = M2 + sb * M_BYTES + r * 128;
       uint32_t xa[32], ya[32], xb[32], yb[32];
-      auto grad_chunk_impl = [&](auto mask_tag, const uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
-        constexpr bool MASKED = decltype(mask_tag)::value;
+      // Masked tiles (the diagonal, the sequence tail) turn their dead scores into -inf in the
+      // registers, which makes both P and dS exact zeros (dvec and dP are finite everywhere, the
+      // padding rows of dvec are written as zeros), and then run the same code as every other tile.
+      auto grad_chunk_impl = [&](uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
+        if (need_mask) {
+          const int col0 = ti * 64 + c;
+          const int hi = p.S - col0;                                   // first column past the sequence
+          if (MODE == 0) {                                             // col = query, row = key
+            const int lo = p.causal ? row_g - col0 : -0x7fffffff;      // queries before the key are dead
+#pragma unroll
+            for (int e = 0; e < 32; ++e) xv[e] = (e < lo || e >= hi) ? 0xff800000u : xv[e];
+          } else {                                                     // col = key, row = query
+            const int lim = min(p.causal ? row_g - col0 : 0x7fffffff, hi - 1);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) xv[e] = (e > lim) ? 0xff800000u : xv[e];
+          }
+        }
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -1148,14 +1161,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
             }
             pe[u] = fast_exp2(fmaf(__uint_as_float(xv[e + u]), sl2, -lse_e));
             de[u] = pe[u] * (__uint_as_float(yv[e + u]) - dv_e);
-            if constexpr (MASKED) {
-              const int col_g = ti * 64 + col;
-              bool dead;
-              if (MODE == 0) dead = (p.causal && col_g < row_g) || col_g >= p.S;  // col = query, row = key
-              else dead = (p.causal && col_g > row_g) || col_g >= p.S;            // col = key, row = query
-              pe[u] = dead ? 0.f : pe[u];
-              de[u] = dead ? 0.f : de[u];
-            }
           }
           pp[e >> 1] = pack_bf16x2(pe[0], pe[1]);
           dd[e >> 1] = pack_bf16x2(de[0], de[1]);
@@ -1179,7 +1184,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
               make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]);
         }
       };
-      auto grad_chunk = [&](const uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
+      auto grad_chunk = [&](uint32_t (&xv)[32], const uint32_t (&yv)[32], int c) {
         // alive / mixed / dead for this warp's 32 rows x 32 columns; a dead chunk costs no math
         const int row_lo = rt * 128 + quarter * 32;
         const int kind = need_mask ? mask_class<MODE == 0>(row_lo, row_lo + 31, ti * 64 + c, ti * 64 + c + 31,
@@ -1192,10 +1197,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
           const uint32_t pt = tmem_base + lane_base + PT_COL + sb * 64 + (c >> 1);
           if (MODE == 0) tmem_st_32x16(pt, zeros);
           tmem_st_32x16(pt + 32, zeros);
-        } else if (kind != 0) {
-          grad_chunk_impl(std::true_type{}, xv, yv, c);
         } else {
-          grad_chunk_impl(std::false_type{}, xv, yv, c);
+          grad_chunk_impl(xv, yv, c);
         }
       };
       const uint32_t x_addr = tmem_base + lane_base + sb * 64;
