@@ -113,6 +113,47 @@ __device__ __forceinline__ void mma_tmn(uint32_t d, uint32_t a_tmem, uint32_t b,
 }
 
 // ---------------------------------------------------------------------------
+// Epilogue stores. An accumulator row lives in one thread, so a direct store instruction writes 16
+// bytes to each of 32 different rows: 32 passes through the load/store unit per instruction, which
+// made the epilogues of these kernels LSU-bound (about 1,000 cycles per 128 x 64 output tile). The
+// rows are therefore transposed through a per-warp staging area in shared memory (XOR-swizzled, free
+// of bank conflicts both ways) and leave as whole 64- or 128-byte row segments.
+// ---------------------------------------------------------------------------
+// 32 rows x 32 bf16 columns; w = this lane's row (16 packed words); stage: 2 KB of this warp.
+__device__ __forceinline__ void store_rows_32x32(uint8_t* stage, const uint32_t (&w)[16], int lane,
+                                                 __nv_bfloat16* g0, long long row_stride, int rows_valid) {
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4)
+    *reinterpret_cast<uint4*>(stage + lane * 64 + ((q4 ^ ((lane >> 1) & 3)) << 4)) =
+        make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = (lane >> 2) + 8 * i;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4));
+    if (row < rows_valid) *reinterpret_cast<uint4*>(g0 + row * row_stride + (lane & 3) * 8) = v;
+  }
+  __syncwarp();
+}
+
+// 32 rows x 64 bf16 columns; w = this lane's row (32 packed words); stage: 4 KB of this warp.
+__device__ __forceinline__ void store_rows_32x64(uint8_t* stage, const uint32_t (&w)[32], int lane,
+                                                 __nv_bfloat16* g0, long long row_stride, int rows_valid) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch)
+    *reinterpret_cast<uint4*>(stage + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+        make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = (lane >> 3) + 4 * i;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+    if (row < rows_valid) *reinterpret_cast<uint4*>(g0 + row * row_stride + (lane & 7) * 8) = v;
+  }
+  __syncwarp();
+}
+
+// ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
 struct FwdParams {
@@ -385,16 +426,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     fold_pv(n_kv - 1, alpha_prev);
 
     const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-    if (row_g < p.S) {
-      __nv_bfloat16* dst = p.O + row_g * p.o_ss + b * p.o_bs + h * p.o_hs;
+    {
+      // every P V MMA has completed (the last fold waited for it): the P buffer serves as staging
+      uint8_t* stage = Ps + (r >> 5) * 4096;
+      const int row0 = row_g - lane;
+      __nv_bfloat16* g0 = p.O + row0 * p.o_ss + b * p.o_bs + h * p.o_hs;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 w;
-        w.x = pack_bf16x2(o[c + 0] * inv_l, o[c + 1] * inv_l);
-        w.y = pack_bf16x2(o[c + 2] * inv_l, o[c + 3] * inv_l);
-        w.z = pack_bf16x2(o[c + 4] * inv_l, o[c + 5] * inv_l);
-        w.w = pack_bf16x2(o[c + 6] * inv_l, o[c + 7] * inv_l);
-        *reinterpret_cast<uint4*>(dst + c) = w;
+      for (int hf = 0; hf < D / 64; ++hf) {
+        uint32_t ow[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) ow[e] = pack_bf16x2(o[hf * 64 + 2 * e] * inv_l, o[hf * 64 + 2 * e + 1] * inv_l);
+        store_rows_32x64(stage, ow, lane, g0 + hf * 64, p.o_ss, p.S - row0);
       }
     }
     if (row_g < p.S_pad) {
@@ -417,11 +459,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 // softmax warps while K/V tiles are fetched once for 256 query rows. S, P V and P each live
 // in tensor memory (S_A S_B | PV_A PV_B | P_A P_B = 512 columns): the probabilities are
 // handed to the P V MMA as its TMEM A operand, nothing of the softmax goes through shared
-// memory. K/V use a 4-stage ring (three: 111.1 us, four: 109.4 us at the GPT-124M shape).
+// memory. K/V use a 4-stage ring (three: 111.1 us, four: 109.4 us at the GPT-124M shape with an
+// earlier version; six stages measured 1.5 % slower than four with this one).
 // ---------------------------------------------------------------------------
 constexpr int FWD64_THREADS = 64 + 256;
 constexpr int FWD64_KS = 4;
-constexpr int FWD64_SMEM = 2 * 16384 + FWD64_KS * 32768 + 256;
+constexpr int FWD64_SMEM = 2 * 16384 + FWD64_KS * 32768 + 512;
 
 // Persistent: each CTA walks work items (pair of query tiles, batch*head), heaviest pairs
 // first, so barrier set-up, the TMEM allocation and the CTA launch gap are paid once per SM
@@ -824,10 +867,12 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------
-// Backward pre-pass: dvec[b,h,s] = sum_d dO[s,b,h,d] * O[s,b,h,d]; one warp per row.
+// Backward pre-pass: dvec[b,h,s] = sum_d dO[s,b,h,d] * O[s,b,h,d]; one warp per row. Also writes
+// lse2 = lse * log2(e), the form the backward's exp2 wants (saves a multiply per score there).
 // ---------------------------------------------------------------------------
 __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                 float* __restrict__ dvec, int S, int S_pad, int B, int nh, int D, long long do_ss,
+                                 float* __restrict__ dvec, const float* __restrict__ lse, float* __restrict__ lse2,
+                                 int S, int S_pad, int B, int nh, int D, long long do_ss,
                                  long long do_bs, long long do_hs, long long o_ss, long long o_bs, long long o_hs) {
   // D/8 threads per (s, b, h) row, 16-byte loads; rows ordered h fastest (memory order of [S,B,nh,D]).
   const int tpr = D >> 3;                       // 8 or 16 threads per row
@@ -856,6 +901,10 @@ __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __n
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pad_total;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     dvec[(i / pad) * S_pad + S + (i % pad)] = 0.f;
+  const long long n_lse = static_cast<long long>(S_pad) * B * nh;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_lse;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    lse2[i] = lse[i] * LOG2E_F;
 }
 
 // ---------------------------------------------------------------------------
@@ -866,7 +915,7 @@ struct BwdParams {
   __nv_bfloat16* out2;  // mode 0: dV
   long long o1_ss, o1_bs, o1_hs;
   long long o2_ss, o2_bs, o2_hs;
-  const float* lse;   // [B, nh, S_pad]
+  const float* lse;   // [B, nh, S_pad], already multiplied by log2(e)
   const float* dvec;  // [B, nh, S_pad]
   int S, S_pad, B, nh;
   float scale;
@@ -880,8 +929,11 @@ struct BwdParams {
 // CW = number of compute warps (4 or 8). With 8, every accumulator row is shared by two
 // threads that each take half of the 64 streamed columns (no exchange is needed: the
 // row/column statistics are inputs), which doubles the warps available to hide latency.
-// TS = stages of the streamed-tile ring (a stage is only released when the gradient MMAs that
-// read it have finished, so two stages would put the TMA latency on the critical path).
+// TS = stages of the streamed-tile ring. A stage is only released when the gradient MMAs that read
+// it have finished, and the score MMAs run two tiles ahead, so the TMA of a tile has (TS - 2) tile
+// periods to land. head_dim 64 (P / dS in tensor memory, so the shared memory is free) uses 8
+// stages: 214 us against 224 us with 4 for the whole backward at the GPT-124M shape, 217 us with
+// 10; head_dim 128 has room for 3.
 template <int D, int MODE, int NBUF, int CW, int TS>
 __global__ void __launch_bounds__(64 + 32 * CW, NBUF == 1 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
@@ -906,8 +958,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   uint8_t* T1 = R2 + R_BYTES;        // 2 stages
   uint8_t* T2 = T1 + TS * T_BYTES;
   uint8_t* M1 = T2 + TS * T_BYTES;
-  uint8_t* M2 = M1 + NBUF * M_BYTES;
-  float* stats = reinterpret_cast<float*>(M2 + NBUF * M_BYTES);  // mode 0: [TS stages][lse 64 | dvec 64]
+  // P / dS through tensor memory: M1 is only the 16 KB staging area of the epilogue, M2 is not used
+  uint8_t* M2 = M1 + (PT ? M_BYTES : NBUF * M_BYTES);
+  float* stats = reinterpret_cast<float*>(M2 + (PT ? 0 : NBUF * M_BYTES));  // mode 0: [TS stages][lse 64 | dvec 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + TS * 512);
   uint64_t* r_full = bars;
   uint64_t* t_full = bars + 1;             // [TS]
@@ -1107,7 +1160,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     const int row_g = rt * 128 + r;  // mode 0: key position, mode 1: query position
     float row_lse = 0.f, row_dvec = 0.f;
     if (MODE == 1 && row_g < p.S_pad) {
-      row_lse = p.lse[static_cast<size_t>(bh) * p.S_pad + row_g] * LOG2E_F;
+      row_lse = p.lse[static_cast<size_t>(bh) * p.S_pad + row_g];
       row_dvec = p.dvec[static_cast<size_t>(bh) * p.S_pad + row_g];
     }
     for (int t = 0; t < n_t; ++t) {
@@ -1146,24 +1199,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         }
         uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pe[2], de[2];
+        for (int e = 0; e < 32; e += 4) {
+          float ls[4], dv[4];
+          if (MODE == 0) {   // per-column statistics of the streamed query tile (same address in all lanes)
+            const float4 l4 = *reinterpret_cast<const float4*>(st_lse + c + e);
+            const float4 d4 = *reinterpret_cast<const float4*>(st_dv + c + e);
+            ls[0] = l4.x; ls[1] = l4.y; ls[2] = l4.z; ls[3] = l4.w;
+            dv[0] = d4.x; dv[1] = d4.y; dv[2] = d4.z; dv[3] = d4.w;
+          } else {
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c + e + u;
-            float lse_e, dv_e;
-            if (MODE == 0) {
-              lse_e = st_lse[col] * LOG2E_F;
-              dv_e = st_dv[col];
-            } else {
-              lse_e = row_lse;
-              dv_e = row_dvec;
+            for (int u = 0; u < 4; ++u) {
+              ls[u] = row_lse;
+              dv[u] = row_dvec;
             }
-            pe[u] = fast_exp2(fmaf(__uint_as_float(xv[e + u]), sl2, -lse_e));
-            de[u] = pe[u] * (__uint_as_float(yv[e + u]) - dv_e);
           }
-          pp[e >> 1] = pack_bf16x2(pe[0], pe[1]);
+          float pe[4], de[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            pe[u] = fast_exp2(fmaf(__uint_as_float(xv[e + u]), sl2, -ls[u]));
+            de[u] = pe[u] * (__uint_as_float(yv[e + u]) - dv[u]);
+          }
+          if (MODE == 0) {
+            pp[e >> 1] = pack_bf16x2(pe[0], pe[1]);
+            pp[(e >> 1) + 1] = pack_bf16x2(pe[2], pe[3]);
+          }
           dd[e >> 1] = pack_bf16x2(de[0], de[1]);
+          dd[(e >> 1) + 1] = pack_bf16x2(de[2], de[3]);
         }
         if (PT) {
           // columns c .. c+31 of this row -> 16 packed columns of the P / dS tensor-memory tiles
@@ -1232,55 +1293,50 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     g0 += n_t;
     mbar_wait(acc_full, it & 1, wctx, STATUS_TIMEOUT_TMEM_FULL);
     tc_fence_after();
-    const bool live = row_g < p.S;
-    __nv_bfloat16* d1 = p.out1 + row_g * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
-    __nv_bfloat16* d2 = (MODE == 0) ? p.out2 + row_g * p.o2_ss + b * p.o2_bs + h * p.o2_hs : nullptr;
+    // The accumulators leave through a staging area in the M1 buffer (nothing reads it any more:
+    // acc_full covers the item's last gradient MMAs): rows [32 * quarter, +32) of M1 are only ever
+    // written by the two warps of this quarter, which meet at a named barrier before either of them
+    // goes on to the next item's first block.
+    const int row0 = rt * 128 + quarter * 32;
+    uint8_t* stage = M1 + quarter * 4096 + chalf * 2048;
+    __nv_bfloat16* g1 = p.out1 + row0 * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
+    __nv_bfloat16* g2 = (MODE == 0) ? p.out2 + row0 * p.o2_ss + b * p.o2_bs + h * p.o2_hs : nullptr;
 #pragma unroll 1
     for (int c = chalf * (D / (CW / 4)); c < (chalf + 1) * (D / (CW / 4)); c += 32) {
-      uint32_t v[32];
+      uint32_t v[32], w[16];
       // mode 0: ACC2 holds dK (scaled), ACC1 holds dV; mode 1: ACC1 holds dQ (scaled)
       tmem_ld_32x32(tmem_base + lane_base + (MODE == 0 ? ACC2 : ACC1) + c, v);
       tmem_ld_wait();
-      if (live) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          float f[8];
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * q4 + e]) * p.scale;
-          if (p.rope_cos != nullptr) {  // inverse rotation: sin -> -sin
-            const size_t ti = static_cast<size_t>(row_g) * (D / 2) + ((c + 8 * q4) >> 1);
-            const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
-            const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
-            const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
-            f[0] = a0 * cs.x + a1 * sn.x; f[1] = a1 * cs.x - a0 * sn.x;
-            f[2] = a2 * cs.y + a3 * sn.y; f[3] = a3 * cs.y - a2 * sn.y;
-            f[4] = a4 * cs.z + a5 * sn.z; f[5] = a5 * cs.z - a4 * sn.z;
-            f[6] = a6 * cs.w + a7 * sn.w; f[7] = a7 * cs.w - a6 * sn.w;
-          }
-          uint4 w;
-          w.x = pack_bf16x2(f[0], f[1]);
-          w.y = pack_bf16x2(f[2], f[3]);
-          w.z = pack_bf16x2(f[4], f[5]);
-          w.w = pack_bf16x2(f[6], f[7]);
-          *reinterpret_cast<uint4*>(d1 + c + 8 * q4) = w;
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * q4 + e]) * p.scale;
+        if (p.rope_cos != nullptr && row_g < p.S) {  // inverse rotation: sin -> -sin
+          const size_t ti = static_cast<size_t>(row_g) * (D / 2) + ((c + 8 * q4) >> 1);
+          const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
+          const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
+          const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
+          f[0] = a0 * cs.x + a1 * sn.x; f[1] = a1 * cs.x - a0 * sn.x;
+          f[2] = a2 * cs.y + a3 * sn.y; f[3] = a3 * cs.y - a2 * sn.y;
+          f[4] = a4 * cs.z + a5 * sn.z; f[5] = a5 * cs.z - a4 * sn.z;
+          f[6] = a6 * cs.w + a7 * sn.w; f[7] = a7 * cs.w - a6 * sn.w;
         }
+        w[4 * q4 + 0] = pack_bf16x2(f[0], f[1]);
+        w[4 * q4 + 1] = pack_bf16x2(f[2], f[3]);
+        w[4 * q4 + 2] = pack_bf16x2(f[4], f[5]);
+        w[4 * q4 + 3] = pack_bf16x2(f[6], f[7]);
       }
+      store_rows_32x32(stage, w, lane, g1 + c, p.o1_ss, p.S - row0);
       if (MODE == 0) {
         tmem_ld_32x32(tmem_base + lane_base + ACC1 + c, v);
         tmem_ld_wait();
-        if (live) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]), __uint_as_float(v[8 * q4 + 1]));
-            w.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-            w.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-            w.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
-            *reinterpret_cast<uint4*>(d2 + c + 8 * q4) = w;
-          }
-        }
+        for (int e = 0; e < 16; ++e) w[e] = pack_bf16x2(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+        store_rows_32x32(stage, w, lane, g2 + c, p.o2_ss, p.S - row0);
       }
     }
+    if (CW == 8) named_barrier_sync(8 + quarter, 64);
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(acc_empty);  // the accumulators may be overwritten by the next item
@@ -1378,13 +1434,15 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   const int S_pad = ((S + 127) / 128) * 128;
   const long long *sq = strides, *sk = strides + 3, *sv = strides + 6, *so = strides + 9, *sdo = strides + 12,
                   *sdq = strides + 15, *sdk = strides + 18, *sdv = strides + 21;
+  // second half of the dvec buffer: lse * log2(e)
+  float* lse2 = static_cast<float*>(dvec) + static_cast<size_t>(S_pad) * B * nh;
   {
     const long long rows = static_cast<long long>(S) * B * nh;
     const int threads = 256;
     const int rows_per_block = threads / (D >> 3);
     attn_dvec_kernel<<<static_cast<int>((rows + rows_per_block - 1) / rows_per_block), threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec), S,
-        S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+        static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec),
+        static_cast<const float*>(lse), lse2, S, S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
     if (cudaGetLastError() != cudaSuccess) return -11;
   }
   const CUtensorMap* q128 = make_map(q, D, S, nh, B, sq, 128);
@@ -1397,7 +1455,7 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   const CUtensorMap* do64 = make_map(dO, D, S, nh, B, sdo, 64);
   if (!q128 || !k128 || !v128 || !do128 || !q64 || !k64 || !v64 || !do64) return -3;
   BwdParams p;
-  p.lse = static_cast<const float*>(lse);
+  p.lse = lse2;
   p.dvec = static_cast<const float*>(dvec);
   p.S = S; p.S_pad = S_pad; p.B = B; p.nh = nh; p.scale = scale; p.causal = causal;
   p.status = gfs_host::status_words();
@@ -1408,8 +1466,9 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   const int ctas = std::min(n_items, gfs_host::sm_count());
   const int nbuf = 2;
   const int bwd_threads = 64 + 32 * 8;
-  const int ts = (D == 64) ? 4 : 3;
-  const int smem = 2 * (D / 64) * 16384 + 2 * ts * (D / 64) * 8192 + 2 * nbuf * 16384 + ts * 512 + 256 + 1024;
+  const int ts = (D == 64) ? 8 : 3;
+  const int m_bytes = (D == 64) ? 16384 : 2 * nbuf * 16384;   // head_dim 64: epilogue staging only
+  const int smem = 2 * (D / 64) * 16384 + 2 * ts * (D / 64) * 8192 + m_bytes + ts * 512 + 512 + 1024;
   static bool set_done[4] = {false, false, false, false};
   // mode 0: dK, dV
   BwdParams p0 = p;
@@ -1419,11 +1478,11 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p1.out1 = static_cast<__nv_bfloat16*>(dq); p1.o1_ss = sdq[0]; p1.o1_bs = sdq[1]; p1.o1_hs = sdq[2];
   p1.out2 = nullptr; p1.o2_ss = p1.o2_bs = p1.o2_hs = 0;
   if (D == 64) {
-    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 4>, smem)) return -10; set_done[0] = true; }
-    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 4>, smem)) return -10; set_done[1] = true; }
-    flash_bwd_kernel<64, 0, 2, 8, 4><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
+    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 8>, smem)) return -10; set_done[0] = true; }
+    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 8>, smem)) return -10; set_done[1] = true; }
+    flash_bwd_kernel<64, 0, 2, 8, 8><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<64, 1, 2, 8, 4><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
+    flash_bwd_kernel<64, 1, 2, 8, 8><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
   } else {
     if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3>, smem)) return -10; set_done[2] = true; }
     if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3>, smem)) return -10; set_done[3] = true; }

@@ -60,7 +60,8 @@ def flash_fwd_native(q, k, v, out, causal: bool, scale: float) -> torch.Tensor:
 def flash_bwd_native(q, k, v, out, dout, lse, dq, dk, dv, causal: bool, scale: float, rope=None) -> None:
     """``rope = (cos, sin)``: dq and dk are rotated back (inverse RoPE) as they are written."""
     S, B, nh, D = q.shape
-    dvec = torch.empty_like(lse)
+    # scratch of the pre-pass: dvec = rowsum(dO * O), then a copy of lse scaled by log2(e)
+    dvec = torch.empty((2,) + tuple(lse.shape), dtype=torch.float32, device=lse.device)
     st = (ctypes.c_longlong * 24)(*_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out), *_strides3(dout),
                                   *_strides3(dq), *_strides3(dk), *_strides3(dv))
     rc = _lib.lib().gfs_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
