@@ -280,8 +280,8 @@ def measure(config_name: str, cfgd: dict, args, rank: int, world: int, local_ran
     e2e = None
     if with_e2e:
         # the end-to-end loop is the headline and goes first; the resident-input loop after it
-        # explains it (under the power cap the clocks keep sinking for the first seconds of load,
-        # so whichever loop runs second reads about 2 % slower on the same work)
+        # explains it (two identical loops run back to back have differed by a percent or two in
+        # either direction on the same GPU, so the order is fixed rather than meaningful)
         ms_e2e, last_loss = timed_loop(step_fn, batches, args.steps, "e2e")
     l0 = launches() if launches else 0
     ms_dev, _ = timed_loop(step_fn, batches, args.steps, "device")
