@@ -158,6 +158,8 @@ class TrainEngine:
         from .ops import _lib
         self._static_inputs.copy_(inputs, non_blocking=True)
         self._static_labels.copy_(labels, non_blocking=True)
+        from .parallel import symm
+        symm.fold_pending()          # launches made outside the graph since the last replay
         self._graph.replay()
         if self._host_counted:
             self._host_counted = False

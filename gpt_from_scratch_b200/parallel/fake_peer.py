@@ -46,6 +46,9 @@ class FakePeerGroup(symm.SymmGroup):
         self._pools = {}
         self._next_slot = 0
         self.has_multicast = False
+        import numpy as np
+        self._target_store = (ctypes.c_uint * symm.NUM_FLAG_SLOTS)()
+        self._target_view = np.frombuffer(self._target_store, dtype=np.uint32)
         flags = self.alloc("__flags__", 2 * symm.NUM_FLAG_SLOTS, torch.int32, zero=True)
         self.flags = flags
         self.flag_ptrs = flags.ptrs

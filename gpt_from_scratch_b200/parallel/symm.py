@@ -50,12 +50,14 @@ class SymmBuffer:
 
 
 class Site:
-    """Flag slots + cumulative target of one call site."""
+    """Flag slots + cumulative target of one call site. ``target`` is a ``c_uint`` that lives inside
+    the group's target array when one is given (so "has any site counted since the last fold" is one
+    vector test)."""
     __slots__ = ("slot0", "target")
 
-    def __init__(self, slot0: int):
+    def __init__(self, slot0: int, store=None):
         self.slot0 = slot0
-        self.target = ctypes.c_uint(0)
+        self.target = ctypes.c_uint(0) if store is None else ctypes.c_uint.from_buffer(store, 4 * slot0)
 
 
 class SymmGroup:
@@ -70,6 +72,9 @@ class SymmGroup:
         self._pools: dict = {}
         self._next_slot = 0
         self.has_multicast = False
+        import numpy as np
+        self._target_store = (ctypes.c_uint * NUM_FLAG_SLOTS)()        # Site.target objects point into it
+        self._target_view = np.frombuffer(self._target_store, dtype=np.uint32)
         # counters [0, NUM_FLAG_SLOTS) + their base words [NUM_FLAG_SLOTS, 2*NUM_FLAG_SLOTS)
         flags = self.alloc("__flags__", 2 * NUM_FLAG_SLOTS, torch.int32, zero=True)
         self.flags = flags
@@ -125,7 +130,7 @@ class SymmGroup:
         if s is None:
             if self._next_slot + self.world > NUM_FLAG_SLOTS:
                 raise RuntimeError("out of flag slots")
-            s = Site(self._next_slot)
+            s = Site(self._next_slot, self._target_store)
             self._next_slot += self.world
             self._sites[name] = s
         return s
@@ -173,6 +178,16 @@ def begin_graph_capture() -> None:
     """Call on every rank right before a step is captured (outside the capture)."""
     for g in _groups.values():
         g.fold_targets_into_base()
+
+
+def fold_pending() -> None:
+    """Call before replaying a captured step: launches made outside the graph since the capture (an
+    evaluation pass, :meth:`DistributedOptimizer.sync_params`) advanced the flags and the host
+    counts but not the base words the captured waits start from; fold them in. Local, cheap when
+    nothing is pending (one vector test per group)."""
+    for g in _groups.values():
+        if g._target_view.any():
+            g.fold_targets_into_base()
 
 
 def graph_epilogue() -> None:
