@@ -239,6 +239,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();       // set-up above may overlap the tail of the preceding kernel (programmatic launch)
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -540,6 +542,8 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();       // set-up above may overlap the tail of the preceding kernel (programmatic launch)
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -874,6 +878,8 @@ __global__ void attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, const __n
                                  float* __restrict__ dvec, const float* __restrict__ lse, float* __restrict__ lse2,
                                  int S, int S_pad, int B, int nh, int D, long long do_ss,
                                  long long do_bs, long long do_hs, long long o_ss, long long o_bs, long long o_hs) {
+  pdl_wait();
+  pdl_trigger();
   // D/8 threads per (s, b, h) row, 16-byte loads; rows ordered h fastest (memory order of [S,B,nh,D]).
   const int tpr = D >> 3;                       // 8 or 16 threads per row
   const int rows_per_block = blockDim.x / tpr;
@@ -1033,6 +1039,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();       // set-up above may overlap the tail of the preceding kernel (programmatic launch)
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -1406,11 +1414,12 @@ int gfs_flash_fwd(const void* q, const void* k, const void* v, void* o, void* ls
     const int n_pairs = (static_cast<int>(grid.x) + 1) / 2;
     const int n_items = n_pairs * B * nh;
     const int ctas = std::min(n_items, gfs_host::sm_count());
-    flash_fwd64_kernel<<<ctas, FWD64_THREADS, FWD64_SMEM, stream>>>(*tq, *tk, *tv, p, n_pairs, n_items);
+    gfs_host::launch_pdl(flash_fwd64_kernel, dim3(ctas), dim3(FWD64_THREADS), FWD64_SMEM, stream, *tq, *tk, *tv, p,
+                         n_pairs, n_items);
   } else {
     const int smem = 32768 * 5 + 2 * 32768 + 256;
     if (!set128) { if (set_smem(flash_fwd_kernel<128, 2>, smem)) return -10; set128 = true; }
-    flash_fwd_kernel<128, 2><<<grid, ATT_THREADS, smem, stream>>>(*tq, *tk, *tv, p);
+    gfs_host::launch_pdl(flash_fwd_kernel<128, 2>, grid, dim3(ATT_THREADS), smem, stream, *tq, *tk, *tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
@@ -1440,9 +1449,11 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
     const long long rows = static_cast<long long>(S) * B * nh;
     const int threads = 256;
     const int rows_per_block = threads / (D >> 3);
-    attn_dvec_kernel<<<static_cast<int>((rows + rows_per_block - 1) / rows_per_block), threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec),
-        static_cast<const float*>(lse), lse2, S, S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+    gfs_host::launch_pdl(attn_dvec_kernel, dim3(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block)),
+                         dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(dO),
+                         static_cast<const __nv_bfloat16*>(o), static_cast<float*>(dvec),
+                         static_cast<const float*>(lse), lse2, S, S_pad, B, nh, D, sdo[0], sdo[1], sdo[2], so[0],
+                         so[1], so[2]);
     if (cudaGetLastError() != cudaSuccess) return -11;
   }
   const CUtensorMap* q128 = make_map(q, D, S, nh, B, sq, 128);
@@ -1480,15 +1491,19 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   if (D == 64) {
     if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 8>, smem)) return -10; set_done[0] = true; }
     if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 8>, smem)) return -10; set_done[1] = true; }
-    flash_bwd_kernel<64, 0, 2, 8, 8><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
+    gfs_host::launch_pdl(flash_bwd_kernel<64, 0, 2, 8, 8>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
+                         *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<64, 1, 2, 8, 8><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
+    gfs_host::launch_pdl(flash_bwd_kernel<64, 1, 2, 8, 8>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
+                         *k64, *v64, p1, n_rt, n_items);
   } else {
     if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3>, smem)) return -10; set_done[2] = true; }
     if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3>, smem)) return -10; set_done[3] = true; }
-    flash_bwd_kernel<128, 0, 2, 8, 3><<<ctas, bwd_threads, smem, stream>>>(*k128, *v128, *q64, *do64, p0, n_rt, n_items);
+    gfs_host::launch_pdl(flash_bwd_kernel<128, 0, 2, 8, 3>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
+                         *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    flash_bwd_kernel<128, 1, 2, 8, 3><<<ctas, bwd_threads, smem, stream>>>(*q128, *do128, *k64, *v64, p1, n_rt, n_items);
+    gfs_host::launch_pdl(flash_bwd_kernel<128, 1, 2, 8, 3>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
+                         *k64, *v64, p1, n_rt, n_items);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }

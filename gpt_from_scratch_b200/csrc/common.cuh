@@ -347,6 +347,12 @@ __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf)
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Programmatic dependent launch (see gfs_host::launch_pdl). pdl_wait(): returns once the preceding
+// kernel of the stream has completed and its writes are visible (a no-op for a normal launch);
+// nothing before it may touch global memory that another kernel writes or reads. pdl_trigger():
+// this CTA no longer objects to the next kernel's CTAs being scheduled on SMs that become free.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -624,5 +630,27 @@ const CUtensorMap* tmap_nd_cached(const void* base, int rank, const uint64_t* di
 // Device status words owned by the library (allocated on first use per device).
 uint32_t* status_words();
 int sm_count();
+// Programmatic dependent launch allowed (GFS_PDL, default on).
+bool pdl_enabled();
+
+// Launch with programmatic stream serialization: the kernel's CTAs may become resident and run
+// their set-up while the preceding kernel of the stream drains; the kernel must call
+// gfs::pdl_wait() before its first access to global memory. Inside a stream capture the
+// dependency becomes a programmatic edge of the graph.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 }  // namespace gfs_host

@@ -38,6 +38,8 @@ template <int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int H, float eps) {
+  pdl_wait();       // launched programmatically: the preceding kernel's output is complete from here on
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -106,6 +108,8 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw_partial, int rows, int H, int rows_per_cta) {
   extern __shared__ float red[];  // [warps][H]
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
@@ -203,6 +207,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int H, int rows_per_cta) {
   extern __shared__ float red[];  // [warps][H]
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
@@ -563,9 +569,10 @@ int gfs_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows,
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   float* rp = static_cast<float*>(rstd);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (H <= 1024) rmsnorm_fwd_kernel<4><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
-  else if (H <= 2048) rmsnorm_fwd_kernel<8><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
-  else rmsnorm_fwd_kernel<16><<<blocks, NORM_WARPS * 32, 0, st>>>(xp, wp, yp, rp, rows, H, eps);
+  const dim3 grid(blocks), block(NORM_WARPS * 32);
+  if (H <= 1024) gfs_host::launch_pdl(rmsnorm_fwd_kernel<4>, grid, block, 0, st, xp, wp, yp, rp, rows, H, eps);
+  else if (H <= 2048) gfs_host::launch_pdl(rmsnorm_fwd_kernel<8>, grid, block, 0, st, xp, wp, yp, rp, rows, H, eps);
+  else gfs_host::launch_pdl(rmsnorm_fwd_kernel<16>, grid, block, 0, st, xp, wp, yp, rp, rows, H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -607,16 +614,16 @@ int gfs_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rs
   static int set_gen = 0, set_r4 = 0, set_r8 = 0;
   if (H <= 1024) {
     if (ensure_smem(rmsnorm_bwd_reg_kernel<4>, set_r4)) return -10;
-    rmsnorm_bwd_reg_kernel<4><<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows,
-                                                                   H, rows_per_cta);
+    gfs_host::launch_pdl(rmsnorm_bwd_reg_kernel<4>, dim3(parts), dim3(warps * 32), smem, stream, a_dy, a_x, a_w, a_rstd,
+                         a_res, a_dx, a_part, rows, H, rows_per_cta);
   } else if (H <= 2048) {
     if (ensure_smem(rmsnorm_bwd_reg_kernel<8>, set_r8)) return -10;
-    rmsnorm_bwd_reg_kernel<8><<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows,
-                                                                   H, rows_per_cta);
+    gfs_host::launch_pdl(rmsnorm_bwd_reg_kernel<8>, dim3(parts), dim3(warps * 32), smem, stream, a_dy, a_x, a_w, a_rstd,
+                         a_res, a_dx, a_part, rows, H, rows_per_cta);
   } else {
     if (ensure_smem(rmsnorm_bwd_kernel, set_gen)) return -10;
-    rmsnorm_bwd_kernel<<<parts, warps * 32, smem, stream>>>(a_dy, a_x, a_w, a_rstd, a_res, a_dx, a_part, rows, H,
-                                                            rows_per_cta);
+    gfs_host::launch_pdl(rmsnorm_bwd_kernel, dim3(parts), dim3(warps * 32), smem, stream, a_dy, a_x, a_w, a_rstd, a_res,
+                         a_dx, a_part, rows, H, rows_per_cta);
   }
   if (cudaGetLastError() != cudaSuccess) return -11;
   if (dw == nullptr) return 0;   // the caller reduces `partial` later (gfs_rmsnorm_dw_reduce_multi)

@@ -164,6 +164,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();       // set-up above may overlap the tail of the preceding kernel (programmatic launch)
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_base_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -588,7 +590,9 @@ int launch_variant(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParam
     attr_set = true;
     attr_dev = dev;
   }
-  kern<<<grid, GEMM_THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0), Cfg::TOTAL, stream>>>(*ta, *tb, p);
+  if (gfs_host::launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS + (COMM != COMM_NONE ? COMM_THREADS : 0)), Cfg::TOTAL,
+                           stream, *ta, *tb, p) != cudaSuccess)
+    return -11;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

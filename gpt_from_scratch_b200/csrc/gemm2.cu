@@ -241,6 +241,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   tc_fence_before();
   cluster_sync_all();  // barriers of both CTAs initialised, TMEM allocated
   tc_fence_after();
+  // everything above ran while the preceding kernel of the stream may still have been draining
+  pdl_wait();
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -793,6 +796,8 @@ gemm2_grouped_kernel(const __grid_constant__ GroupMaps maps, const __grid_consta
   tc_fence_before();
   cluster_sync_all();
   tc_fence_after();
+  pdl_wait();
+  pdl_trigger();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wctx{abort_flag, p.status, GFS_WAIT_LIMIT_NS};
 
@@ -977,7 +982,9 @@ int launch2(const CUtensorMap* ta, const CUtensorMap* tb, const Params2& p, int 
   }
   Params2 pt = p;
   pt.trace = g_trace;
-  kern<<<grid, threads2(COMM), SMEM_TOTAL, stream>>>(*ta, *tb, ta_local ? *ta_local : *ta, pt);
+  if (gfs_host::launch_pdl(kern, dim3(grid), dim3(threads2(COMM)), SMEM_TOTAL, stream, *ta, *tb,
+                           ta_local ? *ta_local : *ta, pt) != cudaSuccess)
+    return -11;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -1294,7 +1301,9 @@ int gfs_gemm2_wgrad_grouped(int n, const unsigned long long* A, const unsigned l
     attr_dev = dev;
   }
   const int pairs = std::min(total, gfs_host::sm_count() / 2);
-  gemm2_grouped_kernel<<<2 * pairs, THREADS, SMEM_TOTAL, stream>>>(maps, p);
+  if (gfs_host::launch_pdl(gemm2_grouped_kernel, dim3(2 * pairs), dim3(THREADS), SMEM_TOTAL, stream, maps, p) !=
+      cudaSuccess)
+    return -11;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

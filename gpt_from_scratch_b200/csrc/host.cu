@@ -1,6 +1,7 @@
 // Host-side runtime shared by all kernels: tensor-map encoding (driver entry point
 // fetched at run time so the library links against cudart only), a small tensor-map
 // cache, the per-device status words and device properties.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -164,6 +165,15 @@ uint32_t* status_words() {
     per_dev[dev] = p;
   }
   return per_dev[dev];
+}
+
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = std::getenv("GFS_PDL");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
 }
 
 int sm_count() {
