@@ -1299,6 +1299,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     }
     // epilogue: accumulators -> global
     g0 += n_t;
+    // the rotary table entries of this thread's row and columns are fetched while the item's last
+    // gradient MMAs finish (their global-memory latency would otherwise sit between the
+    // accumulator load and the stores)
+    constexpr int EC = D / (CW / 4);   // accumulator columns per thread
+    float4 rope_c[EC / 8], rope_s[EC / 8];
+    const bool rope_on = p.rope_cos != nullptr && row_g < p.S;
+    if (rope_on) {
+#pragma unroll
+      for (int i = 0; i < EC / 8; ++i) {
+        const size_t ti = static_cast<size_t>(row_g) * (D / 2) + ((chalf * EC + 8 * i) >> 1);
+        rope_c[i] = *reinterpret_cast<const float4*>(p.rope_cos + ti);
+        rope_s[i] = *reinterpret_cast<const float4*>(p.rope_sin + ti);
+      }
+    }
     mbar_wait(acc_full, it & 1, wctx, STATUS_TIMEOUT_TMEM_FULL);
     tc_fence_after();
     // The accumulators leave through a staging area in the M1 buffer (nothing reads it any more:
@@ -1309,8 +1323,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     uint8_t* stage = M1 + quarter * 4096 + chalf * 2048;
     __nv_bfloat16* g1 = p.out1 + row0 * p.o1_ss + b * p.o1_bs + h * p.o1_hs;
     __nv_bfloat16* g2 = (MODE == 0) ? p.out2 + row0 * p.o2_ss + b * p.o2_bs + h * p.o2_hs : nullptr;
-#pragma unroll 1
-    for (int c = chalf * (D / (CW / 4)); c < (chalf + 1) * (D / (CW / 4)); c += 32) {
+#pragma unroll
+    for (int ci = 0; ci < EC / 32; ++ci) {
+      const int c = chalf * EC + 32 * ci;
       uint32_t v[32], w[16];
       // mode 0: ACC2 holds dK (scaled), ACC1 holds dV; mode 1: ACC1 holds dQ (scaled)
       tmem_ld_32x32(tmem_base + lane_base + (MODE == 0 ? ACC2 : ACC1) + c, v);
@@ -1320,10 +1335,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         float f[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * q4 + e]) * p.scale;
-        if (p.rope_cos != nullptr && row_g < p.S) {  // inverse rotation: sin -> -sin
-          const size_t ti = static_cast<size_t>(row_g) * (D / 2) + ((c + 8 * q4) >> 1);
-          const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + ti);
-          const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + ti);
+        if (rope_on) {  // inverse rotation: sin -> -sin
+          const float4 cs = rope_c[4 * ci + q4];
+          const float4 sn = rope_s[4 * ci + q4];
           const float a0 = f[0], a1 = f[1], a2 = f[2], a3 = f[3], a4 = f[4], a5 = f[5], a6 = f[6], a7 = f[7];
           f[0] = a0 * cs.x + a1 * sn.x; f[1] = a1 * cs.x - a0 * sn.x;
           f[2] = a2 * cs.y + a3 * sn.y; f[3] = a3 * cs.y - a2 * sn.y;
