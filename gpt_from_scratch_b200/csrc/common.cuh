@@ -103,7 +103,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. Returns false if the wait was abandoned (status recorded). The global timer
 // is slow to read, so it is only consulted every 4096 failed polls; the first reading
-// starts the budget.
+// starts the clock.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*ctx.abort_flag) return false;

@@ -3,6 +3,8 @@
     python -m gpt_from_scratch_b200.kernel_bench                 # all kernels, GPT-124M shapes
     python -m gpt_from_scratch_b200.kernel_bench --only gemm     # substring filter
     python -m gpt_from_scratch_b200.kernel_bench --small         # small shapes (for ncu captures)
+    python -m gpt_from_scratch_b200.kernel_bench --vs-cublas     # every GEMM shape next to torch.matmul
+    python -m gpt_from_scratch_b200.kernel_bench --vs-reference  # attention / RoPE next to the reference's Triton kernels
 
 Each kernel is launched directly through the native library (no autograd), timed with CUDA
 events after warm-up; between timed launches a buffer larger than the 126 MB L2 is
@@ -266,10 +268,52 @@ def vs_reference(dev, timer, iters):
           f"{t_ref:9.1f} {t_our:9.1f} {t_ref / t_our:6.2f}x")
 
 
+def vs_cublas(dev, timer, iters: int, small: bool) -> None:
+    """Every GEMM shape of the training step next to cuBLAS (``torch.matmul`` / ``torch.addmm`` on
+    the same operands and layouts; the residual GEMMs are compared against matmul + add, which is
+    what a framework without the epilogue launches)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g).bfloat16()  # noqa: E731
+    if small:
+        S, B, H, I, V = 1024, 4, 768, 3072, 8192
+    else:
+        S, B, H, I, V = 1024, 16, 768, 3072, 50304
+    M = S * B
+    shapes = [("fwd qkv", M, 3 * H, H, False, False, False), ("fwd out + residual", M, H, H, False, False, True),
+              ("fwd gate_up", M, 2 * I, H, False, False, False), ("fwd down + residual", M, H, I, False, False, True),
+              ("fwd lm_head", M, V, H, False, False, False),
+              ("dgrad qkv", M, H, 3 * H, False, True, False), ("dgrad gate_up", M, H, 2 * I, False, True, False),
+              ("dgrad down", M, I, H, False, True, False), ("dgrad lm_head", M, H, V, False, True, False),
+              ("wgrad gate_up", 2 * I, H, M, True, True, False), ("wgrad down", H, I, M, True, True, False),
+              ("wgrad lm_head", V, H, M, True, True, False)]
+    print(f"{'GEMM (M x N x K)':44s} {'cuBLAS us':>10s} {'ours us':>9s} {'ratio':>6s} {'ours TFLOP/s':>13s}")
+    for name, M_, N_, K_, a_mn, b_mn, add in shapes:
+        a = rnd(K_, M_) if a_mn else rnd(M_, K_)
+        b = rnd(K_, N_) if b_mn else rnd(N_, K_)
+        out = torch.empty(M_, N_, device=dev, dtype=torch.bfloat16)
+        res = rnd(M_, N_) if add else None
+        a_op = a.t() if a_mn else a                   # logical [M, K]
+        b_op = b if b_mn else b.t()                   # logical [K, N]
+
+        def ref():
+            torch.matmul(a_op, b_op, out=out)
+            if add:
+                out.add_(res)
+
+        def ours():
+            gemm_bf16(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, addend=res)
+        t_ref = timer.time_us(ref, iters=iters)
+        t_our = timer.time_us(ours, iters=iters)
+        tag = f"{name} ({M_} x {N_} x {K_})"
+        print(f"{tag:44s} {t_ref:10.1f} {t_our:9.1f} {t_ref / t_our:6.2f}x {2.0 * M_ * N_ * K_ / t_our / 1e6:13.1f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--vs-reference", action="store_true",
                     help="time the reference's Triton attention / RoPE (baseline/_ref) next to ours")
+    ap.add_argument("--vs-cublas", action="store_true",
+                    help="time cuBLAS (torch.matmul) on every GEMM shape of the step next to ours")
     ap.add_argument("--only", default=None)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
@@ -280,6 +324,9 @@ def main():
     bw, fl, kind = peaks()
     if args.vs_reference:
         vs_reference(dev, Timer(dev), args.iters)
+        return
+    if args.vs_cublas:
+        vs_cublas(dev, Timer(dev), args.iters, args.small)
         return
     cases = build_cases(dev, args.small)
     if args.only:

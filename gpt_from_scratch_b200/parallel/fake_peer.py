@@ -13,7 +13,7 @@ buffers that nothing executes for. What the absent ranks would have contributed 
 * or left missing (``peers_ready=False``): the flags never move, so a kernel's bounded wait
   runs out and reports ``STATUS_TIMEOUT_PEER_FLAG``. This exercises the time-out path of the
   signal protocol without a second process and without hanging anything (used with a
-  millisecond budget, comm kernels only).
+  millisecond limit, comm kernels only).
 
 Installed with ``with fake_peers(world, rank): ...`` it takes the place of the tensor- and
 data-parallel :class:`~.symm.SymmGroup` objects, so the operators of ``fused_comm`` run

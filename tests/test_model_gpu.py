@@ -91,7 +91,7 @@ def test_wait_probe_reports_timeout_and_context_survives(cuda_device, request):
     """A device-side wait on a flag nothing sets must give up, record a status and return."""
     from gpt_from_scratch_b200.ops import _lib
     flag = torch.zeros(1, dtype=torch.int32, device=cuda_device)
-    rc = _lib.lib().gfs_wait_probe(flag.data_ptr(), 2_000_000, _lib.stream_ptr())  # 2 ms budget
+    rc = _lib.lib().gfs_wait_probe(flag.data_ptr(), 2_000_000, _lib.stream_ptr())  # 2 ms limit
     assert rc == 0
     code, _ = _lib.read_status(clear=True)
     assert code == 9
