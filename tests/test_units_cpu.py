@@ -364,3 +364,44 @@ def test_gradient_buckets_cover_the_flat_buffer_in_aligned_pieces():
     b = st._make_buckets()
     assert b[-1] == (sum(sizes) - 50304 * 768, sum(sizes)), b
     assert b[0] == (0, 50304 * 768), b     # and the embedding table, produced last, another
+
+
+def test_pending_flag_counts_are_folded_into_the_base_words():
+    """Launches made outside a captured step advance the per-site host counts; before the next
+    replay they must move into the base words (the captured waits start from those) and restart
+    at zero. The bookkeeping is plain host code: exercised here on a group object without any
+    symmetric memory behind it."""
+    import ctypes
+    from gpt_from_scratch_b200.parallel import symm
+
+    grp = symm.SymmGroup.__new__(symm.SymmGroup)        # no CUDA, no rendezvous
+    grp.world, grp.rank, grp.device = 2, 0, torch.device("cpu")
+    grp._sites, grp._next_slot = {}, 0
+    grp._target_store = (ctypes.c_uint * symm.NUM_FLAG_SLOTS)()
+    grp._target_view = np.frombuffer(grp._target_store, dtype=np.uint32)
+    grp.base = torch.zeros(symm.NUM_FLAG_SLOTS, dtype=torch.int32)
+    grp.per_step = torch.zeros(symm.NUM_FLAG_SLOTS, dtype=torch.int32)
+    a, b = grp.site("a"), grp.site("b")
+    assert (a.slot0, b.slot0) == (0, 2) and grp.site("a") is a
+    assert not grp._target_view.any()
+    a.target.value += 3                                  # what a launcher does through byref(site.target)
+    ctypes.cast(ctypes.byref(b.target), ctypes.POINTER(ctypes.c_uint))[0] += 5
+    assert grp._target_view.any() and b.target.value == 5
+    saved = dict(symm._groups)
+    symm._groups.clear()
+    symm._groups["dp"] = grp
+    try:
+        symm.fold_pending()
+        assert grp.base[:4].tolist() == [3, 3, 5, 5] and int(grp.base[4:].abs().sum()) == 0
+        assert a.target.value == 0 and b.target.value == 0 and not grp._target_view.any()
+        symm.fold_pending()                              # nothing pending: nothing changes
+        assert grp.base[:4].tolist() == [3, 3, 5, 5]
+        # a capture: counts of the captured step become the per-step increments of the epilogue
+        a.target.value += 2
+        grp.record_per_step()
+        assert grp.per_step[:4].tolist() == [2, 2, 0, 0] and a.target.value == 0
+        symm.graph_epilogue()
+        assert grp.base[:4].tolist() == [5, 5, 5, 5]
+    finally:
+        symm._groups.clear()
+        symm._groups.update(saved)
