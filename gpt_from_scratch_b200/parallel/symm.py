@@ -14,7 +14,9 @@ counters (``csrc/common.cuh``); a kernel waits for ``base + target``. :func:`beg
 moves the counts reached so far into the base words and restarts the host counts at zero,
 :func:`graph_epilogue` (called inside the capture, last) adds the step's per-site totals to the
 base words, and :func:`end_graph_capture` records those totals and restarts the host counts
-again, so eager launches after (or between) replays stay consistent too.
+again. Launches made outside the graph afterwards count on the host again while the flags advance
+on the device; :func:`fold_pending`, called before every replay, moves such counts into the base
+words so that the captured waits keep starting from the flags' actual values.
 
 Allocation is collective: all ranks of the group must create the same buffers in the same
 order, which holds because they run the same program.
