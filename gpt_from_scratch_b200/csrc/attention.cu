@@ -940,8 +940,14 @@ struct BwdParams {
 // periods to land. head_dim 64 (P / dS in tensor memory, so the shared memory is free) uses 8
 // stages: 214 us against 224 us with 4 for the whole backward at the GPT-124M shape, 217 us with
 // 10; head_dim 128 has room for 3.
-template <int D, int MODE, int NBUF, int CW, int TS>
-__global__ void __launch_bounds__(64 + 32 * CW, NBUF == 1 ? 2 : 1)
+// PP ("ping-pong", needs CW = 8 and NBUF = 2): the two groups of four compute warps take alternate
+// streamed tiles (group = X/Y buffer) with all 64 columns per thread instead of column halves of the
+// same tile, so that one group's barrier tests, tensor-memory loads and stores overlap the other
+// group's arithmetic; and the MMAs are issued by TWO warps (warp 1: scores, warp 2: gradients),
+// because a single issuing warp needs ~ 1,350 cycles per tile in that scheme and the compute warps
+// then wait for scores.
+template <int D, int MODE, int NBUF, int CW, int TS, bool PP>
+__global__ void __launch_bounds__((PP ? 96 : 64) + 32 * CW, NBUF == 1 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant__ CUtensorMap tr2,
                  const __grid_constant__ CUtensorMap tt1, const __grid_constant__ CUtensorMap tt2,
                  const BwdParams p, int n_rt, int n_items) {
@@ -1018,8 +1024,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&xy_full[i], 1);
-      mbar_init(&xy_empty[i], CW);
-      mbar_init(&m_full[i], CW);
+      mbar_init(&xy_empty[i], PP ? 4 : CW);
+      mbar_init(&m_full[i], PP ? 4 : CW);
       mbar_init(&m_empty[i], 1);
     }
     mbar_init(acc_full, 1);
@@ -1081,8 +1087,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (PP && warp == 2)) {
     {  // whole warp, converged: the MMA / commit helpers elect the issuing lane
+      static_assert(!PP || (CW == 8 && NBUF == 2), "ping-pong needs two warp groups and two X/Y buffers");
+      const bool do_xy = !PP || warp == 1;      // this warp issues the score MMAs
       constexpr uint32_t idesc_xy = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, 0, 1);
       const uint32_t r1 = smem_u32(R1), r2 = smem_u32(R2);
@@ -1092,7 +1100,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
         if (w >= n_items) break;
         int rt, bh, t_begin, n_t;
         decode(w, rt, bh, t_begin, n_t);
-      mbar_wait(r_full, it & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
+      if (do_xy) mbar_wait(r_full, it & 1, wctx, STATUS_TIMEOUT_PIPE_FULL);
       auto issue_xy = [&](int t) {
         const int g = g0 + t;
         const int st = g % TS;                      // streamed-tile stage
@@ -1111,10 +1119,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       // pulled block t's X/Y into registers (xy_empty is signalled right after those loads),
       // i.e. while they are still doing block t's math, so they never wait for scores.
       constexpr int LA = (NBUF == 2 && TS >= 4) ? 2 : 1;
-      for (int t = 0; t < LA && t < n_t; ++t) issue_xy(t);
-      if (n_t <= LA) umma_commit_e(r_empty);
+      if (PP && do_xy) {
+        // score warp: runs ahead as far as the X/Y buffers and the streamed-tile ring allow
+        for (int t = 0; t < n_t; ++t) issue_xy(t);
+        umma_commit_e(r_empty);
+        g0 += n_t;
+        continue;
+      }
+      if (!PP) {
+        for (int t = 0; t < LA && t < n_t; ++t) issue_xy(t);
+        if (n_t <= LA) umma_commit_e(r_empty);
+      }
       for (int t = 0; t < n_t; ++t) {
-        if (t + LA < n_t) {
+        if (!PP && t + LA < n_t) {
           issue_xy(t + LA);
           if (t + LA + 1 == n_t) umma_commit_e(r_empty);  // the item's last score MMAs are issued
         }
@@ -1152,9 +1169,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
     }
   } else {
     const int quarter = warp & 3;
-    constexpr int COLS = 64 / (CW / 4);          // streamed columns handled by this thread
-    const int chalf = (CW == 8) ? ((warp - 2) >> 2) : 0;
-    const int cbase = chalf * COLS;
+    constexpr int FIRST_CW = PP ? 3 : 2;            // first compute warp
+    constexpr int COLS = PP ? 64 : 64 / (CW / 4);   // streamed columns handled by this thread
+    const int chalf = (CW == 8) ? ((warp - FIRST_CW) >> 2) : 0;   // warp group: epilogue column half; tile parity (PP) or column half of the math
+    const int cbase = PP ? 0 : chalf * COLS;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = p.scale * LOG2E_F;
@@ -1176,6 +1194,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       const int st = g % TS;                      // streamed-tile stage (for the column statistics)
       const int sb = (NBUF == 2) ? (g & 1) : 0;   // X / Y / P / dS buffer
       const uint32_t par = (NBUF == 2) ? ((g >> 1) & 1) : (g & 1);
+      if (PP && sb != chalf) continue;            // the other warp group's tile
       const int ti = t_begin + t;
       bool need_mask;
       if (MODE == 0) need_mask = (p.causal && ti < 2 * rt + 2) || ((ti + 1) * 64 > p.S);
@@ -1272,25 +1291,43 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tr1, const __grid_constant_
       };
       const uint32_t x_addr = tmem_base + lane_base + sb * 64;
       const uint32_t y_addr = tmem_base + lane_base + Y_COL + sb * 64;
-      tmem_ld_32x32(x_addr + cbase, xa);
-      tmem_ld_32x32(y_addr + cbase, ya);
-      if (COLS == 64) {
-        tmem_ld_32x32(x_addr + 32, xb);
-        tmem_ld_32x32(y_addr + 32, yb);
+      if (PP) {
+        // one 32-column half at a time in the same registers (all 64 columns at once would not fit
+        // the 168 registers of a thread); the X/Y buffer goes back once the second half is loaded
+        tmem_ld_32x32(x_addr, xa);
+        tmem_ld_32x32(y_addr, ya);
+        tmem_ld_wait_for(xa);
+        tmem_ld_wait_for(ya);
+        grad_chunk(xa, ya, 0);
+        tmem_ld_32x32(x_addr + 32, xa);
+        tmem_ld_32x32(y_addr + 32, ya);
+        tmem_ld_wait_for(xa);
+        tmem_ld_wait_for(ya);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xy_empty[sb]);
+        grad_chunk(xa, ya, 32);
+      } else {
+        tmem_ld_32x32(x_addr + cbase, xa);
+        tmem_ld_32x32(y_addr + cbase, ya);
+        if (COLS == 64) {
+          tmem_ld_32x32(x_addr + 32, xb);
+          tmem_ld_32x32(y_addr + 32, yb);
+        }
+        tmem_ld_wait_for(xa);
+        tmem_ld_wait_for(ya);
+        if (COLS == 64) {
+          tmem_ld_wait_for(xb);
+          tmem_ld_wait_for(yb);
+        }
+        // X / Y are in registers: hand the buffer back now so the next scores can be computed
+        // into it while this block's math runs
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xy_empty[sb]);
+        grad_chunk(xa, ya, cbase);
+        if (COLS == 64) grad_chunk(xb, yb, 32);
       }
-      tmem_ld_wait_for(xa);
-      tmem_ld_wait_for(ya);
-      if (COLS == 64) {
-        tmem_ld_wait_for(xb);
-        tmem_ld_wait_for(yb);
-      }
-      // X / Y are in registers: hand the buffer back now so the next scores can be computed
-      // into it while this block's math runs
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&xy_empty[sb]);
-      grad_chunk(xa, ya, cbase);
-      if (COLS == 64) grad_chunk(xb, yb, 32);
       if (PT) tmem_st_wait();
       tc_fence_before();
       if (!PT) fence_proxy_async_smem();
@@ -1490,7 +1527,7 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   const int n_items = n_rt * B * nh;
   const int ctas = std::min(n_items, gfs_host::sm_count());
   const int nbuf = 2;
-  const int bwd_threads = 64 + 32 * 8;
+  const int bwd_threads = ((D == 64) ? 96 : 64) + 32 * 8;   // head_dim 64: a second MMA-issuing warp
   const int ts = (D == 64) ? 8 : 3;
   const int m_bytes = (D == 64) ? 16384 : 2 * nbuf * 16384;   // head_dim 64: epilogue staging only
   const int smem = 2 * (D / 64) * 16384 + 2 * ts * (D / 64) * 8192 + m_bytes + ts * 512 + 512 + 1024;
@@ -1503,20 +1540,20 @@ int gfs_flash_bwd(const void* q, const void* k, const void* v, const void* o, co
   p1.out1 = static_cast<__nv_bfloat16*>(dq); p1.o1_ss = sdq[0]; p1.o1_bs = sdq[1]; p1.o1_hs = sdq[2];
   p1.out2 = nullptr; p1.o2_ss = p1.o2_bs = p1.o2_hs = 0;
   if (D == 64) {
-    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 8>, smem)) return -10; set_done[0] = true; }
-    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 8>, smem)) return -10; set_done[1] = true; }
-    gfs_host::launch_pdl(flash_bwd_kernel<64, 0, 2, 8, 8>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
+    if (!set_done[0]) { if (set_smem(flash_bwd_kernel<64, 0, 2, 8, 8, true>, smem)) return -10; set_done[0] = true; }
+    if (!set_done[1]) { if (set_smem(flash_bwd_kernel<64, 1, 2, 8, 8, true>, smem)) return -10; set_done[1] = true; }
+    gfs_host::launch_pdl(flash_bwd_kernel<64, 0, 2, 8, 8, true>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
                          *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    gfs_host::launch_pdl(flash_bwd_kernel<64, 1, 2, 8, 8>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
+    gfs_host::launch_pdl(flash_bwd_kernel<64, 1, 2, 8, 8, true>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
                          *k64, *v64, p1, n_rt, n_items);
   } else {
-    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3>, smem)) return -10; set_done[2] = true; }
-    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3>, smem)) return -10; set_done[3] = true; }
-    gfs_host::launch_pdl(flash_bwd_kernel<128, 0, 2, 8, 3>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
+    if (!set_done[2]) { if (set_smem(flash_bwd_kernel<128, 0, 2, 8, 3, false>, smem)) return -10; set_done[2] = true; }
+    if (!set_done[3]) { if (set_smem(flash_bwd_kernel<128, 1, 2, 8, 3, false>, smem)) return -10; set_done[3] = true; }
+    gfs_host::launch_pdl(flash_bwd_kernel<128, 0, 2, 8, 3, false>, dim3(ctas), dim3(bwd_threads), smem, stream, *k128, *v128,
                          *q64, *do64, p0, n_rt, n_items);
     if (cudaGetLastError() != cudaSuccess) return -12;
-    gfs_host::launch_pdl(flash_bwd_kernel<128, 1, 2, 8, 3>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
+    gfs_host::launch_pdl(flash_bwd_kernel<128, 1, 2, 8, 3, false>, dim3(ctas), dim3(bwd_threads), smem, stream, *q128, *do128,
                          *k64, *v64, p1, n_rt, n_items);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
